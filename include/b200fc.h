@@ -1,0 +1,145 @@
+/*
+ * b200fc — C ABI of the B200 (sm_100a) fully-connected / Llama-MLP engine that stands in for the CPU kernels of
+ * usstq/mm_amx.  Every entry point below replaces one interface of the reference; the citation gives the
+ * reference file:line (paths relative to the mm_amx tree).
+ *
+ * Conventions
+ *   - plain pointers and sizes only; all strides are in BYTES (tensor2D::stride, include/tensor2D.hpp:34);
+ *   - matrices are row-major; bf16 is the upper half of an IEEE fp32 (ov::bfloat16, include/bf16.hpp:18);
+ *   - unless a function name ends in _host, data pointers are DEVICE pointers of the current CUDA device and the
+ *     call is asynchronous on `stream` (a cudaStream_t passed as void*, NULL = default stream);
+ *   - every function returns a b200fc_status_t; b200fc_last_error() gives the message of the calling thread's last
+ *     failure.  Nothing aborts the process (the reference asserts / aborts, include/misc.hpp:289-293).
+ *   - there is no CPU fallback: without a CUDA device every compute call fails with B200FC_ERR_CUDA.
+ */
+#ifndef B200FC_H
+#define B200FC_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    B200FC_OK = 0,
+    B200FC_ERR_INVALID = 1,     /* bad argument (shape, stride, alignment, dtype combination) */
+    B200FC_ERR_CUDA = 2,        /* a CUDA runtime / driver call failed */
+    B200FC_ERR_UNSUPPORTED = 3, /* valid in the reference, not implemented here */
+    B200FC_ERR_NOMEM = 4,
+    B200FC_ERR_KERNEL = 5       /* a kernel reported a bounded wait that ran out */
+} b200fc_status_t;
+
+typedef enum { B200FC_BF16 = 0, B200FC_S8 = 1, B200FC_U8 = 2, B200FC_F32 = 3, B200FC_S32 = 4 } b200fc_dtype_t;
+
+/* Post-op steps, executed in this fixed order (amx_kernel::PP::Steps, include/kernels_amx.hpp:540-550, and
+ * PP::BiasGeluStore::operator(), :586-672):  [int32 accumulator -> fp32] -> DEQUANT -> BIAS -> GELU -> QUANT -> store.
+ * SILU_MUL is this library's addition for the fused MLP (runGateUp, tests/amx-mlp.cpp:707-737): the weight rows
+ * come in groups of 32 = 16 gate rows followed by the 16 up rows of the same channels, and the store writes
+ * silu(gate) * up for those 16 channels at column n/2.  It excludes the other steps. */
+enum {
+    B200FC_STEP_NONE = 0,
+    B200FC_STEP_DEQUANT = 1,
+    B200FC_STEP_BIAS = 2,
+    B200FC_STEP_GELU = 4,
+    B200FC_STEP_QUANT = 8,
+    B200FC_STEP_SILU_MUL = 16
+};
+
+/* What PP::BiasGeluStore<D, steps> captures (include/kernels_amx.hpp:552-583), as plain data.  Arrays are indexed by
+ * the GLOBAL output column n, as the reference functor is (kernels_amx.hpp:1250,1294). */
+typedef struct {
+    int steps;                     /* B200FC_STEP_* bitmask */
+    int out_dtype;                 /* B200FC_F32 / B200FC_BF16 / B200FC_S8, or B200FC_S32 = raw int32 accumulators */
+    void* C;                       /* output matrix [M, N] */
+    int64_t ldc_bytes;
+    const float* bias;             /* [N] fp32, needed with STEP_BIAS (set_bias, :560-563) */
+    float deq_scale;               /* per-tensor dequant scale (set_deq_scale, :565-570) */
+    const float* deq_scale_per_oc; /* optional [N]: extra per-output-channel dequant factor (no reference counterpart;
+                                      needed for per-channel int8 weights) */
+    float q_scale;                 /* per-tensor quant scale (set_q_scale(float), :572-577) */
+    const float* q_scale_per_oc;   /* optional [N]: per-output-channel quant scale (set_q_scale(float*), :578-583) */
+} b200fc_epilogue_t;
+
+/* ---- library ---------------------------------------------------------------------------------------------- */
+const char* b200fc_last_error(void);
+const char* b200fc_version(void);
+/* number of this library's kernels launched by the calling process so far (bench bookkeeping) */
+int64_t b200fc_launch_count(void);
+
+/* waits for `stream` and reports whether any kernel of this library gave up on a bounded wait since the last check
+ * (B200FC_ERR_KERNEL); the _host entry points do this themselves */
+int b200fc_sync_check(void* stream);
+
+/* ---- packed weights: the `internalB` cache of amx_kernel::Matmul (include/kernels_amx.hpp:1045-1072) ---------- */
+typedef struct b200fc_weight b200fc_weight_t;
+
+typedef enum {
+    B200FC_PACK_PLAIN = 0,       /* keep the dtype of B (bf16 / s8 / u8): repackB_1x2, kernels_amx.hpp:761-816 */
+    B200FC_PACK_QUANT_TENSOR = 1,/* bf16 B -> int8 with one absmax scale, the compressed-weight path
+                                    Matmul<bf16,int8_t,float>, kernels_amx.hpp:1363-1377 */
+    B200FC_PACK_INT8_CHANNEL = 2 /* s8 B + caller's per-output-channel fp32 scales [N] (no reference counterpart) */
+} b200fc_pack_mode_t;
+
+/* Packs B once.  transposeB = 0: B is [K, N]; 1: B is [N, K] (Matmul ctor flag, kernels_amx.hpp:1071, getSubMatB
+ * :699-705).  B may be a host or a device pointer.  `scales` is used by B200FC_PACK_INT8_CHANNEL only. */
+int b200fc_weight_pack(const void* B, int dtypeB, int K, int N, int64_t ldb_bytes, int transposeB, int pack_mode,
+                       const float* scales, b200fc_weight_t** out, void* stream);
+int b200fc_weight_free(b200fc_weight_t* w);
+/* K, N, dtype of the stored weights (B200FC_BF16/S8/U8), whether they are dequantised on the fly, tensor scale */
+int b200fc_weight_info(const b200fc_weight_t* w, int* K, int* N, int* dtype, int* compressed, float* deq_scale);
+/* copies the packed weights back as a plain row-major [N, K] matrix of their stored dtype (host or device dst) */
+int b200fc_weight_unpack(const b200fc_weight_t* w, void* dst, int64_t ld_bytes, void* stream);
+
+/* ---- Matmul::operator()(A, B, n0, n1, ppkernel), include/kernels_amx.hpp:1169-1314 and :1343-1516 ------------- */
+/* C[:, n0:n1) = postops(A[M,K] * W[:, n0:n1)).  dtypeA: B200FC_BF16 with bf16 or compressed weights, B200FC_S8 /
+ * B200FC_U8 with s8 / u8 weights.  With compressed weights STEP_DEQUANT is required and the weight's own scale(s)
+ * replace ep->deq_scale, as the reference's set_deq_scale() call does (kernels_amx.hpp:1379). */
+int b200fc_matmul(const b200fc_weight_t* W, const void* A, int dtypeA, int M, int K, int64_t lda_bytes, int n0, int n1,
+                  const b200fc_epilogue_t* ep, void* stream);
+/* Same call with A, ep->C, ep->bias and the per-channel scale arrays in HOST memory: stages them through device
+ * buffers owned by the weight object, runs, copies C back and synchronises the stream (what a caller of the CPU
+ * reference gets: results in host memory when the call returns). */
+int b200fc_matmul_host(b200fc_weight_t* W, const void* A, int dtypeA, int M, int K, int64_t lda_bytes, int n0, int n1,
+                       const b200fc_epilogue_t* ep, void* stream);
+
+/* ---- MatmulVector::operator()(A, b, c) and GemAvB, include/kernels_amx.hpp:959-1042, 1529-1618 --------------- */
+/* c[M] = A[M,K] * b[K]; dtype B200FC_BF16 -> fp32 c, B200FC_S8 -> int32 c.  Any K >= 1 (the reference limits K). */
+int b200fc_matvec(const void* A, int dtype, int M, int K, int64_t lda_bytes, const void* b, void* c, void* stream);
+int b200fc_matvec_host(const void* A, int dtype, int M, int K, int64_t lda_bytes, const void* b, void* c, void* stream);
+
+/* ---- fused Llama MLP: AMX_MLP::MLP::setup / run, tests/amx-mlp.cpp:752-783 ----------------------------------- */
+typedef struct b200fc_mlp b200fc_mlp_t;
+/* gate, up: [N, K]; down: [K, N]; bf16, contiguous, torch nn.Linear layout (host or device pointers).
+ * tp_size > 1 keeps only this rank's Megatron shard: rows [rank*N/tp, (rank+1)*N/tp) of gate and up and the same
+ * columns of down; b200fc_mlp_run_partial then yields the rank's fp32 contribution to the output.
+ * Requirements: K % 64 == 0, (N / tp_size) % 32 == 0 (the reference needs N % 32 == 0, K % 256 == 0, :552-553). */
+int b200fc_mlp_create(const void* gate, const void* up, const void* down, int K, int N, int tp_rank, int tp_size,
+                      b200fc_mlp_t** out, void* stream);
+int b200fc_mlp_free(b200fc_mlp_t* mlp);
+/* grows the internal activation buffer for up to max_M rows (the reference's actUp grows inside run, :771-776) */
+int b200fc_mlp_reserve(b200fc_mlp_t* mlp, int max_M);
+/* out[M,K] bf16 = down(silu(x gate^T) * (x up^T)); x [M,K] bf16.  tp_size must be 1. */
+int b200fc_mlp_run(b200fc_mlp_t* mlp, const void* x, int64_t ldx_bytes, int M, void* out, int64_t ldo_bytes,
+                   void* stream);
+/* this rank's contribution to the output, [M,K] in out_dtype B200FC_F32 or B200FC_BF16; the caller sums it over
+ * ranks (one all-reduce) and, for fp32, rounds to bf16 (the reference rounds after the fp32 sum, :672-680) */
+int b200fc_mlp_run_partial(b200fc_mlp_t* mlp, const void* x, int64_t ldx_bytes, int M, void* partial, int out_dtype,
+                           int64_t ldp_bytes, void* stream);
+/* x and out in HOST memory; copies, runs, copies back, synchronises. */
+int b200fc_mlp_run_host(b200fc_mlp_t* mlp, const void* x, int64_t ldx_bytes, int M, void* out, int64_t ldo_bytes,
+                        void* stream);
+/* device pointer to the [M, N/tp] bf16 activation of the last run (debug / layer-wise parity) */
+const void* b200fc_mlp_act(const b200fc_mlp_t* mlp);
+
+/* ---- helpers -------------------------------------------------------------------------------------------------- */
+/* bf16 round-to-nearest-even of fp32 on the device: out[i] = bf16(a[i] + (b ? b[i] : 0)) */
+int b200fc_add_round_bf16(const float* a, const float* b, void* out_bf16, int64_t n, void* stream);
+/* writes `bytes` bytes of a scratch buffer larger than L2 so that the next kernel starts cache-cold
+ * (the role of the reference's clflush helper, torch-ext/amx_mlp.cpp:514-522) */
+int b200fc_flush_l2(void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200FC_H */

@@ -1,0 +1,483 @@
+// C ABI of the b200fc library (declared in include/b200fc.h): argument checking, packed-weight and MLP objects,
+// dispatch between the decode (gemv.cu) and prefill (gemm_tc.cu) kernels, host-buffer convenience entry points.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <new>
+#include "common.cuh"
+
+namespace b200fc {
+
+// ---- error / bookkeeping --------------------------------------------------------------------------------------------
+static thread_local char g_err[512] = "";
+static std::atomic<long long> g_launches{0};
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+int cuda_fail(cudaError_t e, const char* what) {
+    set_error("CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+    return e == cudaErrorMemoryAllocation ? B200FC_ERR_NOMEM : B200FC_ERR_CUDA;
+}
+void count_launch(int n) { g_launches += n; }
+
+static std::mutex g_mu;
+static std::map<int, int*> g_status;  // per device
+
+int* kernel_status_word() {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_status.find(dev);
+    if (it != g_status.end()) return it->second;
+    int* p = nullptr;
+    if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, sizeof(int));
+    g_status[dev] = p;
+    return p;
+}
+
+int check_kernel_status(cudaStream_t s) {
+    int* p = kernel_status_word();
+    if (!p) { set_error("no kernel status word"); return B200FC_ERR_CUDA; }
+    int v = 0;
+    B200FC_CUDA(cudaMemcpyAsync(&v, p, sizeof(int), cudaMemcpyDeviceToHost, s));
+    B200FC_CUDA(cudaStreamSynchronize(s));
+    if (v != 0) {
+        cudaMemsetAsync(p, 0, sizeof(int), s);
+        set_error("a kernel gave up on a bounded wait (code %d)", v);
+        return B200FC_ERR_KERNEL;
+    }
+    return B200FC_OK;
+}
+
+// Per-(device, stream) scratch for re-strided activations.  Work on one stream is ordered, so one buffer per stream
+// is enough; it only grows.
+struct Scratch { void* p = nullptr; size_t bytes = 0; };
+static std::map<std::pair<int, cudaStream_t>, Scratch> g_scratch;
+
+static int get_scratch(size_t bytes, cudaStream_t s, void** out) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lk(g_mu);
+    Scratch& sc = g_scratch[{dev, s}];
+    if (sc.bytes < bytes) {
+        if (sc.p) { cudaStreamSynchronize(s); cudaFree(sc.p); sc.p = nullptr; sc.bytes = 0; }
+        B200FC_CUDA(cudaMalloc(&sc.p, bytes));
+        sc.bytes = bytes;
+    }
+    *out = sc.p;
+    return B200FC_OK;
+}
+
+static int grow(void** p, size_t* have, size_t need, cudaStream_t s) {
+    if (*have >= need) return B200FC_OK;
+    if (*p) { cudaStreamSynchronize(s); cudaFree(*p); *p = nullptr; *have = 0; }
+    B200FC_CUDA(cudaMalloc(p, need));
+    *have = need;
+    return B200FC_OK;
+}
+
+static int elem_size(int dtype) {
+    switch (dtype) {
+        case B200FC_BF16: return 2;
+        case B200FC_S8: case B200FC_U8: return 1;
+        case B200FC_F32: case B200FC_S32: return 4;
+    }
+    return 0;
+}
+
+static bool is_device_ptr(const void* p) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
+    return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+static int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+static int alloc_weight(Weight& w, int K, int N, int dtype) {
+    const int es = elem_size(dtype);
+    w.K = K; w.N = N; w.dtype = dtype;
+    w.K_pad = round_up(K * es, kKPadBytes) / es;
+    w.N_pad = round_up(N, kRowPad);
+    B200FC_CUDA(cudaMalloc(&w.data, (size_t)w.N_pad * w.K_pad * es));
+    return B200FC_OK;
+}
+
+static void free_weight(Weight* w) {
+    if (!w) return;
+    cudaFree(w->data); cudaFree(w->scale_per_oc); cudaFree(w->dequant_bf16);
+    cudaFree(w->stage_A); cudaFree(w->stage_C); cudaFree(w->stage_vec);
+}
+
+// Makes [rows, row_bytes] of a host or device matrix available on the device.  Device sources are used in place.
+struct DevSrc {
+    const void* p = nullptr; int64_t ld = 0; void* owned = nullptr;
+    ~DevSrc() { if (owned) cudaFree(owned); }
+};
+static int to_device(const void* src, int64_t ld, int rows, size_t row_bytes, cudaStream_t s, DevSrc& out) {
+    if (is_device_ptr(src)) { out.p = src; out.ld = ld; return B200FC_OK; }
+    size_t pitch = (row_bytes + 15) / 16 * 16;
+    B200FC_CUDA(cudaMalloc(&out.owned, pitch * (size_t)rows));
+    B200FC_CUDA(cudaMemcpy2DAsync(out.owned, pitch, src, (size_t)ld, row_bytes, (size_t)rows, cudaMemcpyHostToDevice, s));
+    out.p = out.owned; out.ld = (int64_t)pitch;
+    return B200FC_OK;
+}
+
+static int validate_epilogue(const b200fc_epilogue_t* ep, bool int_acc) {
+    if (!ep || !ep->C) { set_error("epilogue / C is null"); return B200FC_ERR_INVALID; }
+    const int s = ep->steps;
+    if (s & ~31) { set_error("unknown post-op bits 0x%x", s); return B200FC_ERR_INVALID; }
+    if (s & B200FC_STEP_SILU_MUL) {
+        if (s != B200FC_STEP_SILU_MUL || ep->out_dtype != B200FC_BF16 || int_acc) {
+            set_error("SILU_MUL excludes the other steps and needs a bf16 GEMM with bf16 output");
+            return B200FC_ERR_INVALID;
+        }
+    }
+    if ((s & B200FC_STEP_BIAS) && !ep->bias) { set_error("STEP_BIAS without a bias pointer"); return B200FC_ERR_INVALID; }
+    if (ep->out_dtype == B200FC_S32) {
+        if (!int_acc || s != 0) { set_error("raw int32 output needs an 8-bit GEMM and no post-op"); return B200FC_ERR_INVALID; }
+    } else if (ep->out_dtype != B200FC_F32 && ep->out_dtype != B200FC_BF16 && ep->out_dtype != B200FC_S8) {
+        set_error("out_dtype must be f32, bf16, s8 (or s32 for raw accumulators)");
+        return B200FC_ERR_INVALID;
+    }
+    return B200FC_OK;
+}
+
+static int matmul_device(const Weight& w, Weight* w_mut, const void* A, int dtypeA, int M, int K, int64_t lda, int n0,
+                         int n1, const b200fc_epilogue_t* ep_in, cudaStream_t s) {
+    if (M < 0 || K != w.K) { set_error("matmul: K=%d does not match the packed weights (K=%d) or M<0", K, w.K); return B200FC_ERR_INVALID; }
+    if (n0 < 0 || n1 > w.N || n0 > n1) { set_error("matmul: column range [%d,%d) outside [0,%d)", n0, n1, w.N); return B200FC_ERR_INVALID; }
+    const bool a8 = dtypeA == B200FC_S8 || dtypeA == B200FC_U8;
+    if (!a8 && dtypeA != B200FC_BF16) { set_error("matmul: dtypeA must be bf16, s8 or u8"); return B200FC_ERR_INVALID; }
+    if (a8 && (w.dtype == B200FC_BF16 || w.compressed)) { set_error("matmul: 8-bit activations need plain 8-bit weights"); return B200FC_ERR_INVALID; }
+    if (!a8 && w.dtype != B200FC_BF16 && !w.compressed) { set_error("matmul: bf16 activations need bf16 or compressed weights"); return B200FC_ERR_INVALID; }
+    int rc = validate_epilogue(ep_in, a8);
+    if (rc) return rc;
+    if (lda < (int64_t)K * elem_size(dtypeA)) { set_error("matmul: lda smaller than a row"); return B200FC_ERR_INVALID; }
+    if (M == 0 || n0 == n1) return B200FC_OK;
+
+    Epilogue ep;
+    ep.steps = ep_in->steps; ep.out_dtype = ep_in->out_dtype; ep.C = ep_in->C; ep.ldc = ep_in->ldc_bytes;
+    ep.bias = ep_in->bias; ep.deq_scale = ep_in->deq_scale; ep.deq_per_oc = ep_in->deq_scale_per_oc;
+    ep.q_scale = ep_in->q_scale; ep.q_per_oc = ep_in->q_scale_per_oc;
+    if (w.compressed) {
+        if (!(ep.steps & B200FC_STEP_DEQUANT)) { set_error("matmul: compressed weights need STEP_DEQUANT"); return B200FC_ERR_INVALID; }
+        ep.deq_scale = w.deq_scale;          // the weight's scale replaces the caller's (kernels_amx.hpp:1379)
+        ep.deq_per_oc = w.scale_per_oc;
+    }
+    if ((ep.steps & B200FC_STEP_SILU_MUL) && ((n0 % 32) || ((n1 - n0) % 32))) {
+        set_error("matmul: SILU_MUL needs n0 and n1 multiples of 32");
+        return B200FC_ERR_INVALID;
+    }
+
+    if (!a8 && M <= 16) return launch_gemv(w, A, M, K, lda, n0, n1, ep, s);
+
+    // tensor-core path: TMA needs a 16-byte aligned base and leading dimension
+    const void* A_use = A;
+    int64_t lda_use = lda;
+    if (((uintptr_t)A & 15) || (lda & 15)) {
+        const int es = elem_size(dtypeA);
+        int64_t ld2 = round_up(K * es, 16);
+        void* buf = nullptr;
+        rc = get_scratch((size_t)ld2 * M, s, &buf);
+        if (rc) return rc;
+        rc = launch_copy2d(A, lda, buf, ld2, M, K * es, (int)ld2, s);
+        if (rc) return rc;
+        A_use = buf; lda_use = ld2;
+    }
+    if (w.compressed) {
+        // M > 16 with int8-compressed weights: widen the weights to bf16 once (exact) and run the bf16 GEMM
+        if (!w.dequant_bf16) {
+            if (!w_mut) { set_error("internal: compressed weight without a mutable handle"); return B200FC_ERR_INVALID; }
+            B200FC_CUDA(cudaMalloc(&w_mut->dequant_bf16, (size_t)w.N_pad * w.K_pad * 2));
+            rc = launch_dequant_bf16(w, w_mut->dequant_bf16, w.K_pad, s);
+            if (rc) return rc;
+        }
+        return launch_gemm_tc(w.dequant_bf16, B200FC_BF16, w.K_pad, w.N_pad, A_use, B200FC_BF16, M, K, lda_use, n0, n1, ep, s);
+    }
+    return launch_gemm_tc(w.data, w.dtype, w.K_pad, w.N_pad, A_use, dtypeA, M, K, lda_use, n0, n1, ep, s);
+}
+
+struct Mlp {
+    int K = 0, N = 0, Ns = 0;  // hidden, intermediate, this rank's share of the intermediate dimension
+    int tp_rank = 0, tp_size = 1;
+    Weight gate_up, down;
+    void* act = nullptr; size_t act_bytes = 0;      // [M, Ns] bf16
+    void* stage_x = nullptr; size_t stage_x_bytes = 0;
+    void* stage_o = nullptr; size_t stage_o_bytes = 0;
+};
+
+static int mlp_run_device(Mlp& m, const void* x, int64_t ldx, int M, void* out, int out_dtype, int64_t ldo, cudaStream_t s) {
+    if (M < 0) { set_error("mlp: M < 0"); return B200FC_ERR_INVALID; }
+    if (M == 0) return B200FC_OK;
+    int rc = grow(&m.act, &m.act_bytes, (size_t)M * m.Ns * 2, s);
+    if (rc) return rc;
+    b200fc_epilogue_t e1 = {};
+    e1.steps = B200FC_STEP_SILU_MUL; e1.out_dtype = B200FC_BF16; e1.C = m.act; e1.ldc_bytes = (int64_t)m.Ns * 2;
+    rc = matmul_device(m.gate_up, nullptr, x, B200FC_BF16, M, m.K, ldx, 0, 2 * m.Ns, &e1, s);
+    if (rc) return rc;
+    b200fc_epilogue_t e2 = {};
+    e2.steps = 0; e2.out_dtype = out_dtype; e2.C = out; e2.ldc_bytes = ldo;
+    return matmul_device(m.down, nullptr, m.act, B200FC_BF16, M, m.Ns, (int64_t)m.Ns * 2, 0, m.K, &e2, s);
+}
+
+}  // namespace b200fc
+
+using namespace b200fc;
+
+struct b200fc_weight { Weight w; };
+struct b200fc_mlp { Mlp m; };
+
+extern "C" {
+
+const char* b200fc_last_error(void) { return g_err; }
+const char* b200fc_version(void) { return "b200fc 0.1 (sm_100a)"; }
+int64_t b200fc_launch_count(void) { return (int64_t)g_launches.load(); }
+
+int b200fc_sync_check(void* stream) { return check_kernel_status((cudaStream_t)stream); }
+
+int b200fc_weight_pack(const void* B, int dtypeB, int K, int N, int64_t ldb, int transposeB, int pack_mode,
+                       const float* scales, b200fc_weight_t** out, void* stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!B || !out || K <= 0 || N <= 0) { set_error("weight_pack: null pointer or empty shape"); return B200FC_ERR_INVALID; }
+    const int es = elem_size(dtypeB);
+    if (dtypeB != B200FC_BF16 && dtypeB != B200FC_S8 && dtypeB != B200FC_U8) { set_error("weight_pack: dtypeB must be bf16, s8 or u8"); return B200FC_ERR_INVALID; }
+    const int rows = transposeB ? N : K, cols = transposeB ? K : N;
+    if (ldb < (int64_t)cols * es) { set_error("weight_pack: ldb smaller than a row"); return B200FC_ERR_INVALID; }
+    if (pack_mode == B200FC_PACK_QUANT_TENSOR && dtypeB != B200FC_BF16) { set_error("weight_pack: QUANT_TENSOR needs bf16 weights"); return B200FC_ERR_INVALID; }
+    if (pack_mode == B200FC_PACK_INT8_CHANNEL && (dtypeB != B200FC_S8 || !scales)) { set_error("weight_pack: INT8_CHANNEL needs s8 weights and scales"); return B200FC_ERR_INVALID; }
+    if (pack_mode < 0 || pack_mode > 2) { set_error("weight_pack: unknown pack mode"); return B200FC_ERR_INVALID; }
+
+    b200fc_weight_t* h = new (std::nothrow) b200fc_weight_t;
+    if (!h) { set_error("out of host memory"); return B200FC_ERR_NOMEM; }
+    Weight& w = h->w;
+    int rc;
+    {
+        DevSrc src;
+        rc = to_device(B, ldb, rows, (size_t)cols * es, s, src);
+        if (!rc) rc = alloc_weight(w, K, N, pack_mode == B200FC_PACK_QUANT_TENSOR ? B200FC_S8 : dtypeB);
+        if (!rc) {
+            if (pack_mode == B200FC_PACK_QUANT_TENSOR) {
+                float* absmax = nullptr;
+                rc = cudaMalloc(&absmax, sizeof(float)) == cudaSuccess ? 0 : B200FC_ERR_NOMEM;
+                if (!rc) rc = launch_absmax(src.p, rows, cols, src.ld, absmax, s);
+                if (!rc) rc = launch_quant_pack(src.p, K, N, src.ld, transposeB, w, absmax, s);
+                float mx = 0.0f;
+                if (!rc && cudaMemcpyAsync(&mx, absmax, sizeof(float), cudaMemcpyDeviceToHost, s) != cudaSuccess) rc = B200FC_ERR_CUDA;
+                if (!rc && cudaStreamSynchronize(s) != cudaSuccess) rc = B200FC_ERR_CUDA;
+                cudaFree(absmax);
+                w.compressed = true;
+                w.deq_scale = mx / 127;  // dequant_scale_B = max / 127 (kernels_amx.hpp:1373)
+            } else {
+                rc = launch_pack(src.p, dtypeB, K, N, src.ld, transposeB, w, s);
+                if (!rc && pack_mode == B200FC_PACK_INT8_CHANNEL) {
+                    w.compressed = true;
+                    w.deq_scale = 1.0f;
+                    if (cudaMalloc(&w.scale_per_oc, sizeof(float) * w.N_pad) != cudaSuccess) rc = B200FC_ERR_NOMEM;
+                    if (!rc) cudaMemsetAsync(w.scale_per_oc, 0, sizeof(float) * w.N_pad, s);
+                    if (!rc && cudaMemcpyAsync(w.scale_per_oc, scales, sizeof(float) * N, cudaMemcpyDefault, s) != cudaSuccess) rc = B200FC_ERR_CUDA;
+                }
+            }
+        }
+        if (!rc && cudaStreamSynchronize(s) != cudaSuccess) rc = B200FC_ERR_CUDA;  // the staged source dies with `src`
+    }
+    if (rc) {
+        if (rc == B200FC_ERR_NOMEM) set_error("weight_pack: out of device memory");
+        else if (rc == B200FC_ERR_CUDA && !g_err[0]) set_error("weight_pack: CUDA failure: %s", cudaGetErrorString(cudaGetLastError()));
+        free_weight(&w); delete h; return rc;
+    }
+    *out = h;
+    return B200FC_OK;
+}
+
+int b200fc_weight_free(b200fc_weight_t* w) {
+    if (!w) return B200FC_OK;
+    free_weight(&w->w);
+    delete w;
+    return B200FC_OK;
+}
+
+int b200fc_weight_info(const b200fc_weight_t* w, int* K, int* N, int* dtype, int* compressed, float* deq_scale) {
+    if (!w) { set_error("weight_info: null handle"); return B200FC_ERR_INVALID; }
+    if (K) *K = w->w.K;
+    if (N) *N = w->w.N;
+    if (dtype) *dtype = w->w.dtype;
+    if (compressed) *compressed = w->w.compressed ? 1 : 0;
+    if (deq_scale) *deq_scale = w->w.deq_scale;
+    return B200FC_OK;
+}
+
+int b200fc_weight_unpack(const b200fc_weight_t* h, void* dst, int64_t ld_bytes, void* stream) {
+    if (!h || !dst) { set_error("weight_unpack: null pointer"); return B200FC_ERR_INVALID; }
+    const Weight& w = h->w;
+    const int es = elem_size(w.dtype);
+    B200FC_CUDA(cudaMemcpy2DAsync(dst, (size_t)ld_bytes, w.data, (size_t)w.K_pad * es, (size_t)w.K * es, (size_t)w.N,
+                                  cudaMemcpyDefault, (cudaStream_t)stream));
+    B200FC_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    return B200FC_OK;
+}
+
+int b200fc_matmul(const b200fc_weight_t* W, const void* A, int dtypeA, int M, int K, int64_t lda_bytes, int n0, int n1,
+                  const b200fc_epilogue_t* ep, void* stream) {
+    if (!W || !A) { set_error("matmul: null pointer"); return B200FC_ERR_INVALID; }
+    return matmul_device(W->w, const_cast<Weight*>(&W->w), A, dtypeA, M, K, lda_bytes, n0, n1, ep, (cudaStream_t)stream);
+}
+
+int b200fc_matmul_host(b200fc_weight_t* W, const void* A, int dtypeA, int M, int K, int64_t lda, int n0, int n1,
+                       const b200fc_epilogue_t* ep, void* stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!W || !A || !ep || !ep->C) { set_error("matmul_host: null pointer"); return B200FC_ERR_INVALID; }
+    Weight& w = W->w;
+    if (M <= 0 || n1 <= n0 || n0 < 0 || n1 > w.N) { set_error("matmul_host: empty or invalid range"); return B200FC_ERR_INVALID; }
+    const int esA = elem_size(dtypeA), esC = elem_size(ep->out_dtype);
+    if (!esA || !esC) { set_error("matmul_host: bad dtype"); return B200FC_ERR_INVALID; }
+    const bool silu = (ep->steps & B200FC_STEP_SILU_MUL) != 0;
+    const size_t rowA = (size_t)K * esA, ldA = (rowA + 15) / 16 * 16;
+    const int out_cols = silu ? (n1 - n0) / 2 : (n1 - n0);
+    const size_t rowC = (size_t)out_cols * esC, ldC = (rowC + 15) / 16 * 16;
+    int rc = grow(&w.stage_A, &w.stage_A_bytes, ldA * M, s);
+    if (!rc) rc = grow(&w.stage_C, &w.stage_C_bytes, ldC * M, s);
+    size_t vec_floats = (size_t)n1 * 3;
+    void* sv = w.stage_vec; size_t have = w.stage_vec_floats * sizeof(float);
+    if (!rc) rc = grow(&sv, &have, vec_floats * sizeof(float), s);
+    w.stage_vec = (float*)sv; w.stage_vec_floats = have / sizeof(float);
+    if (rc) return rc;
+    B200FC_CUDA(cudaMemcpy2DAsync(w.stage_A, ldA, A, (size_t)lda, rowA, (size_t)M, cudaMemcpyHostToDevice, s));
+    b200fc_epilogue_t e = *ep;
+    float* v = w.stage_vec;
+    if (ep->bias) { B200FC_CUDA(cudaMemcpyAsync(v, ep->bias, sizeof(float) * n1, cudaMemcpyHostToDevice, s)); e.bias = v; }
+    if (ep->deq_scale_per_oc) { B200FC_CUDA(cudaMemcpyAsync(v + n1, ep->deq_scale_per_oc, sizeof(float) * n1, cudaMemcpyHostToDevice, s)); e.deq_scale_per_oc = v + n1; }
+    if (ep->q_scale_per_oc) { B200FC_CUDA(cudaMemcpyAsync(v + 2 * (size_t)n1, ep->q_scale_per_oc, sizeof(float) * n1, cudaMemcpyHostToDevice, s)); e.q_scale_per_oc = v + 2 * (size_t)n1; }
+    // the kernels index C by the global column: shift the base so that column n0 lands at the start of the staging row
+    const int64_t col0 = silu ? (int64_t)(n0 / 2) * esC : (int64_t)n0 * esC;
+    e.C = (char*)w.stage_C - col0;
+    e.ldc_bytes = (int64_t)ldC;
+    rc = matmul_device(w, &w, w.stage_A, dtypeA, M, K, (int64_t)ldA, n0, n1, &e, s);
+    if (rc) return rc;
+    B200FC_CUDA(cudaMemcpy2DAsync((char*)ep->C + col0, (size_t)ep->ldc_bytes, w.stage_C, ldC, rowC, (size_t)M,
+                                  cudaMemcpyDeviceToHost, s));
+    return check_kernel_status(s);
+}
+
+int b200fc_matvec(const void* A, int dtype, int M, int K, int64_t lda, const void* b, void* c, void* stream) {
+    if (!A || !b || !c || K <= 0 || M < 0) { set_error("matvec: null pointer or bad shape"); return B200FC_ERR_INVALID; }
+    if (lda < (int64_t)K * elem_size(dtype)) { set_error("matvec: lda smaller than a row"); return B200FC_ERR_INVALID; }
+    return launch_matvec(A, dtype, M, K, lda, b, c, (cudaStream_t)stream);
+}
+
+int b200fc_matvec_host(const void* A, int dtype, int M, int K, int64_t lda, const void* b, void* c, void* stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!A || !b || !c || K <= 0 || M <= 0) { set_error("matvec_host: null pointer or bad shape"); return B200FC_ERR_INVALID; }
+    const int es = elem_size(dtype);
+    if (dtype != B200FC_BF16 && dtype != B200FC_S8) { set_error("matvec: dtype must be bf16 or s8"); return B200FC_ERR_INVALID; }
+    const size_t row = (size_t)K * es, ld = (row + 15) / 16 * 16;
+    void* buf = nullptr;
+    int rc = get_scratch(ld * M + ld + (size_t)M * 4 + 64, s, &buf);
+    if (rc) return rc;
+    char* dA = (char*)buf; char* db = dA + ld * M; char* dc = db + ld;
+    B200FC_CUDA(cudaMemcpy2DAsync(dA, ld, A, (size_t)lda, row, (size_t)M, cudaMemcpyHostToDevice, s));
+    B200FC_CUDA(cudaMemcpyAsync(db, b, row, cudaMemcpyHostToDevice, s));
+    rc = launch_matvec(dA, dtype, M, K, (int64_t)ld, db, dc, s);
+    if (rc) return rc;
+    B200FC_CUDA(cudaMemcpyAsync(c, dc, (size_t)M * 4, cudaMemcpyDeviceToHost, s));
+    B200FC_CUDA(cudaStreamSynchronize(s));
+    return B200FC_OK;
+}
+
+int b200fc_mlp_create(const void* gate, const void* up, const void* down, int K, int N, int tp_rank, int tp_size,
+                      b200fc_mlp_t** out, void* stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!gate || !up || !down || !out) { set_error("mlp_create: null pointer"); return B200FC_ERR_INVALID; }
+    if (tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size || K <= 0 || N <= 0 || N % tp_size) { set_error("mlp_create: bad tensor-parallel split"); return B200FC_ERR_INVALID; }
+    const int Ns = N / tp_size;
+    if (K % 64 || Ns % 32) { set_error("mlp_create: need K %% 64 == 0 and (N / tp_size) %% 32 == 0"); return B200FC_ERR_INVALID; }
+    b200fc_mlp_t* h = new (std::nothrow) b200fc_mlp_t;
+    if (!h) { set_error("out of host memory"); return B200FC_ERR_NOMEM; }
+    Mlp& m = h->m;
+    m.K = K; m.N = N; m.Ns = Ns; m.tp_rank = tp_rank; m.tp_size = tp_size;
+    int rc;
+    {
+        // this rank's rows of gate / up ([N, K]) and columns of down ([K, N])
+        const char* g0 = (const char*)gate + (size_t)tp_rank * Ns * K * 2;
+        const char* u0 = (const char*)up + (size_t)tp_rank * Ns * K * 2;
+        const char* d0 = (const char*)down + (size_t)tp_rank * Ns * 2;
+        DevSrc sg, su, sd;
+        rc = to_device(g0, (int64_t)K * 2, Ns, (size_t)K * 2, s, sg);
+        if (!rc) rc = to_device(u0, (int64_t)K * 2, Ns, (size_t)K * 2, s, su);
+        if (!rc) rc = to_device(d0, (int64_t)N * 2, K, (size_t)Ns * 2, s, sd);
+        if (!rc && sg.ld != su.ld) { set_error("mlp_create: gate and up must live in the same kind of memory"); rc = B200FC_ERR_INVALID; }
+        if (!rc) rc = alloc_weight(m.gate_up, K, 2 * Ns, B200FC_BF16);
+        if (!rc) rc = alloc_weight(m.down, Ns, K, B200FC_BF16);
+        if (!rc) rc = launch_pack_gate_up(sg.p, su.p, sg.ld, K, Ns, m.gate_up, s);
+        if (!rc) rc = launch_pack(sd.p, B200FC_BF16, Ns, K, sd.ld, 1, m.down, s);
+        if (!rc && cudaStreamSynchronize(s) != cudaSuccess) { rc = cuda_fail(cudaGetLastError(), "mlp_create sync"); }
+    }
+    if (rc) { free_weight(&m.gate_up); free_weight(&m.down); delete h; return rc; }
+    *out = h;
+    return B200FC_OK;
+}
+
+int b200fc_mlp_free(b200fc_mlp_t* h) {
+    if (!h) return B200FC_OK;
+    free_weight(&h->m.gate_up); free_weight(&h->m.down);
+    cudaFree(h->m.act); cudaFree(h->m.stage_x); cudaFree(h->m.stage_o);
+    delete h;
+    return B200FC_OK;
+}
+
+int b200fc_mlp_reserve(b200fc_mlp_t* h, int max_M) {
+    if (!h || max_M < 0) { set_error("mlp_reserve: bad argument"); return B200FC_ERR_INVALID; }
+    return grow(&h->m.act, &h->m.act_bytes, (size_t)max_M * h->m.Ns * 2, 0);
+}
+
+int b200fc_mlp_run(b200fc_mlp_t* h, const void* x, int64_t ldx, int M, void* out, int64_t ldo, void* stream) {
+    if (!h || !x || !out) { set_error("mlp_run: null pointer"); return B200FC_ERR_INVALID; }
+    if (h->m.tp_size != 1) { set_error("mlp_run: tensor-parallel shard; use mlp_run_partial and sum over ranks"); return B200FC_ERR_INVALID; }
+    return mlp_run_device(h->m, x, ldx, M, out, B200FC_BF16, ldo, (cudaStream_t)stream);
+}
+
+int b200fc_mlp_run_partial(b200fc_mlp_t* h, const void* x, int64_t ldx, int M, void* partial, int out_dtype, int64_t ldp,
+                           void* stream) {
+    if (!h || !x || !partial) { set_error("mlp_run_partial: null pointer"); return B200FC_ERR_INVALID; }
+    if (out_dtype != B200FC_F32 && out_dtype != B200FC_BF16) { set_error("mlp_run_partial: out_dtype must be f32 or bf16"); return B200FC_ERR_INVALID; }
+    return mlp_run_device(h->m, x, ldx, M, partial, out_dtype, ldp, (cudaStream_t)stream);
+}
+
+int b200fc_mlp_run_host(b200fc_mlp_t* h, const void* x, int64_t ldx, int M, void* out, int64_t ldo, void* stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!h || !x || !out || M <= 0) { set_error("mlp_run_host: null pointer or M <= 0"); return B200FC_ERR_INVALID; }
+    Mlp& m = h->m;
+    if (m.tp_size != 1) { set_error("mlp_run_host: tensor-parallel shard"); return B200FC_ERR_INVALID; }
+    const size_t row = (size_t)m.K * 2;
+    int rc = grow(&m.stage_x, &m.stage_x_bytes, row * M, s);
+    if (!rc) rc = grow(&m.stage_o, &m.stage_o_bytes, row * M, s);
+    if (rc) return rc;
+    B200FC_CUDA(cudaMemcpy2DAsync(m.stage_x, row, x, (size_t)ldx, row, (size_t)M, cudaMemcpyHostToDevice, s));
+    rc = mlp_run_device(m, m.stage_x, (int64_t)row, M, m.stage_o, B200FC_BF16, (int64_t)row, s);
+    if (rc) return rc;
+    B200FC_CUDA(cudaMemcpy2DAsync(out, (size_t)ldo, m.stage_o, row, row, (size_t)M, cudaMemcpyDeviceToHost, s));
+    return check_kernel_status(s);
+}
+
+const void* b200fc_mlp_act(const b200fc_mlp_t* h) { return h ? h->m.act : nullptr; }
+
+int b200fc_add_round_bf16(const float* a, const float* b, void* out, int64_t n, void* stream) {
+    if (!a || !out || n < 0) { set_error("add_round_bf16: bad argument"); return B200FC_ERR_INVALID; }
+    return launch_add_round_bf16(a, b, out, n, (cudaStream_t)stream);
+}
+
+int b200fc_flush_l2(void* stream) {
+    static void* buf = nullptr;
+    static const size_t bytes = (size_t)256 << 20;  // twice the 126 MB L2
+    if (!buf) B200FC_CUDA(cudaMalloc(&buf, bytes));
+    return launch_fill(buf, bytes, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,148 @@
+// Shared declarations of the b200fc library: packed-weight object, kernel launch entry points, post-op math.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include "../../include/b200fc.h"
+
+namespace b200fc {
+
+// ---------------------------------------------------------------------------------------------------------------
+// Packed weights.  One layout serves every kernel: a row-major [N_pad, K_pad] matrix with K contiguous
+// ("K-major"), zero padded.  A 2-D TMA box of it with 128-byte swizzle lands in shared memory in the canonical
+// tcgen05 K-major operand layout; the decode kernels stream its rows with 16-byte loads.
+//   K_pad: multiple of 128 bytes of elements (64 bf16 / 128 int8)     N_pad: multiple of 256 rows
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kRowPad = 256;
+constexpr int kKPadBytes = 128;
+
+struct Weight {
+    int K = 0, N = 0;
+    int K_pad = 0, N_pad = 0;
+    int dtype = B200FC_BF16;        // stored element type: BF16, S8, U8
+    bool compressed = false;        // int8 weights used with bf16 activations
+    float deq_scale = 1.0f;         // per-tensor dequant scale of compressed weights
+    void* data = nullptr;           // [N_pad, K_pad]
+    float* scale_per_oc = nullptr;  // optional [N_pad] per-output-channel dequant scales
+    // lazily created scratch / staging owned by the object
+    void* dequant_bf16 = nullptr;   // [N_pad, K_pad64] bf16 copy of compressed weights for the tensor-core path
+    void* stage_A = nullptr; size_t stage_A_bytes = 0;
+    void* stage_C = nullptr; size_t stage_C_bytes = 0;
+    float* stage_vec = nullptr; size_t stage_vec_floats = 0;
+    int64_t ld_bytes() const { return (int64_t)K_pad * (dtype == B200FC_BF16 ? 2 : 1); }
+};
+
+// Post-op description handed to kernels (device pointers).
+struct Epilogue {
+    int steps;
+    int out_dtype;
+    void* C;
+    long long ldc;  // bytes
+    const float* bias;
+    float deq_scale;
+    const float* deq_per_oc;
+    float q_scale;
+    const float* q_per_oc;
+};
+
+// error plumbing (api.cu)
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+void count_launch(int n = 1);
+int* kernel_status_word();  // device int, 0 = OK; kernels store a non-zero code when a bounded wait runs out
+int check_kernel_status(cudaStream_t s);  // synchronises and reads it
+
+#define B200FC_CUDA(call)                                                   \
+    do {                                                                    \
+        cudaError_t e__ = (call);                                           \
+        if (e__ != cudaSuccess) return ::b200fc::cuda_fail(e__, #call);     \
+    } while (0)
+
+// ---- launchers -------------------------------------------------------------------------------------------------
+// pack.cu
+int launch_pack(const void* B_dev, int dtypeB, int K, int N, int64_t ldb, int transposeB, Weight& w, cudaStream_t s);
+int launch_pack_gate_up(const void* gate, const void* up, int64_t ld_bytes, int K, int rows, Weight& w, cudaStream_t s);
+int launch_quant_pack(const void* B_dev, int K, int N, int64_t ldb, int transposeB, Weight& w, float* absmax_dev,
+                      cudaStream_t s);
+int launch_absmax(const void* B_dev, int rows, int cols, int64_t ldb, float* absmax_dev, cudaStream_t s);
+int launch_dequant_bf16(const Weight& w, void* dst_bf16, int dst_K_pad, cudaStream_t s);
+int launch_copy2d(const void* src, int64_t lds, void* dst, int64_t ldd, int rows, int row_bytes, int dst_row_bytes,
+                  cudaStream_t s);
+int launch_add_round_bf16(const float* a, const float* b, void* out, int64_t n, cudaStream_t s);
+int launch_fill(void* p, size_t bytes, cudaStream_t s);
+// gemv.cu: M <= 16, bf16 activations, bf16 or int8 weights
+int launch_gemv(const Weight& w, const void* A, int M, int K, int64_t lda, int n0, int n1, const Epilogue& ep,
+                cudaStream_t s);
+// gemm_tc.cu: tcgen05 GEMM, bf16 x bf16 -> fp32 or 8-bit x 8-bit -> int32
+int launch_gemm_tc(const void* W_data, int w_dtype, int W_K_pad, int W_N_pad, const void* A, int dtypeA, int M, int K,
+                   int64_t lda, int n0, int n1, const Epilogue& ep, cudaStream_t s);
+// matvec.cu
+int launch_matvec(const void* A, int dtype, int M, int K, int64_t lda, const void* b, void* c, cudaStream_t s);
+
+// ---------------------------------------------------------------------------------------------------------------
+// Post-op math shared by all kernels (device).
+// ---------------------------------------------------------------------------------------------------------------
+#ifdef __CUDACC__
+
+// erf-GeLU through the minimax polynomial in x^2 that the reference evaluates (gelu_erf_minmax_approx,
+// include/kernels_amx.hpp:242-289): x < -5 -> 0, |x| > 5 -> x, |x| <= 2^-24 -> x/2, else x/2 * (1 + x * P(x^2)).
+__device__ __forceinline__ float gelu_erf_poly(float x) {
+    const float x2 = x * x, ax = fabsf(x), xh = 0.5f * x;
+    float p = __uint_as_float(0x1f1c83fdu);
+    p = fmaf(p, x2, __uint_as_float(0xa3198977u));
+    p = fmaf(p, x2, __uint_as_float(0x268a7927u));
+    p = fmaf(p, x2, __uint_as_float(0xa998c963u));
+    p = fmaf(p, x2, __uint_as_float(0x2c67ddb2u));
+    p = fmaf(p, x2, __uint_as_float(0xaf013b2cu));
+    p = fmaf(p, x2, __uint_as_float(0x315d4a4fu));
+    p = fmaf(p, x2, __uint_as_float(0xb3969b11u));
+    p = fmaf(p, x2, __uint_as_float(0x35a776e9u));
+    p = fmaf(p, x2, __uint_as_float(0xb79b0914u));
+    p = fmaf(p, x2, __uint_as_float(0x3970b255u));
+    p = fmaf(p, x2, __uint_as_float(0xbb1b7399u));
+    p = fmaf(p, x2, __uint_as_float(0x3ca3621fu));
+    p = fmaf(p, x2, __uint_as_float(0xbe082bc7u));
+    p = fmaf(p, x2, __uint_as_float(0x3f4c4228u));
+    p = fmaf(p, x, 1.0f) * xh;
+    if (x < -5.0f) x = 0.0f;
+    if (!(ax <= 5.0f)) p = x;
+    if (ax <= __uint_as_float(0x33800000u)) p = xh;
+    return p;
+}
+
+// SiLU of the fused MLP (silu_ps_avx512, tests/amx-mlp.cpp:445-451): x / (1 + exp(-x)).  The reference pairs a
+// degree-5 exp polynomial with a 14-bit reciprocal; here expf and a true division (differences <= ~2^-13 relative,
+// below the bf16 rounding that follows).
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+
+// fp32 -> int8 like VCVTPS2DQ + VPMOVSDB (include/kernels_amx.hpp:657-664): round to nearest even, saturate; NaN -> -128.
+__device__ __forceinline__ int f32_to_s8(float v) {
+    if (v != v) return -128;
+    int r;
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return r;
+}
+
+__device__ __forceinline__ unsigned short f32_to_bf16_bits(float v) {
+    return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+
+// DEQUANT -> BIAS -> GELU -> QUANT on one fp32 value of output column n.
+__device__ __forceinline__ float postop_scalar(float v, int n, const Epilogue& ep) {
+    if (ep.steps & B200FC_STEP_DEQUANT) v *= ep.deq_per_oc ? ep.deq_scale * __ldg(ep.deq_per_oc + n) : ep.deq_scale;
+    if (ep.steps & B200FC_STEP_BIAS) v += __ldg(ep.bias + n);
+    if (ep.steps & B200FC_STEP_GELU) v = gelu_erf_poly(v);
+    if (ep.steps & B200FC_STEP_QUANT) v *= ep.q_per_oc ? __ldg(ep.q_per_oc + n) : ep.q_scale;
+    return v;
+}
+
+__device__ __forceinline__ void store_scalar(float v, int m, int n, const Epilogue& ep) {
+    char* row = (char*)ep.C + (long long)m * ep.ldc;
+    if (ep.out_dtype == B200FC_F32) ((float*)row)[n] = v;
+    else if (ep.out_dtype == B200FC_BF16) ((unsigned short*)row)[n] = f32_to_bf16_bits(v);
+    else ((signed char*)row)[n] = (signed char)f32_to_s8(v);
+}
+
+#endif  // __CUDACC__
+
+}  // namespace b200fc

@@ -1,0 +1,526 @@
+// Prefill-shaped fully-connected layer on the 5th-generation tensor cores (tcgen05) of sm_100a.
+//
+// Replaces the M > 16 branches of amx_kernel::Matmul::operator() (kernel_2x2 over loop2D_opt_Mtail,
+// include/kernels_amx.hpp:1255-1313) and the JIT 32x32 micro-kernel of the fused MLP (tests/amx-mlp.cpp:199-334),
+// with PP::BiasGeluStore (kernels_amx.hpp:552-673) and the gate/up SiLU epilogue (tests/amx-mlp.cpp:716-734) fused
+// behind the accumulator.
+//
+// Shape of the kernel
+//   C tile 128 (M) x BN (N, 256 or 128); K advances in 128-byte slabs (64 bf16 / 128 int8).
+//   A [M, K] (row-major, K contiguous) and the packed weights [N_pad, K_pad] (K contiguous) are both K-major, so a
+//   2-D TMA box {128 bytes, rows} with 128-byte swizzle lands directly in the canonical tcgen05 operand layout.
+//   One CTA per SM, persistent over tiles (m fastest, so CTAs running together share the same weight slab in L2).
+//   Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer (one lane) and TMEM owner, warps 2-5 = epilogue.
+//   The fp32 / int32 accumulator lives in TMEM, double buffered (2 x BN columns), so the epilogue of tile i
+//   overlaps the main loop of tile i+1.
+//   Tails: M and K tails come from TMA out-of-bounds zero fill, the N tail from zero rows of the packed weights;
+//   stores are predicated.
+// Every mbarrier wait is bounded: when one runs out, the CTA raises an abort flag, all roles fall through to the
+// common exit (TMEM is freed there) and the kernel stores an error code for the host.
+#include <cuda.h>
+#include "common.cuh"
+
+namespace b200fc {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int SLAB_BYTES = 128;          // K extent of one pipeline stage, in bytes of operand elements
+constexpr int MMA_K_BYTES = 32;          // K extent of one tcgen05.mma (16 bf16 / 32 int8)
+constexpr int NUM_THREADS = 192;
+constexpr int EPI_WARP0 = 2;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+template <int BN> struct Cfg {
+    static constexpr int STAGES = BN == 256 ? 4 : 6;
+    static constexpr int A_BYTES = BM * SLAB_BYTES;
+    static constexpr int B_BYTES = BN * SLAB_BYTES;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int TMEM_COLS = 2 * BN;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+struct GemmParams {
+    int M, K, n0, n1;
+    int tiles_m, tiles_n, k_slabs;
+    unsigned idesc;
+    int acc_is_int;
+    int vec_ok;
+    Epilogue ep;
+    int* status;
+};
+
+// ---- PTX wrappers ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long globaltimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the CTA is aborting (this wait or another role's ran out of time).
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = globaltimer();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (globaltimer() - t0 > WAIT_LIMIT_NS) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, unsigned bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+template <bool I8>
+__device__ __forceinline__ void tc_mma(unsigned d_tmem, unsigned long long adesc, unsigned long long bdesc,
+                                       unsigned idesc, unsigned accumulate) {
+    if constexpr (I8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+__device__ __forceinline__ void tc_ld32(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory operand descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes
+// apart (stride-dimension byte offset); descriptor version 1 (Blackwell).
+__device__ __forceinline__ unsigned long long make_smem_desc(unsigned smem_addr) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (unsigned long long)1 << 16;            // leading-dimension byte offset (unused for swizzled K-major)
+    d |= (unsigned long long)(1024 >> 4) << 32;  // stride-dimension byte offset
+    d |= (unsigned long long)1 << 46;            // descriptor version
+    d |= (unsigned long long)2 << 61;            // SWIZZLE_128B
+    return d;
+}
+
+// ---- epilogue on 32 consecutive columns of one output row ------------------------------------------------------------
+__device__ __forceinline__ void epilogue_chunk(const unsigned (&r)[32], int m, int n, const GemmParams& p, bool row_ok) {
+    const Epilogue& ep = p.ep;
+    if (!row_ok) return;
+    char* crow = (char*)ep.C + (long long)m * ep.ldc;
+    if (ep.out_dtype == B200FC_S32) {  // raw accumulators
+        if (p.vec_ok && n + 32 <= p.n1) {
+            int4* dst = (int4*)(crow + (long long)n * 4);
+#pragma unroll
+            for (int j = 0; j < 8; j++) dst[j] = make_int4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        } else {
+            for (int j = 0; j < 32; j++)
+                if (n + j < p.n1) ((int*)crow)[n + j] = (int)r[j];
+        }
+        return;
+    }
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; j++) v[j] = p.acc_is_int ? (float)(int)r[j] : __uint_as_float(r[j]);
+
+    if (ep.steps & B200FC_STEP_SILU_MUL) {
+        // columns [0,16) gate, [16,32) up of the same 16 channels -> 16 bf16 outputs at column n/2
+        __align__(16) unsigned short o[16];
+#pragma unroll
+        for (int j = 0; j < 16; j++) o[j] = f32_to_bf16_bits(silu_f(v[j]) * v[16 + j]);
+        int nc = n >> 1;
+        unsigned short* dst = (unsigned short*)crow + nc;
+        if (p.vec_ok && n + 32 <= p.n1) {
+            ((int4*)dst)[0] = *(int4*)&o[0];
+            ((int4*)dst)[1] = *(int4*)&o[8];
+        } else {
+            for (int j = 0; j < 16; j++)
+                if (n + 16 + j < p.n1) dst[j] = o[j];
+        }
+        return;
+    }
+
+    if (ep.steps & B200FC_STEP_DEQUANT) {
+        if (ep.deq_per_oc) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] *= ep.deq_scale * __ldg(ep.deq_per_oc + min(n + j, p.n1 - 1));
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] *= ep.deq_scale;
+        }
+    }
+    if (ep.steps & B200FC_STEP_BIAS) {
+#pragma unroll
+        for (int j = 0; j < 32; j++) v[j] += __ldg(ep.bias + min(n + j, p.n1 - 1));
+    }
+    if (ep.steps & B200FC_STEP_GELU) {
+#pragma unroll
+        for (int j = 0; j < 32; j++) v[j] = gelu_erf_poly(v[j]);
+    }
+    if (ep.steps & B200FC_STEP_QUANT) {
+        if (ep.q_per_oc) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] *= __ldg(ep.q_per_oc + min(n + j, p.n1 - 1));
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] *= ep.q_scale;
+        }
+    }
+    const bool full = p.vec_ok && n + 32 <= p.n1;
+    if (ep.out_dtype == B200FC_F32) {
+        if (full) {
+            float4* dst = (float4*)(crow + (long long)n * 4);
+#pragma unroll
+            for (int j = 0; j < 8; j++) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        } else {
+            for (int j = 0; j < 32; j++)
+                if (n + j < p.n1) ((float*)crow)[n + j] = v[j];
+        }
+    } else if (ep.out_dtype == B200FC_BF16) {
+        if (full) {
+            __align__(16) unsigned o[16];
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                o[j] = *(unsigned*)&h;
+            }
+            int4* dst = (int4*)(crow + (long long)n * 2);
+#pragma unroll
+            for (int j = 0; j < 4; j++) dst[j] = *(int4*)&o[4 * j];
+        } else {
+            for (int j = 0; j < 32; j++)
+                if (n + j < p.n1) ((unsigned short*)crow)[n + j] = f32_to_bf16_bits(v[j]);
+        }
+    } else {  // int8
+        if (full) {
+            __align__(16) unsigned o[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                unsigned b0 = f32_to_s8(v[4 * j]) & 0xff, b1 = f32_to_s8(v[4 * j + 1]) & 0xff;
+                unsigned b2 = f32_to_s8(v[4 * j + 2]) & 0xff, b3 = f32_to_s8(v[4 * j + 3]) & 0xff;
+                o[j] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+            }
+            int4* dst = (int4*)(crow + n);
+            dst[0] = *(int4*)&o[0];
+            dst[1] = *(int4*)&o[4];
+        } else {
+            for (int j = 0; j < 32; j++)
+                if (n + j < p.n1) ((signed char*)crow)[n + j] = (signed char)f32_to_s8(v[j]);
+        }
+    }
+}
+
+// ---- the kernel --------------------------------------------------------------------------------------------------------
+template <int BN, bool I8>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+               const GemmParams p) {
+    using C = Cfg<BN>;
+    extern __shared__ unsigned char smem_raw[];
+    // operand stages need 1024-byte alignment (128-byte swizzle atom = 8 rows x 128 bytes)
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned long long* bars = (unsigned long long*)(smem + C::STAGES * C::STAGE_BYTES);
+    // barrier slots: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+    const unsigned bar_full = smem_u32(bars);
+    const unsigned bar_empty = smem_u32(bars + C::STAGES);
+    const unsigned bar_acc_full = smem_u32(bars + 2 * C::STAGES);
+    const unsigned bar_acc_empty = smem_u32(bars + 2 * C::STAGES + 2);
+    unsigned* tmem_holder = (unsigned*)(bars + 2 * C::STAGES + 4);
+    volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_tiles = p.tiles_m * p.tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < C::STAGES; i++) {
+            mbar_init(bar_full + 8 * i, 1);
+            mbar_init(bar_empty + 8 * i, 1);
+        }
+        for (int i = 0; i < 2; i++) {
+            mbar_init(bar_acc_full + 8 * i, 1);
+            mbar_init(bar_acc_empty + 8 * i, 4);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
+                     "r"((unsigned)C::TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            unsigned phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+                const int row_a = tm * BM, row_w = p.n0 + tn * BN;
+                for (int ks = 0; ks < p.k_slabs; ks++) {
+                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag)) { ok = false; break; }
+                    const unsigned full = bar_full + 8 * stage;
+                    mbar_expect_tx(full, C::STAGE_BYTES);
+                    const unsigned sa = smem_u32(smem + stage * C::STAGE_BYTES);
+                    const int kx = ks * (I8 ? SLAB_BYTES : SLAB_BYTES / 2);  // element coordinate along K
+                    tma_load_2d(sa, &map_a, full, kx, row_a);
+                    tma_load_2d(sa + C::A_BYTES, &map_w, full, kx, row_w);
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        int stage = 0;
+        unsigned phase = 0;
+        int it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, it++) {
+            const int ab = it & 1;
+            const unsigned acc_phase = (unsigned)(it >> 1) & 1;
+            if (!mbar_wait(bar_acc_empty + 8 * ab, acc_phase ^ 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const unsigned d_tmem = tmem_base + (unsigned)(ab * BN);
+            for (int ks = 0; ks < p.k_slabs; ks++) {
+                if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                if (lane == 0) {
+                    const unsigned sa = smem_u32(smem + stage * C::STAGE_BYTES);
+                    const unsigned long long adesc = make_smem_desc(sa);
+                    const unsigned long long bdesc = make_smem_desc(sa + C::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < SLAB_BYTES / MMA_K_BYTES; k++) {
+                        // advancing K inside the swizzle atom = advancing the start address (units of 16 bytes)
+                        tc_mma<I8>(d_tmem, adesc + (unsigned long long)(k * (MMA_K_BYTES >> 4)),
+                                   bdesc + (unsigned long long)(k * (MMA_K_BYTES >> 4)), p.idesc,
+                                   (unsigned)((ks | k) != 0));
+                    }
+                    tc_commit(bar_empty + 8 * stage);  // frees the stage once these MMAs have read it
+                    if (ks == p.k_slabs - 1) tc_commit(bar_acc_full + 8 * ab);
+                }
+                __syncwarp();
+                if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else {
+        // ---------------- epilogue warps ----------------
+        const int quarter = warp & 3;  // TMEM lanes this warp may read: [32*quarter, 32*quarter + 32)
+        int it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, it++) {
+            const int ab = it & 1;
+            const unsigned acc_phase = (unsigned)(it >> 1) & 1;
+            const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+            if (!mbar_wait(bar_acc_full + 8 * ab, acc_phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const int m = tm * BM + quarter * 32 + lane;
+            const bool row_ok = m < p.M;
+            const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(ab * BN);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c++) {
+                const int n = p.n0 + tn * BN + c * 32;
+                if (n >= p.n1) break;  // warp-uniform
+                unsigned r[32];
+                tc_ld32(taddr + (unsigned)(c * 32), r);
+                tc_wait_ld();
+                epilogue_chunk(r, m, n, p, row_ok);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acc_empty + 8 * ab);
+        }
+    }
+
+    // ---------------- common exit ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // give copies that may still be in flight time to land before shared memory is released
+        if (threadIdx.x == 0) {
+            atomicExch(p.status, 1);
+            const unsigned long long t0 = globaltimer();
+            while (globaltimer() - t0 < 200000ull) { }
+        }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)C::TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// ---- host side -----------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)sym;
+    }
+    return fn;
+}
+
+// 2-D K-major tensor map: inner dimension = K elements, outer = rows; box = {128 bytes of K, box_rows}.
+int make_map(CUtensorMap* map, const void* base, bool i8, uint64_t k_elems, uint64_t rows, uint64_t ld_bytes,
+             uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) { set_error("cuTensorMapEncodeTiled entry point not available"); return B200FC_ERR_CUDA; }
+    cuuint64_t dims[2] = {k_elems, rows};
+    cuuint64_t strides[1] = {ld_bytes};
+    cuuint32_t box[2] = {(cuuint32_t)(i8 ? SLAB_BYTES : SLAB_BYTES / 2), box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, i8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims,
+                    strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed (%d)", (int)r); return B200FC_ERR_CUDA; }
+    return B200FC_OK;
+}
+
+// tcgen05 instruction descriptor (dense, K-major A and B, M = 128): accumulator format bits [4,6), A format [7,10),
+// B format [10,13), N >> 3 at [17,23), M >> 4 at [24,29).
+unsigned make_idesc(bool i8, bool a_signed, bool b_signed, int bn) {
+    unsigned d = 0;
+    if (i8) {
+        d |= 2u << 4;                       // int32 accumulator
+        d |= (a_signed ? 1u : 0u) << 7;     // 8-bit integer: 1 = signed, 0 = unsigned
+        d |= (b_signed ? 1u : 0u) << 10;
+    } else {
+        d |= 1u << 4;                       // fp32 accumulator
+        d |= 1u << 7;                       // bf16
+        d |= 1u << 10;
+    }
+    d |= (unsigned)(bn >> 3) << 17;
+    d |= (unsigned)(BM >> 4) << 24;
+    return d;
+}
+
+int num_sms() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
+template <int BN, bool I8>
+int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& p, cudaStream_t s) {
+    using C = Cfg<BN>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        B200FC_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, I8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         C::SMEM_BYTES));
+        attr_done = true;
+    }
+    int tiles = p.tiles_m * p.tiles_n;
+    int grid = tiles < num_sms() ? tiles : num_sms();
+    gemm_tc_kernel<BN, I8><<<grid, NUM_THREADS, C::SMEM_BYTES, s>>>(ma, mw, p);
+    count_launch();
+    B200FC_CUDA(cudaGetLastError());
+    return B200FC_OK;
+}
+
+}  // namespace
+
+int launch_gemm_tc(const void* W_data, int w_dtype, int W_K_pad, int W_N_pad, const void* A, int dtypeA, int M, int K,
+                   int64_t lda, int n0, int n1, const Epilogue& ep, cudaStream_t s) {
+    const bool i8 = dtypeA != B200FC_BF16;
+    if (i8 != (w_dtype != B200FC_BF16)) { set_error("gemm_tc: activation / weight dtype mismatch"); return B200FC_ERR_INVALID; }
+    if (((uintptr_t)A & 15) || (lda & 15)) {
+        set_error("gemm_tc: A must be 16-byte aligned with a 16-byte multiple leading dimension");
+        return B200FC_ERR_INVALID;
+    }
+    if (M <= 0 || n1 <= n0) return B200FC_OK;
+    const int nspan = n1 - n0;
+    // 256-wide tiles unless that leaves SMs idle while 128-wide tiles would not
+    const int tiles_m = (M + BM - 1) / BM;
+    int bn = 256;
+    {
+        int t256 = tiles_m * ((nspan + 255) / 256), t128 = tiles_m * ((nspan + 127) / 128);
+        int sms = num_sms();
+        auto waves_eff = [&](int t) { return (double)t / (double)(((t + sms - 1) / sms) * sms); };
+        if (nspan <= 128 || (t256 < sms && t128 > t256) || waves_eff(t128) > waves_eff(t256) + 0.08) bn = 128;
+    }
+    GemmParams p;
+    p.M = M; p.K = K; p.n0 = n0; p.n1 = n1;
+    p.tiles_m = tiles_m;
+    p.tiles_n = (nspan + bn - 1) / bn;
+    const int slab_elems = i8 ? SLAB_BYTES : SLAB_BYTES / 2;
+    p.k_slabs = (K + slab_elems - 1) / slab_elems;
+    p.idesc = make_idesc(i8, dtypeA == B200FC_S8, w_dtype == B200FC_S8, bn);
+    p.acc_is_int = i8 ? 1 : 0;
+    p.ep = ep;
+    p.status = kernel_status_word();
+    int es = ep.out_dtype == B200FC_F32 || ep.out_dtype == B200FC_S32 ? 4 : (ep.out_dtype == B200FC_BF16 ? 2 : 1);
+    if (ep.steps & B200FC_STEP_SILU_MUL)
+        p.vec_ok = (((uintptr_t)ep.C & 15) == 0 && (ep.ldc & 15) == 0 && (n0 % 32) == 0) ? 1 : 0;
+    else
+        p.vec_ok = (((uintptr_t)ep.C & 15) == 0 && (ep.ldc & 15) == 0 && ((n0 * es) & 15) == 0) ? 1 : 0;
+    if (ep.out_dtype == B200FC_S32 && !i8) { set_error("raw int32 output needs an 8-bit GEMM"); return B200FC_ERR_INVALID; }
+
+    CUtensorMap ma, mw;
+    int rc = make_map(&ma, A, i8, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BM);
+    if (rc) return rc;
+    rc = make_map(&mw, W_data, i8, (uint64_t)W_K_pad, (uint64_t)W_N_pad, (uint64_t)W_K_pad * (i8 ? 1 : 2), (uint32_t)bn);
+    if (rc) return rc;
+    if (bn == 256) return i8 ? launch_cfg<256, true>(ma, mw, p, s) : launch_cfg<256, false>(ma, mw, p, s);
+    return i8 ? launch_cfg<128, true>(ma, mw, p, s) : launch_cfg<128, false>(ma, mw, p, s);
+}
+
+}  // namespace b200fc

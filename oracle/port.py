@@ -1,0 +1,140 @@
+"""TEST INFRASTRUCTURE: ctypes wrapper around oracle/liboracle.so (the plain C++ oracle port)."""
+import ctypes
+import os
+import subprocess
+import numpy as np
+from ._common import ptr, c_contig, c_int, c_int64, c_float, c_void_p
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+DEQUANT, BIAS, GELU, QUANT = 1, 2, 4, 8
+F32, BF16, S8 = 0, 1, 2
+_NP = {F32: np.float32, BF16: np.uint16, S8: np.int8}
+
+
+def build():
+    subprocess.check_call(["make", "-s", "-C", _HERE, "liboracle.so"])
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        path = os.path.join(_HERE, "liboracle.so")
+        if not os.path.exists(path):
+            build()
+        _LIB = ctypes.CDLL(path)
+        _LIB.orc_threads.restype = c_int
+    return _LIB
+
+
+def threads():
+    return lib().orc_threads()
+
+
+def gelu(x):
+    x = c_contig(x, np.float32); y = np.empty_like(x)
+    lib().orc_gelu(ptr(x), ptr(y), c_int64(x.size)); return y
+
+
+def silu(x):
+    x = c_contig(x, np.float32); y = np.empty_like(x)
+    lib().orc_silu(ptr(x), ptr(y), c_int64(x.size)); return y
+
+
+def f32_to_bf16(x):
+    x = c_contig(x, np.float32); y = np.empty(x.shape, np.uint16)
+    lib().orc_f32_to_bf16(ptr(x), ptr(y), c_int64(x.size)); return y
+
+
+def gemm_bf16(A, B, transposeB=False):
+    """A [M,K], B [K,N] (or [N,K] with transposeB) as bf16 bits -> fp32 accumulators [M,N]."""
+    A = c_contig(A, np.uint16); B = c_contig(B, np.uint16)
+    M, K = A.shape
+    N = B.shape[0] if transposeB else B.shape[1]
+    assert (B.shape[1] if transposeB else B.shape[0]) == K
+    acc = np.empty((M, N), np.float32)
+    lib().orc_gemm_bf16(ptr(A), c_int64(A.strides[0]), ptr(B), c_int64(B.strides[0]), c_int(int(transposeB)),
+                        c_int(M), c_int(K), c_int(N), ptr(acc), c_int64(N))
+    return acc
+
+
+def gemm_i8(A, B, transposeB=False):
+    """int8/uint8 A [M,K] x int8/uint8 B -> exact int32 accumulators."""
+    A = np.ascontiguousarray(A); B = np.ascontiguousarray(B)
+    assert A.dtype in (np.int8, np.uint8) and B.dtype in (np.int8, np.uint8)
+    M, K = A.shape
+    N = B.shape[0] if transposeB else B.shape[1]
+    acc = np.empty((M, N), np.int32)
+    lib().orc_gemm_i8(ptr(A), c_int64(A.strides[0]), c_int(int(A.dtype == np.uint8)), ptr(B), c_int64(B.strides[0]),
+                      c_int(int(B.dtype == np.uint8)), c_int(int(transposeB)), c_int(M), c_int(K), c_int(N),
+                      ptr(acc), c_int64(N))
+    return acc
+
+
+def gemm_bf16_w8(A, Wq, transposeB=False):
+    A = c_contig(A, np.uint16); Wq = c_contig(Wq, np.int8)
+    M, K = A.shape
+    N = Wq.shape[0] if transposeB else Wq.shape[1]
+    acc = np.empty((M, N), np.float32)
+    lib().orc_gemm_bf16_w8(ptr(A), c_int64(A.strides[0]), ptr(Wq), c_int64(Wq.strides[0]), c_int(int(transposeB)),
+                           c_int(M), c_int(K), c_int(N), ptr(acc), c_int64(N))
+    return acc
+
+
+def postops(acc, steps, out_dtype, bias=None, deq_scale=1.0, deq_scale_per_oc=None, q_scale=1.0,
+            q_scale_per_oc=None):
+    acc = np.ascontiguousarray(acc)
+    assert acc.dtype in (np.float32, np.int32)
+    M, N = acc.shape
+    f = lambda a: None if a is None else c_contig(a, np.float32)
+    bias, deq_scale_per_oc, q_scale_per_oc = f(bias), f(deq_scale_per_oc), f(q_scale_per_oc)
+    C = np.empty((M, N), _NP[out_dtype])
+    lib().orc_postops(ptr(acc), c_int(int(acc.dtype == np.int32)), c_int64(N), c_int(M), c_int(N), c_int(steps),
+                      c_float(deq_scale), ptr(deq_scale_per_oc), ptr(bias), c_float(q_scale), ptr(q_scale_per_oc),
+                      c_int(out_dtype), ptr(C), c_int64(C.strides[0]))
+    return C
+
+
+def quantize_weight(W):
+    """bf16 bits [rows, cols] -> (int8 [rows, cols], quant_scale, dequant_scale), per-tensor absmax."""
+    W = c_contig(W, np.uint16)
+    Wq = np.empty(W.shape, np.int8)
+    q, d = c_float(), c_float()
+    lib().orc_quantize_weight(ptr(W), c_int64(W.strides[0]), c_int(W.shape[0]), c_int(W.shape[1]), ptr(Wq),
+                              ctypes.byref(q), ctypes.byref(d))
+    return Wq, q.value, d.value
+
+
+def matvec_bf16(A, b):
+    A = c_contig(A, np.uint16); b = c_contig(b, np.uint16)
+    c = np.empty(A.shape[0], np.float32)
+    lib().orc_matvec_bf16(ptr(A), c_int64(A.strides[0]), c_int(A.shape[0]), c_int(A.shape[1]), ptr(b), ptr(c))
+    return c
+
+
+def matvec_s8(A, b):
+    A = c_contig(A, np.int8); b = c_contig(b, np.int8)
+    c = np.empty(A.shape[0], np.int32)
+    lib().orc_matvec_s8(ptr(A), c_int64(A.strides[0]), c_int(A.shape[0]), c_int(A.shape[1]), ptr(b), ptr(c))
+    return c
+
+
+def mlp(x, gate, up, down, want_act=False, want_partial=False):
+    """x [M,K], gate/up [N,K], down [K,N] (bf16 bits) -> out [M,K] bf16 bits (+ act [M,N], + fp32 partial)."""
+    x = c_contig(x, np.uint16); gate = c_contig(gate, np.uint16); up = c_contig(up, np.uint16)
+    down = c_contig(down, np.uint16)
+    M, K = x.shape
+    N = gate.shape[0]
+    assert gate.shape == (N, K) and up.shape == (N, K) and down.shape == (K, N)
+    out = np.empty((M, K), np.uint16)
+    act = np.empty((M, N), np.uint16) if want_act else None
+    part = np.empty((M, K), np.float32) if want_partial else None
+    lib().orc_mlp(ptr(x), c_int64(x.strides[0]), c_int(M), ptr(gate), ptr(up), ptr(down), c_int(K), c_int(N),
+                  ptr(out), c_int64(out.strides[0]), ptr(act), ptr(part))
+    res = (out,)
+    if want_act:
+        res += (act,)
+    if want_partial:
+        res += (part,)
+    return res[0] if len(res) == 1 else res

