@@ -126,11 +126,21 @@ int b200fc_mlp_run(b200fc_mlp_t* mlp, const void* x, int64_t ldx_bytes, int M, v
  * ranks (one all-reduce) and, for fp32, rounds to bf16 (the reference rounds after the fp32 sum, :672-680) */
 int b200fc_mlp_run_partial(b200fc_mlp_t* mlp, const void* x, int64_t ldx_bytes, int M, void* partial, int out_dtype,
                            int64_t ldp_bytes, void* stream);
+/* The two stages on their own, as the reference exposes them (Linear::runGateUp, tests/amx-mlp.cpp:707-737, and
+ * Linear::run, :648-704): gate_up writes the internal [M, N/tp] bf16 activation, down consumes it. */
+int b200fc_mlp_gate_up(b200fc_mlp_t* mlp, const void* x, int64_t ldx_bytes, int M, void* stream);
+int b200fc_mlp_down(b200fc_mlp_t* mlp, int M, void* out, int out_dtype, int64_t ldo_bytes, void* stream);
 /* x and out in HOST memory; copies, runs, copies back, synchronises. */
 int b200fc_mlp_run_host(b200fc_mlp_t* mlp, const void* x, int64_t ldx_bytes, int M, void* out, int64_t ldo_bytes,
                         void* stream);
 /* device pointer to the [M, N/tp] bf16 activation of the last run (debug / layer-wise parity) */
 const void* b200fc_mlp_act(const b200fc_mlp_t* mlp);
+
+/* ---- device memory for callers that do not link the CUDA runtime themselves ------------------------------------ */
+int b200fc_device_malloc(void** ptr, int64_t bytes);
+int b200fc_device_free(void* ptr);
+/* copy between any two of host / device memory (direction inferred), ordered on `stream`, then waits for it */
+int b200fc_memcpy(void* dst, const void* src, int64_t bytes, void* stream);
 
 /* ---- helpers -------------------------------------------------------------------------------------------------- */
 /* bf16 round-to-nearest-even of fp32 on the device: out[i] = bf16(a[i] + (b ? b[i] : 0)) */

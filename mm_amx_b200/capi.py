@@ -44,8 +44,13 @@ SIGNATURES = {
     "b200fc_mlp_reserve": (c_int, [c_void_p, c_int]),
     "b200fc_mlp_run": (c_int, [c_void_p, c_void_p, c_i64, c_int, c_void_p, c_i64, c_void_p]),
     "b200fc_mlp_run_partial": (c_int, [c_void_p, c_void_p, c_i64, c_int, c_void_p, c_int, c_i64, c_void_p]),
+    "b200fc_mlp_gate_up": (c_int, [c_void_p, c_void_p, c_i64, c_int, c_void_p]),
+    "b200fc_mlp_down": (c_int, [c_void_p, c_int, c_void_p, c_int, c_i64, c_void_p]),
     "b200fc_mlp_run_host": (c_int, [c_void_p, c_void_p, c_i64, c_int, c_void_p, c_i64, c_void_p]),
     "b200fc_mlp_act": (c_void_p, [c_void_p]),
+    "b200fc_device_malloc": (c_int, [ctypes.POINTER(c_void_p), c_i64]),
+    "b200fc_device_free": (c_int, [c_void_p]),
+    "b200fc_memcpy": (c_int, [c_void_p, c_void_p, c_i64, c_void_p]),
     "b200fc_add_round_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_i64, c_void_p]),
     "b200fc_flush_l2": (c_int, [c_void_p]),
 }
@@ -151,6 +156,12 @@ class Mlp:
     def run_partial(self, x_ptr, ldx_bytes, M, out_ptr, out_dtype, ldo_bytes, stream=None):
         check(lib().b200fc_mlp_run_partial(self.h, x_ptr, ldx_bytes, M, out_ptr, out_dtype, ldo_bytes, stream))
 
+    def gate_up(self, x_ptr, ldx_bytes, M, stream=None):
+        check(lib().b200fc_mlp_gate_up(self.h, x_ptr, ldx_bytes, M, stream))
+
+    def down(self, M, out_ptr, out_dtype, ldo_bytes, stream=None):
+        check(lib().b200fc_mlp_down(self.h, M, out_ptr, out_dtype, ldo_bytes, stream))
+
     def run_host(self, x_ptr, ldx_bytes, M, out_ptr, ldo_bytes, stream=None):
         check(lib().b200fc_mlp_run_host(self.h, x_ptr, ldx_bytes, M, out_ptr, ldo_bytes, stream))
 
@@ -175,6 +186,10 @@ def matvec(A_ptr, dtype, M, K, lda_bytes, b_ptr, c_ptr, stream=None):
 
 def matvec_host(A_ptr, dtype, M, K, lda_bytes, b_ptr, c_ptr, stream=None):
     check(lib().b200fc_matvec_host(A_ptr, dtype, M, K, lda_bytes, b_ptr, c_ptr, stream))
+
+
+def memcpy(dst_ptr, src_ptr, nbytes, stream=None):
+    check(lib().b200fc_memcpy(dst_ptr, src_ptr, nbytes, stream))
 
 
 def add_round_bf16(a_ptr, b_ptr, out_ptr, n, stream=None):

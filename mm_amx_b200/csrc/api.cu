@@ -210,22 +210,34 @@ struct Mlp {
     int tp_rank = 0, tp_size = 1;
     Weight gate_up, down;
     void* act = nullptr; size_t act_bytes = 0;      // [M, Ns] bf16
+    int act_rows = 0;                               // rows of the last gate_up
     void* stage_x = nullptr; size_t stage_x_bytes = 0;
     void* stage_o = nullptr; size_t stage_o_bytes = 0;
 };
 
-static int mlp_run_device(Mlp& m, const void* x, int64_t ldx, int M, void* out, int out_dtype, int64_t ldo, cudaStream_t s) {
+static int mlp_gate_up_device(Mlp& m, const void* x, int64_t ldx, int M, cudaStream_t s) {
     if (M < 0) { set_error("mlp: M < 0"); return B200FC_ERR_INVALID; }
     if (M == 0) return B200FC_OK;
     int rc = grow(&m.act, &m.act_bytes, (size_t)M * m.Ns * 2, s);
     if (rc) return rc;
+    m.act_rows = M;
     b200fc_epilogue_t e1 = {};
     e1.steps = B200FC_STEP_SILU_MUL; e1.out_dtype = B200FC_BF16; e1.C = m.act; e1.ldc_bytes = (int64_t)m.Ns * 2;
-    rc = matmul_device(m.gate_up, nullptr, x, B200FC_BF16, M, m.K, ldx, 0, 2 * m.Ns, &e1, s);
-    if (rc) return rc;
+    return matmul_device(m.gate_up, nullptr, x, B200FC_BF16, M, m.K, ldx, 0, 2 * m.Ns, &e1, s);
+}
+
+static int mlp_down_device(Mlp& m, int M, void* out, int out_dtype, int64_t ldo, cudaStream_t s) {
+    if (M < 0 || M > m.act_rows) { set_error("mlp_down: no activation of %d rows (gate_up ran %d)", M, m.act_rows); return B200FC_ERR_INVALID; }
+    if (M == 0) return B200FC_OK;
     b200fc_epilogue_t e2 = {};
     e2.steps = 0; e2.out_dtype = out_dtype; e2.C = out; e2.ldc_bytes = ldo;
     return matmul_device(m.down, nullptr, m.act, B200FC_BF16, M, m.Ns, (int64_t)m.Ns * 2, 0, m.K, &e2, s);
+}
+
+static int mlp_run_device(Mlp& m, const void* x, int64_t ldx, int M, void* out, int out_dtype, int64_t ldo, cudaStream_t s) {
+    int rc = mlp_gate_up_device(m, x, ldx, M, s);
+    if (rc) return rc;
+    return mlp_down_device(m, M, out, out_dtype, ldo, s);
 }
 
 }  // namespace b200fc
@@ -450,6 +462,17 @@ int b200fc_mlp_run_partial(b200fc_mlp_t* h, const void* x, int64_t ldx, int M, v
     return mlp_run_device(h->m, x, ldx, M, partial, out_dtype, ldp, (cudaStream_t)stream);
 }
 
+int b200fc_mlp_gate_up(b200fc_mlp_t* h, const void* x, int64_t ldx, int M, void* stream) {
+    if (!h || !x) { set_error("mlp_gate_up: null pointer"); return B200FC_ERR_INVALID; }
+    return mlp_gate_up_device(h->m, x, ldx, M, (cudaStream_t)stream);
+}
+
+int b200fc_mlp_down(b200fc_mlp_t* h, int M, void* out, int out_dtype, int64_t ldo, void* stream) {
+    if (!h || !out) { set_error("mlp_down: null pointer"); return B200FC_ERR_INVALID; }
+    if (out_dtype != B200FC_F32 && out_dtype != B200FC_BF16) { set_error("mlp_down: out_dtype must be f32 or bf16"); return B200FC_ERR_INVALID; }
+    return mlp_down_device(h->m, M, out, out_dtype, ldo, (cudaStream_t)stream);
+}
+
 int b200fc_mlp_run_host(b200fc_mlp_t* h, const void* x, int64_t ldx, int M, void* out, int64_t ldo, void* stream) {
     cudaStream_t s = (cudaStream_t)stream;
     if (!h || !x || !out || M <= 0) { set_error("mlp_run_host: null pointer or M <= 0"); return B200FC_ERR_INVALID; }
@@ -467,6 +490,22 @@ int b200fc_mlp_run_host(b200fc_mlp_t* h, const void* x, int64_t ldx, int M, void
 }
 
 const void* b200fc_mlp_act(const b200fc_mlp_t* h) { return h ? h->m.act : nullptr; }
+
+int b200fc_device_malloc(void** ptr, int64_t bytes) {
+    if (!ptr || bytes < 0) { set_error("device_malloc: bad argument"); return B200FC_ERR_INVALID; }
+    B200FC_CUDA(cudaMalloc(ptr, (size_t)(bytes > 0 ? bytes : 1)));
+    return B200FC_OK;
+}
+int b200fc_device_free(void* ptr) {
+    B200FC_CUDA(cudaFree(ptr));
+    return B200FC_OK;
+}
+int b200fc_memcpy(void* dst, const void* src, int64_t bytes, void* stream) {
+    if (bytes < 0 || (bytes > 0 && (!dst || !src))) { set_error("memcpy: bad argument"); return B200FC_ERR_INVALID; }
+    B200FC_CUDA(cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDefault, (cudaStream_t)stream));
+    B200FC_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    return B200FC_OK;
+}
 
 int b200fc_add_round_bf16(const float* a, const float* b, void* out, int64_t n, void* stream) {
     if (!a || !out || n < 0) { set_error("add_round_bf16: bad argument"); return B200FC_ERR_INVALID; }

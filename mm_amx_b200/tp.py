@@ -1,0 +1,101 @@
+"""Megatron-style tensor-parallel Llama MLP: one process per GPU, one all-reduce on the down-projection output.
+
+The reference shards the same way across CPU cores: gate/up by output channels (Linear::setup, tests/amx-mlp.cpp:554-593)
+and the down projection by K with an fp32 add of the partial results before the bf16 rounding (:559-589, :656-683).
+Here rank r keeps rows [r*N/t, (r+1)*N/t) of gate and up and the same columns of down; every rank computes its
+contribution to out[M, K]; one torch.distributed all-reduce (NCCL over NVLink on GPUs) sums them.
+
+  partial dtype "f32": contributions are summed in fp32 and rounded to bf16 once, like the reference's split-K.
+  partial dtype "bf16": contributions are rounded to bf16 first (half the bytes on the wire); the sum of t bf16
+                        values stays within the 1e-2 bound of the bf16 paths.
+
+The local computation is the CUDA library (capi.Mlp).  `local` can be replaced by another object with the same
+run_partial() signature; the CPU tests use that to check the sharding and reduction logic under gloo.
+"""
+import torch
+import torch.distributed as dist
+
+from . import capi
+
+
+def shard_rows(n_total, rank, world):
+    """Row range of gate/up (= column range of down) owned by `rank`; N must divide evenly, in 32-row units."""
+    if n_total % world:
+        raise ValueError("intermediate size %d is not divisible by tensor-parallel size %d" % (n_total, world))
+    ns = n_total // world
+    if ns % 32:
+        raise ValueError("per-rank intermediate size %d must be a multiple of 32" % ns)
+    return rank * ns, (rank + 1) * ns
+
+
+class CudaLocalMLP:
+    """This rank's shard on its GPU.  gate/up: [N, K], down: [K, N] bf16 torch tensors (CPU or CUDA), FULL matrices."""
+
+    def __init__(self, gate, up, down, rank, world):
+        N, K = gate.shape
+        assert up.shape == (N, K) and down.shape == (K, N)
+        for t in (gate, up, down):
+            assert t.dtype == torch.bfloat16 and t.is_contiguous()
+        shard_rows(N, rank, world)
+        self.K, self.N, self.world = K, N, world
+        self.mlp = capi.Mlp(gate.data_ptr(), up.data_ptr(), down.data_ptr(), K, N, rank, world,
+                            torch.cuda.current_stream().cuda_stream)
+
+    def run_partial(self, x, out):
+        """x [M, K] bf16 CUDA; out [M, K] fp32 or bf16 CUDA: this rank's contribution."""
+        dt = capi.F32 if out.dtype == torch.float32 else capi.BF16
+        self.mlp.run_partial(x.data_ptr(), x.stride(0) * 2, x.shape[0], out.data_ptr(), dt,
+                             out.stride(0) * out.element_size(), torch.cuda.current_stream().cuda_stream)
+
+
+class TensorParallelMLP:
+    def __init__(self, local, K, group=None, partial_dtype=torch.float32, chunk_rows=0):
+        """local: object with run_partial(x, out); chunk_rows > 0 splits M so that the all-reduce of one chunk overlaps
+        the computation of the next (CUDA only)."""
+        self.local, self.K, self.group = local, K, group
+        self.partial_dtype = partial_dtype
+        self.chunk_rows = chunk_rows
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self._comm_stream = None
+
+    def _round(self, partial, out):
+        if partial.dtype == torch.bfloat16:
+            if out.data_ptr() != partial.data_ptr():
+                out.copy_(partial)
+        elif partial.is_cuda:
+            capi.add_round_bf16(partial.data_ptr(), None, out.data_ptr(), partial.numel(),
+                                torch.cuda.current_stream().cuda_stream)
+        else:
+            out.copy_(partial.to(torch.bfloat16))  # round to nearest even, CPU test path only
+
+    def forward(self, x, out=None, partial=None):
+        """x [M, K] bf16 (replicated on every rank) -> out [M, K] bf16 (identical on every rank)."""
+        M = x.shape[0]
+        if out is None:
+            out = torch.empty((M, self.K), dtype=torch.bfloat16, device=x.device)
+        if partial is None:
+            partial = out if self.partial_dtype == torch.bfloat16 else torch.empty((M, self.K), dtype=torch.float32,
+                                                                                   device=x.device)
+        chunk = self.chunk_rows if (self.chunk_rows and x.is_cuda and self.world > 1) else M
+        if chunk >= M:
+            self.local.run_partial(x, partial)
+            if self.world > 1:
+                dist.all_reduce(partial, group=self.group)
+            self._round(partial, out)
+            return out
+        # chunked: compute chunk i+1 on the current stream while NCCL reduces chunk i on a side stream
+        if self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream()
+        cur = torch.cuda.current_stream()
+        works = []
+        for m0 in range(0, M, chunk):
+            m1 = min(M, m0 + chunk)
+            self.local.run_partial(x[m0:m1], partial[m0:m1])
+            ev = torch.cuda.Event()
+            ev.record(cur)
+            with torch.cuda.stream(self._comm_stream):
+                self._comm_stream.wait_event(ev)
+                dist.all_reduce(partial[m0:m1], group=self.group)
+        cur.wait_stream(self._comm_stream)
+        self._round(partial, out)
+        return out

@@ -5,6 +5,7 @@ mounted) or the host CPU lacks AMX; callers then fall back to oracle.port.
 """
 import ctypes
 import os
+import sys
 import numpy as np
 from ._common import ptr, c_contig, c_int, c_float, c_void_p
 
@@ -42,7 +43,16 @@ def lib():
         _LIB = ctypes.CDLL(_PATH)
         for name in ("ref_fc_create", "ref_mlp_create", "ref_mlp_act"):
             getattr(_LIB, name).restype = c_void_p
-        if _LIB.ref_init() != 0:
+        # the reference prints a banner on stdout when it obtains the AMX tile permission: keep stdout clean
+        sys.stdout.flush()
+        saved = os.dup(1)
+        devnull = os.open(os.devnull, os.O_WRONLY)
+        try:
+            os.dup2(devnull, 1)
+            rc = _LIB.ref_init()
+        finally:
+            os.dup2(saved, 1); os.close(saved); os.close(devnull)
+        if rc != 0:
             raise RuntimeError("AMX tile permission request failed")
     return _LIB
 
