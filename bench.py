@@ -243,18 +243,20 @@ def run_ours(args, w, M, name):
     value = flops_of(w, M) / (ms * 1e-3) / 1e12
 
     # ---- dominant kernel alone: gate/up GEMM of this rank, K launches back to back (sustained regime) ----
-    for _ in range(3):
+    roofline = None
+    for _ in range(3 if "kernel" in args.legs else 0):
         mlp.gate_up(x.data_ptr(), H * 2, M, stream)
-    torch.cuda.synchronize()
-    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    k0.record()
-    for _ in range(args.steps):
+    if "kernel" in args.legs:
+      torch.cuda.synchronize()
+      k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+      k0.record()
+      for _ in range(args.steps):
         mlp.gate_up(x.data_ptr(), H * 2, M, stream)
-    k1.record(); torch.cuda.synchronize()
-    k_ms = k0.elapsed_time(k1) / args.steps
-    k_flops = 4.0 * M * H * Is
-    achieved = k_flops / (k_ms * 1e-3) / 1e12
-    roofline = {"kernel": "gemm_tc_kernel (gate/up projection + SiLU*up epilogue)", "bound": "tensor",
+      k1.record(); torch.cuda.synchronize()
+      k_ms = k0.elapsed_time(k1) / args.steps
+      k_flops = 4.0 * M * H * Is
+      achieved = k_flops / (k_ms * 1e-3) / 1e12
+      roofline = {"kernel": "gemm_tc_kernel (gate/up projection + SiLU*up epilogue)", "bound": "tensor",
                 "achieved": achieved, "peak": peaks["bf16_sustained"], "unit": "TFLOP/s",
                 "frac": achieved / peaks["bf16_sustained"], "peak_source": peaks["source"] + " (sustained cuBLAS bf16)",
                 "frac_of_burst_peak": achieved / peaks["bf16_burst"], "us_per_launch": k_ms * 1e3,
@@ -272,6 +274,12 @@ def run_ours(args, w, M, name):
         line["clocks"] = clocks
 
     # ---- end to end through the host-buffer entry point (1 GPU) / host x in + host out back (N GPUs) ----
+    if "e2e" not in args.legs:
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+        if world > 1:
+            dist.barrier(); dist.destroy_process_group()
+        return
     xh = torch.empty((M, H), dtype=torch.bfloat16).pin_memory(); xh.copy_(x.cpu())
     oh = torch.empty((M, H), dtype=torch.bfloat16).pin_memory()
     if world == 1:
@@ -302,7 +310,7 @@ def run_ours(args, w, M, name):
                           "host x -> device, tensor-parallel forward, device out -> host, per rank"}
 
     # ---- decode-shaped leg: M = 1, the weight stream in GB/s against the measured HBM copy bandwidth ----
-    if world == 1:
+    if world == 1 and "decode" in args.legs:
         x1 = x[:1].contiguous()
         o1 = torch.empty((1, H), dtype=torch.bfloat16, device=dev)
         def dstep():
@@ -335,7 +343,7 @@ def run_ours(args, w, M, name):
                                        "frac": gbs / peaks["hbm_gbs"], "peak_source": peaks["source"]}}
 
     # ---- CPU baseline beside it (rank 0, 1 GPU only) ----
-    if rank == 0 and world == 1 and not args.no_cpu:
+    if rank == 0 and world == 1 and "cpu" in args.legs:
         try:
             sec, info = cpu_arm(w, M, budget_s=15.0)
             info["value"] = flops_of(w, M) / sec / 1e12; info["unit"] = "TFLOP/s"
@@ -360,10 +368,15 @@ def main():
     ap.add_argument("--M", type=int, default=None)
     ap.add_argument("--chunk-rows", type=int, default=1024)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--legs", default="kernel,e2e,decode,cpu",
+                    help="optional legs after the main timed loop (comma list of kernel,e2e,decode,cpu; '' = none)")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1:
         args.gpus = world
+    args.legs = set(x for x in args.legs.split(",") if x)
+    if args.no_cpu:
+        args.legs.discard("cpu")
     name = args.workload or ("llama7b_mlp" if args.gpus == 1 else "llama70b_mlp")
     w = WORKLOADS[name]
     M = args.M or w["M"]
