@@ -37,7 +37,7 @@ WORKLOADS = {
 }
 # DRAM traffic of one gate/up GEMM launch (dram__bytes_read.sum + dram__bytes_write.sum), from the ncu capture
 # summarised in profiles/ (file named there); None until a capture exists for the workload.
-NCU_TRAFFIC_BYTES = {"llama7b_mlp": None, "llama70b_mlp": None}
+NCU_TRAFFIC_BYTES = {"llama7b_mlp": 231.05e6, "llama70b_mlp": None}  # profiles/gemm_tc_kernel_llama7b_mlp_M2048.md
 
 
 def measured_peaks():
@@ -257,9 +257,11 @@ def run_ours(args, w, M, name):
       k_flops = 4.0 * M * H * Is
       achieved = k_flops / (k_ms * 1e-3) / 1e12
       roofline = {"kernel": "gemm_tc_kernel (gate/up projection + SiLU*up epilogue)", "bound": "tensor",
-                "achieved": achieved, "peak": peaks["bf16_sustained"], "unit": "TFLOP/s",
-                "frac": achieved / peaks["bf16_sustained"], "peak_source": peaks["source"] + " (sustained cuBLAS bf16)",
-                "frac_of_burst_peak": achieved / peaks["bf16_burst"], "us_per_launch": k_ms * 1e3,
+                "achieved": achieved, "peak": peaks["bf16_burst"], "unit": "TFLOP/s",
+                "frac": achieved / peaks["bf16_burst"],
+                "peak_source": peaks["source"] + " (cuBLAS bf16 burst figure: the kernel is timed alone, in a loop "
+                                                 "far shorter than the power-cap time constant)",
+                "frac_of_sustained_peak": achieved / peaks["bf16_sustained"], "us_per_launch": k_ms * 1e3,
                 "flops_per_launch": k_flops, "traffic": NCU_TRAFFIC_BYTES.get(name)}
 
     line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
@@ -274,40 +276,35 @@ def run_ours(args, w, M, name):
         line["clocks"] = clocks
 
     # ---- end to end through the host-buffer entry point (1 GPU) / host x in + host out back (N GPUs) ----
-    if "e2e" not in args.legs:
-        if rank == 0:
-            print(json.dumps(line), flush=True)
+    if "e2e" in args.legs:
+        xh = torch.empty((M, H), dtype=torch.bfloat16).pin_memory(); xh.copy_(x.cpu())
+        oh = torch.empty((M, H), dtype=torch.bfloat16).pin_memory()
+        if world == 1:
+            def e2e_step():
+                mlp.run_host(xh.data_ptr(), H * 2, M, oh.data_ptr(), H * 2, stream)
+        else:
+            def e2e_step():
+                x.copy_(xh, non_blocking=True)
+                step()
+                oh.copy_(out, non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        e1.record()
+        barrier()
+        e_ms = e0.elapsed_time(e1) / args.steps
         if world > 1:
-            dist.barrier(); dist.destroy_process_group()
-        return
-    xh = torch.empty((M, H), dtype=torch.bfloat16).pin_memory(); xh.copy_(x.cpu())
-    oh = torch.empty((M, H), dtype=torch.bfloat16).pin_memory()
-    if world == 1:
-        def e2e_step():
-            mlp.run_host(xh.data_ptr(), H * 2, M, oh.data_ptr(), H * 2, stream)
-    else:
-        def e2e_step():
-            x.copy_(xh, non_blocking=True)
-            step()
-            oh.copy_(out, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-    for _ in range(3):
-        e2e_step()
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        e2e_step()
-    e1.record()
-    barrier()
-    e_ms = e0.elapsed_time(e1) / args.steps
-    if world > 1:
-        t = torch.tensor([e_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e_ms = float(t.item())
-    line["e2e"] = {"value": flops_of(w, M) / (e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e_ms,
-                   "h2d_bytes_per_step": M * H * 2 * world, "d2h_bytes_per_step": M * H * 2 * world,
-                   "api": "b200fc_mlp_run_host (pinned host buffers)" if world == 1 else
-                          "host x -> device, tensor-parallel forward, device out -> host, per rank"}
+            t = torch.tensor([e_ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e_ms = float(t.item())
+        line["e2e"] = {"value": flops_of(w, M) / (e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e_ms,
+                       "h2d_bytes_per_step": M * H * 2 * world, "d2h_bytes_per_step": M * H * 2 * world,
+                       "api": "b200fc_mlp_run_host (pinned host buffers)" if world == 1 else
+                              "host x -> device, tensor-parallel forward, device out -> host, per rank"}
 
     # ---- decode-shaped leg: M = 1, the weight stream in GB/s against the measured HBM copy bandwidth ----
     if world == 1 and "decode" in args.legs:

@@ -150,7 +150,7 @@ static int validate_epilogue(const b200fc_epilogue_t* ep, bool int_acc) {
     return B200FC_OK;
 }
 
-static int matmul_device(const Weight& w, Weight* w_mut, const void* A, int dtypeA, int M, int K, int64_t lda, int n0,
+int matmul_device(const Weight& w, Weight* w_mut, const void* A, int dtypeA, int M, int K, int64_t lda, int n0,
                          int n1, const b200fc_epilogue_t* ep_in, cudaStream_t s) {
     if (M < 0 || K != w.K) { set_error("matmul: K=%d does not match the packed weights (K=%d) or M<0", K, w.K); return B200FC_ERR_INVALID; }
     if (n0 < 0 || n1 > w.N || n0 > n1) { set_error("matmul: column range [%d,%d) outside [0,%d)", n0, n1, w.N); return B200FC_ERR_INVALID; }
@@ -205,15 +205,6 @@ static int matmul_device(const Weight& w, Weight* w_mut, const void* A, int dtyp
     return launch_gemm_tc(w.data, w.dtype, w.K_pad, w.N_pad, A_use, dtypeA, M, K, lda_use, n0, n1, ep, s);
 }
 
-struct Mlp {
-    int K = 0, N = 0, Ns = 0;  // hidden, intermediate, this rank's share of the intermediate dimension
-    int tp_rank = 0, tp_size = 1;
-    Weight gate_up, down;
-    void* act = nullptr; size_t act_bytes = 0;      // [M, Ns] bf16
-    int act_rows = 0;                               // rows of the last gate_up
-    void* stage_x = nullptr; size_t stage_x_bytes = 0;
-    void* stage_o = nullptr; size_t stage_o_bytes = 0;
-};
 
 static int mlp_gate_up_device(Mlp& m, const void* x, int64_t ldx, int M, cudaStream_t s) {
     if (M < 0) { set_error("mlp: M < 0"); return B200FC_ERR_INVALID; }
@@ -244,8 +235,6 @@ static int mlp_run_device(Mlp& m, const void* x, int64_t ldx, int M, void* out, 
 
 using namespace b200fc;
 
-struct b200fc_weight { Weight w; };
-struct b200fc_mlp { Mlp m; };
 
 extern "C" {
 

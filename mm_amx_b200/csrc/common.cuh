@@ -45,6 +45,17 @@ struct Epilogue {
     const float* q_per_oc;
 };
 
+// Fused Llama MLP object (b200fc_mlp_t)
+struct Mlp {
+    int K = 0, N = 0, Ns = 0;  // hidden, intermediate, this rank's share of the intermediate dimension
+    int tp_rank = 0, tp_size = 1;
+    Weight gate_up, down;
+    void* act = nullptr; size_t act_bytes = 0;      // [M, Ns] bf16
+    int act_rows = 0;                               // rows of the last gate_up
+    void* stage_x = nullptr; size_t stage_x_bytes = 0;
+    void* stage_o = nullptr; size_t stage_o_bytes = 0;
+};
+
 // error plumbing (api.cu)
 void set_error(const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);
@@ -57,6 +68,11 @@ int check_kernel_status(cudaStream_t s);  // synchronises and reads it
         cudaError_t e__ = (call);                                           \
         if (e__ != cudaSuccess) return ::b200fc::cuda_fail(e__, #call);     \
     } while (0)
+
+// api.cu: validated dispatch of one Matmul call on device pointers (w_mut: the same object when the call may create
+// its lazily built bf16 copy of compressed weights, else null)
+int matmul_device(const Weight& w, Weight* w_mut, const void* A, int dtypeA, int M, int K, int64_t lda, int n0, int n1,
+                  const b200fc_epilogue_t* ep, cudaStream_t s);
 
 // ---- launchers -------------------------------------------------------------------------------------------------
 // pack.cu
@@ -146,3 +162,7 @@ __device__ __forceinline__ void store_scalar(float v, int m, int n, const Epilog
 #endif  // __CUDACC__
 
 }  // namespace b200fc
+
+// the opaque handle types of the C ABI
+struct b200fc_weight { b200fc::Weight w; };
+struct b200fc_mlp { b200fc::Mlp m; };
