@@ -133,6 +133,20 @@ int b200fc_mlp_down(b200fc_mlp_t* mlp, int M, void* out, int out_dtype, int64_t 
 /* x and out in HOST memory; copies, runs, copies back, synchronises. */
 int b200fc_mlp_run_host(b200fc_mlp_t* mlp, const void* x, int64_t ldx_bytes, int M, void* out, int64_t ldo_bytes,
                         void* stream);
+/* The same forward for decode-shaped batches (1 <= M <= 16) WITHOUT any allocation — no counterpart in the
+ * reference.  For callers that may not enter the CUDA allocator while they run (a serving loop with a frozen memory
+ * plan, code that must not trigger the device synchronisation cudaMalloc / cudaFree imply).  The gate/up activation
+ * lives in a fixed 1 MiB device array inside the library image, so M * (N / tp) * 2 bytes must not exceed
+ * b200fc_mlp_decode_static_capacity(); larger requests fail with B200FC_ERR_INVALID.  out is [M, K] in out_dtype
+ * B200FC_BF16 (the full result when tp_size == 1) or B200FC_F32 / B200FC_BF16 (this rank's contribution otherwise).
+ *   - The first call on each device looks up the array's device address; make that first call during start-up,
+ *     before any stream capture begins.
+ *   - All calls on a device share the one array: calls whose kernels can overlap on the GPU (different streams
+ *     without ordering) race on it.  Calls on one stream are ordered and safe.
+ *   - The array keeps the previous call's activation; every element a call reads it has written first. */
+int b200fc_mlp_run_decode_static(b200fc_mlp_t* mlp, const void* x, int64_t ldx_bytes, int M, void* out, int out_dtype,
+                                 int64_t ldo_bytes, void* stream);
+int64_t b200fc_mlp_decode_static_capacity(void);
 /* device pointer to the [M, N/tp] bf16 activation of the last run (debug / layer-wise parity) */
 const void* b200fc_mlp_act(const b200fc_mlp_t* mlp);
 

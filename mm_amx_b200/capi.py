@@ -47,6 +47,8 @@ SIGNATURES = {
     "b200fc_mlp_gate_up": (c_int, [c_void_p, c_void_p, c_i64, c_int, c_void_p]),
     "b200fc_mlp_down": (c_int, [c_void_p, c_int, c_void_p, c_int, c_i64, c_void_p]),
     "b200fc_mlp_run_host": (c_int, [c_void_p, c_void_p, c_i64, c_int, c_void_p, c_i64, c_void_p]),
+    "b200fc_mlp_run_decode_static": (c_int, [c_void_p, c_void_p, c_i64, c_int, c_void_p, c_int, c_i64, c_void_p]),
+    "b200fc_mlp_decode_static_capacity": (c_i64, []),
     "b200fc_mlp_act": (c_void_p, [c_void_p]),
     "b200fc_device_malloc": (c_int, [ctypes.POINTER(c_void_p), c_i64]),
     "b200fc_device_free": (c_int, [c_void_p]),
@@ -164,6 +166,10 @@ class Mlp:
 
     def run_host(self, x_ptr, ldx_bytes, M, out_ptr, ldo_bytes, stream=None):
         check(lib().b200fc_mlp_run_host(self.h, x_ptr, ldx_bytes, M, out_ptr, ldo_bytes, stream))
+
+    def run_decode_static(self, x_ptr, ldx_bytes, M, out_ptr, out_dtype, ldo_bytes, stream=None):
+        """Allocation-free forward for 1 <= M <= 16; see b200fc_mlp_run_decode_static in include/b200fc.h."""
+        check(lib().b200fc_mlp_run_decode_static(self.h, x_ptr, ldx_bytes, M, out_ptr, out_dtype, ldo_bytes, stream))
 
     def act_ptr(self):
         return lib().b200fc_mlp_act(self.h)

@@ -1,0 +1,81 @@
+// Decode-shaped fused MLP that never allocates.
+//
+// Some callers are not allowed to enter the CUDA allocator once they are running: a serving loop whose memory plan
+// was fixed at start-up and that hands every remaining byte of HBM to a KV cache, a callback running while another
+// thread holds an allocator lock, a host runtime that forbids any cudaMalloc / cudaFree after initialisation because
+// those calls synchronise the device.  b200fc_mlp_run keeps its gate/up activation in a buffer that it grows with
+// cudaMalloc on demand, so those callers cannot use it.  The entry point below does the same computation for
+// decode-shaped batches with the activation held in a fixed device array that is part of this library's image.
+//
+// It has no counterpart in the reference (whose activation buffer grows inside MLP::run).
+#include <map>
+#include <mutex>
+#include "common.cuh"
+
+namespace {
+
+// The scratch: one activation matrix [M, N / tp] in bf16.  Every GPU that loads this library holds these bytes from
+// load until the process exits.
+constexpr size_t kStaticActBytes = (size_t)1 << 20;  // 1 MiB: M * (N / tp) <= 524288 elements, e.g. 16 rows x 28672
+static __device__ __align__(256) unsigned char g_static_act[kStaticActBytes];
+
+std::mutex g_mu;
+std::map<int, void*> g_addr;  // device ordinal -> device address of g_static_act on that device
+
+// In host code the name g_static_act is only a handle for the symbol, not a device address; the address has to be
+// asked for, once per device, with that device current.
+int static_act_address(void** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return b200fc::cuda_fail(e, "cudaGetDevice");
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_addr.find(dev);
+    if (it == g_addr.end()) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_static_act);
+        if (e != cudaSuccess) return b200fc::cuda_fail(e, "cudaGetSymbolAddress(g_static_act)");
+        if (!p) { b200fc::set_error("mlp_run_decode_static: null symbol address"); return B200FC_ERR_CUDA; }
+        it = g_addr.emplace(dev, p).first;
+    }
+    *out = it->second;
+    return B200FC_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int64_t b200fc_mlp_decode_static_capacity(void) { return (int64_t)kStaticActBytes; }
+
+int b200fc_mlp_run_decode_static(b200fc_mlp_t* h, const void* x, int64_t ldx, int M, void* out, int out_dtype,
+                                 int64_t ldo, void* stream) {
+    using namespace b200fc;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!h || !x || !out) { set_error("mlp_run_decode_static: null pointer"); return B200FC_ERR_INVALID; }
+    if (out_dtype != B200FC_BF16 && out_dtype != B200FC_F32) { set_error("mlp_run_decode_static: out_dtype must be bf16 or f32"); return B200FC_ERR_INVALID; }
+    Mlp& m = h->m;
+    if (M < 1 || M > 16) {
+        set_error("mlp_run_decode_static: M = %d outside [1, 16] (decode-shaped batches only)", M);
+        return B200FC_ERR_INVALID;
+    }
+    const size_t need = (size_t)M * m.Ns * 2;
+    if (need > kStaticActBytes) {
+        set_error("mlp_run_decode_static: activation of %d x %d bf16 = %zu bytes exceeds the fixed %zu-byte scratch",
+                  M, m.Ns, need, kStaticActBytes);
+        return B200FC_ERR_INVALID;
+    }
+    void* act = nullptr;
+    int rc = static_act_address(&act);
+    if (rc) return rc;
+    // gate/up projection + SiLU*up writes all M x Ns activation elements before the down projection reads them, and
+    // the down projection reads nothing beyond them, so nothing in the scratch has to be cleared between calls.
+    b200fc_epilogue_t e1 = {};
+    e1.steps = B200FC_STEP_SILU_MUL; e1.out_dtype = B200FC_BF16; e1.C = act; e1.ldc_bytes = (int64_t)m.Ns * 2;
+    rc = matmul_device(m.gate_up, nullptr, x, B200FC_BF16, M, m.K, ldx, 0, 2 * m.Ns, &e1, s);
+    if (rc) return rc;
+    b200fc_epilogue_t e2 = {};
+    e2.steps = 0; e2.out_dtype = out_dtype; e2.C = out; e2.ldc_bytes = ldo;
+    return matmul_device(m.down, nullptr, act, B200FC_BF16, M, m.Ns, (int64_t)m.Ns * 2, 0, m.K, &e2, s);
+}
+
+}  // extern "C"
