@@ -82,7 +82,10 @@ typedef enum {
 } b200fc_pack_mode_t;
 
 /* Packs B once.  transposeB = 0: B is [K, N]; 1: B is [N, K] (Matmul ctor flag, kernels_amx.hpp:1071, getSubMatB
- * :699-705).  B may be a host or a device pointer.  `scales` is used by B200FC_PACK_INT8_CHANNEL only. */
+ * :699-705).  B may be a host or a device pointer.  `scales`: B200FC_PACK_INT8_CHANNEL needs the [N] per-channel
+ * scales; B200FC_PACK_QUANT_TENSOR accepts an optional pointer to ONE float, the absmax to quantise with (the reference
+ * takes the absmax of the whole B even when a thread packs only its column range, kernels_amx.hpp:1370); NULL = absmax
+ * of the given matrix. */
 int b200fc_weight_pack(const void* B, int dtypeB, int K, int N, int64_t ldb_bytes, int transposeB, int pack_mode,
                        const float* scales, b200fc_weight_t** out, void* stream);
 int b200fc_weight_free(b200fc_weight_t* w);

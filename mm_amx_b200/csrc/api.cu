@@ -268,7 +268,11 @@ int b200fc_weight_pack(const void* B, int dtypeB, int K, int N, int64_t ldb, int
             if (pack_mode == B200FC_PACK_QUANT_TENSOR) {
                 float* absmax = nullptr;
                 rc = cudaMalloc(&absmax, sizeof(float)) == cudaSuccess ? 0 : B200FC_ERR_NOMEM;
-                if (!rc) rc = launch_absmax(src.p, rows, cols, src.ld, absmax, s);
+                if (!rc && scales) {  // caller-supplied absmax (e.g. of a larger matrix this one is a slice of)
+                    if (cudaMemcpyAsync(absmax, scales, sizeof(float), cudaMemcpyDefault, s) != cudaSuccess) rc = B200FC_ERR_CUDA;
+                } else if (!rc) {
+                    rc = launch_absmax(src.p, rows, cols, src.ld, absmax, s);
+                }
                 if (!rc) rc = launch_quant_pack(src.p, K, N, src.ld, transposeB, w, absmax, s);
                 float mx = 0.0f;
                 if (!rc && cudaMemcpyAsync(&mx, absmax, sizeof(float), cudaMemcpyDeviceToHost, s) != cudaSuccess) rc = B200FC_ERR_CUDA;

@@ -9,8 +9,8 @@
 //   The packed weights are [N_pad, K_pad] with K contiguous.  A warp owns 32 output channels (two 16-row blocks).
 //   Thread (g = lane / 4, t = lane % 4) streams rows g and g + 8 of each block with 16-byte
 //   ld.global.nc.L1::no_allocate loads: per 64-byte K block it takes bytes [16t, 16t + 16) of its rows, so four
-//   neighbouring lanes cover one 64-byte segment and a whole iteration (4 K blocks) covers 256 contiguous bytes per
-//   row.  The 16 loads of an iteration (64 registers) are all issued before any is used.
+//   neighbouring lanes cover one 64-byte segment.  Loads are issued a pipeline stage (2 K blocks, 8 loads per thread)
+//   ahead of their use and two stages stay in flight, so a warp always has 8 KB outstanding.
 //   The loaded registers ARE the A fragments of mma.sync.m16n8k16 (weights as the 16-row operand, the <= 16
 //   activation rows as the 8-column operand): K is permuted identically for both operands, which is free because
 //   a dot product does not care about the order of its terms per MMA slot.  int8 weights are widened to bf16 in
@@ -33,7 +33,7 @@ constexpr int WARPS = 4;
 constexpr int ROWS_PER_WARP = 32;
 constexpr int ROWS_PER_CTA = WARPS * ROWS_PER_WARP;  // 128
 constexpr int KB_BYTES = 64;                          // one K block = 64 bytes of a weight row
-constexpr int KB_PER_ITER = 4;
+constexpr int KB_PER_ITER = 2;                        // K blocks per pipeline stage
 constexpr int CHUNK_K = 1024;                         // activation elements staged per chunk
 
 struct GemvParams {
@@ -76,7 +76,7 @@ __device__ __forceinline__ unsigned s8x2_to_bf16x2(unsigned w, unsigned sel) {
 }
 
 template <bool W8, int NT>
-__global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(WARPS * 32, 4) gemv_kernel(const GemvParams p) {
     constexpr int KB_ELEMS = W8 ? 64 : 32;                  // K elements per K block
     constexpr int MP = 8 * NT;                              // padded activation rows
     constexpr int XROW = CHUNK_K * 2 + (W8 ? 16 : 64);      // bytes per staged activation row (bank-conflict free)
@@ -120,48 +120,47 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
 
     const bool x_vec = (((uintptr_t)p.X & 15) == 0) && ((p.ldx & 15) == 0);
 
-    for (int it = it_begin; it < it_end; it++) {
-        // ---- issue this iteration's weight loads (in flight while activations are staged) ----
-        uint4 w[2][2][KB_PER_ITER];
+    // One pipeline stage = KB_PER_ITER K blocks of the warp's four rows (8 x 16-byte loads per thread).  Two stages
+    // are kept in flight: the loads of stage i+1 are issued before stage i is multiplied.
+    uint4 wbuf[2][2][2][KB_PER_ITER];
+    auto issue = [&](int buf, int it) {
         const int kb0 = it * KB_PER_ITER;
 #pragma unroll
         for (int j = 0; j < KB_PER_ITER; j++) {
-            const bool in = kb0 + j < p.n_kb;
+            const bool in = it < it_end && kb0 + j < p.n_kb;
 #pragma unroll
             for (int rb = 0; rb < 2; rb++)
 #pragma unroll
                 for (int h = 0; h < 2; h++)
-                    w[rb][h][j] = in ? ld_stream(wrow[rb][h] + (long long)(kb0 + j) * KB_BYTES) : make_uint4(0, 0, 0, 0);
+                    wbuf[buf][rb][h][j] = in ? ld_stream(wrow[rb][h] + (long long)(kb0 + j) * KB_BYTES) : make_uint4(0, 0, 0, 0);
         }
-
-        // ---- stage the activation chunk when entering it ----
-        const int it_in_chunk = (it - it_begin) % ITERS_PER_CHUNK;
-        const int chunk_k0 = (it - it_in_chunk) * KB_PER_ITER * KB_ELEMS;  // first K element of the chunk
-        if (it_in_chunk == 0) {
-            __syncthreads();  // everyone is done with the previous chunk
-            const int k_need = it_end * KB_PER_ITER * KB_ELEMS;  // nothing beyond this split's K range is read
-            for (int u = threadIdx.x; u < MP * (CHUNK_K / 8); u += blockDim.x) {
-                const int row = u / (CHUNK_K / 8), k = chunk_k0 + (u % (CHUNK_K / 8)) * 8;
-                if (k >= k_need) continue;
-                uint4 v = make_uint4(0, 0, 0, 0);  // zero beyond M rows / K columns: padded weights are zero there
-                if (row < p.M && k < p.K) {
-                    const unsigned char* src = p.X + (long long)row * p.ldx + (long long)k * 2;
-                    if (x_vec && k + 8 <= p.K) {
-                        v = *(const uint4*)src;
-                    } else {
-                        unsigned short e[8];
+    };
+    auto stage_x = [&](int it) {
+        // stage the activation chunk that starts at iteration `it`
+        const int chunk_k0 = it * KB_PER_ITER * KB_ELEMS;
+        __syncthreads();  // everyone is done with the previous chunk
+        const int k_need = it_end * KB_PER_ITER * KB_ELEMS;  // nothing beyond this split's K range is read
+        for (int u = threadIdx.x; u < MP * (CHUNK_K / 8); u += blockDim.x) {
+            const int row = u / (CHUNK_K / 8), k = chunk_k0 + (u % (CHUNK_K / 8)) * 8;
+            if (k >= k_need) continue;
+            uint4 v = make_uint4(0, 0, 0, 0);  // zero beyond M rows / K columns: padded weights are zero there
+            if (row < p.M && k < p.K) {
+                const unsigned char* src = p.X + (long long)row * p.ldx + (long long)k * 2;
+                if (x_vec && k + 8 <= p.K) {
+                    v = *(const uint4*)src;
+                } else {
+                    unsigned short e[8];
 #pragma unroll
-                        for (int q = 0; q < 8; q++) e[q] = (k + q < p.K) ? ((const unsigned short*)src)[q] : (unsigned short)0;
-                        v.x = e[0] | ((unsigned)e[1] << 16); v.y = e[2] | ((unsigned)e[3] << 16);
-                        v.z = e[4] | ((unsigned)e[5] << 16); v.w = e[6] | ((unsigned)e[7] << 16);
-                    }
+                    for (int q = 0; q < 8; q++) e[q] = (k + q < p.K) ? ((const unsigned short*)src)[q] : (unsigned short)0;
+                    v.x = e[0] | ((unsigned)e[1] << 16); v.y = e[2] | ((unsigned)e[3] << 16);
+                    v.z = e[4] | ((unsigned)e[5] << 16); v.w = e[6] | ((unsigned)e[7] << 16);
                 }
-                *(uint4*)(smem + row * XROW + (u % (CHUNK_K / 8)) * 16) = v;
             }
-            __syncthreads();
+            *(uint4*)(smem + row * XROW + (u % (CHUNK_K / 8)) * 16) = v;
         }
-
-        // ---- multiply ----
+        __syncthreads();
+    };
+    auto multiply = [&](int buf, int it_in_chunk) {
 #pragma unroll
         for (int j = 0; j < KB_PER_ITER; j++) {
             // activation fragments of this K block: per row, the bytes matching this thread's weight bytes
@@ -179,8 +178,9 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
             }
 #pragma unroll
             for (int rb = 0; rb < 2; rb++) {
-                const unsigned wa[4] = {w[rb][0][j].x, w[rb][0][j].y, w[rb][0][j].z, w[rb][0][j].w};  // row g
-                const unsigned wb[4] = {w[rb][1][j].x, w[rb][1][j].y, w[rb][1][j].z, w[rb][1][j].w};  // row g + 8
+                const uint4 va = wbuf[buf][rb][0][j], vb = wbuf[buf][rb][1][j];
+                const unsigned wa[4] = {va.x, va.y, va.z, va.w};  // row g
+                const unsigned wb[4] = {vb.x, vb.y, vb.z, vb.w};  // row g + 8
 #pragma unroll
                 for (int q = 0; q < MMA_PER_LOAD; q++) {
                     unsigned a0, a1, a2, a3;
@@ -196,6 +196,21 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const GemvParams p) {
                 }
             }
         }
+    };
+
+    // The weights do not depend on the kernel that precedes this one in the stream, the activations may: start the
+    // weight stream, let the next kernel in the stream begin its own, then wait for the predecessor's results.
+    issue(0, it_begin);
+    issue(1, it_begin + 1);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int it = it_begin; it < it_end; it += 2) {
+        const int it_in_chunk = (it - it_begin) % ITERS_PER_CHUNK;   // even: ITERS_PER_CHUNK is even
+        if (it_in_chunk == 0) stage_x(it);
+        multiply(0, it_in_chunk);
+        issue(0, it + 2);
+        if (it + 1 < it_end) multiply(1, it_in_chunk + 1);
+        issue(1, it + 3);
     }
 
     // ---- partial tile -> shared memory: part[token][row] ----
@@ -263,13 +278,17 @@ int launch_variant(const GemvParams& p, int row_ctas, cudaStream_t s) {
     cfg.blockDim = dim3(WARPS * 32, 1, 1);
     cfg.dynamicSmemBytes = SMEM;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = p.splits;
     attr[0].val.clusterDim.z = 1;
+    // programmatic dependent launch: this kernel may start while its predecessor in the stream drains; it reads
+    // activations only after griddepcontrol.wait
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     B200FC_CUDA(cudaLaunchKernelEx(&cfg, gemv_kernel<W8, NT>, p));
     count_launch();
     return B200FC_OK;
@@ -295,10 +314,10 @@ int launch_gemv(const Weight& w, const void* A, int M, int K, int64_t lda, int n
     p.ep = ep;
     const int row_ctas = (n1 - n0 + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
     const int iters_total = (p.n_kb + KB_PER_ITER - 1) / KB_PER_ITER;
-    // split K over a cluster until the grid covers the GPU about twice (148 SMs), at most 8 ways, at least one
-    // iteration per split
+    // split K over a cluster (at most 8 ways, the portable limit) while the whole grid still fits the GPU in one
+    // wave (148 SMs x 4 resident CTAs) and every split keeps at least two pipeline stages of work
     int S = 1;
-    while (S < 8 && row_ctas * S < 296 && iters_total >= 2 * S) S *= 2;
+    while (S < 8 && row_ctas * S * 2 <= 148 * 4 && iters_total >= 4 * S) S *= 2;
     p.splits = S;
     const bool w8 = w.dtype == B200FC_S8;
     if (M <= 8) return w8 ? launch_variant<true, 1>(p, row_ctas, s) : launch_variant<false, 1>(p, row_ctas, s);

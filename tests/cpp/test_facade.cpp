@@ -1,0 +1,178 @@
+// Accuracy run of the C++ façade (include/mm_amx_gpu.hpp), laid out like the reference's own checks:
+//   amx_FC_acc over the tail shapes of test_FC_acc for int8, bf16 and bf16 x int8-compressed weights, B given as
+//   [K,N] and as [N,K] (main.cpp:235-267, 714-744); MatmulMTOMP-style column split (main.cpp:442-479);
+//   Bias+GeLU against erf (main.cpp:529-555); MatmulVector / GemAvB (main.cpp:313-370); fused MLP (tests/amx-mlp.cpp:845-881).
+// Expected values are computed here with plain loops; inputs are two-valued (tensor2D::fill_rnd), so sums are exact.
+// Prints one line per check and exits non-zero on any mismatch.
+#include <cstdio>
+#include <cmath>
+#include <vector>
+#include "mm_amx_gpu.hpp"
+
+using ov::bfloat16;
+namespace PP = amx_kernel::PP;
+static int g_fail = 0;
+
+static void report(const char* what, int M, int K, int N, bool ok) {
+    std::printf("%-34s (%d,%d,%d) %s\n", what, M, K, N, ok ? "Match" : "MISMATCH");
+    if (!ok) g_fail++;
+}
+
+template <typename T>
+static void expect_matmul(tensor2D<T>& A, tensor2D<T>& B, tensor2D<float>& C) {  // B is [K,N]
+    for (int m = 0; m < C.dims[0]; m++)
+        for (int n = 0; n < C.dims[1]; n++) {
+            double s = 0;
+            for (int k = 0; k < A.dims[1]; k++) s += (double)(float)A(m, k) * (double)(float)B(k, n);
+            C(m, n) = (float)s;
+        }
+}
+
+template <typename T, typename MM, PP::Steps steps>
+static void fc_acc(const char* name, int M, int K, int N) {
+    tensor2D<T> A(M, K, true), B(K, N);
+    tensor2D<T> BT = B.Tr();
+    tensor2D<float> C(M, N), C0(M, N);
+    expect_matmul(A, B, C0);
+    MM fc(true, false), fcTr(true, true);
+    PP::BiasGeluStore<float, steps> pp(C);
+    C = 0.0f;
+    fc(A, B, pp);
+    report(name, M, K, N, C0 == C);
+    C = 0.0f;
+    fcTr(A, BT, pp);
+    report((std::string(name) + " transposeB").c_str(), M, K, N, C0 == C);
+    // second call re-uses the packed weights (constB)
+    C = 0.0f;
+    fc(A, B, pp);
+    report((std::string(name) + " cached").c_str(), M, K, N, C0 == C);
+}
+
+template <typename T, typename MM, PP::Steps steps>
+static void all_shapes(const char* name) {
+    const int shapes[][3] = {{16, 65, 32}, {16, 66, 32}, {16, 67, 32}, {16, 68, 32}, {16, 69, 32}, {32, 64, 5}, {128, 96, 16},
+                             {2, 2560, 1088}, {2, 337, 271}, {22, 2560, 1088}, {704, 320, 256}, {705, 320, 257},
+                             {720, 320, 273}, {735, 320, 271}, {735, 321, 271}, {735, 337, 271}, {2, 320, 256}};
+    for (auto& s : shapes) fc_acc<T, MM, steps>(name, s[0], s[1], s[2]);
+}
+
+static void column_split() {
+    // four "threads", each with its own Matmul object and column range in 32-column units
+    int M = 100, K = 256, N = 300;
+    tensor2D<bfloat16> A(M, K), B(K, N);
+    tensor2D<float> C(M, N), C0(M, N);
+    std::vector<float> bias(N + 32);
+    for (int n = 0; n < N; n++) bias[n] = 0.25f * (n % 7);
+    expect_matmul(A, B, C0);
+    for (int m = 0; m < M; m++) for (int n = 0; n < N; n++) C0(m, n) += bias[n];
+    C = 0.0f;
+    PP::BiasGeluStore<float, PP::BIAS> pp(C, bias.data());
+    const int nthr = 4, units = (N + 31) / 32;
+    std::vector<amx_kernel::Matmul<bfloat16, bfloat16>> ops;
+    for (int t = 0; t < nthr; t++) ops.emplace_back(true, false);
+    for (int rep = 0; rep < 2; rep++)
+        for (int t = 0; t < nthr; t++) {
+            int u0 = units * t / nthr, u1 = units * (t + 1) / nthr;
+            int n0 = std::min(u0 * 32, N), n1 = std::min(u1 * 32, N);
+            if (n1 > n0) ops[t](A, B, n0, n1, pp);
+        }
+    report("column split + bias", M, K, N, C0 == C);
+}
+
+static void bias_gelu() {
+    int M = 88, K = 77, N = 66;
+    tensor2D<bfloat16> A(M, K), B(K, N);
+    tensor2D<float> C(M, N), C0(M, N);
+    std::vector<float> bias(N + 32);
+    for (int n = 0; n < N; n++) bias[n] = 0.125f * ((n % 13) - 6);
+    expect_matmul(A, B, C0);
+    bool ok = true;
+    amx_kernel::Matmul<bfloat16, bfloat16> fc(true, false);
+    PP::BiasGeluStore<float, PP::BIAS_GELU> pp(C, bias.data());
+    fc(A, B, pp);
+    for (int m = 0; m < M; m++)
+        for (int n = 0; n < N; n++) {
+            float x = C0(m, n) + bias[n];
+            float ref = x * 0.5f * (1.0f + std::erf(x / std::sqrt(2.0f)));
+            if (!(std::fabs(ref - C(m, n)) <= 0.001f)) ok = false;
+        }
+    report("bias + gelu vs erf (atol 1e-3)", M, K, N, ok);
+}
+
+static void quant_out() {
+    int M = 64, K = 128, N = 96;
+    tensor2D<int8_t> A(M, K), B(K, N);
+    tensor2D<int8_t> C(M, N);
+    tensor2D<float> acc(M, N);
+    for (int m = 0; m < M; m++) for (int n = 0; n < N; n++) {
+        int s = 0; for (int k = 0; k < K; k++) s += (int)A(m, k) * (int)B(k, n); acc(m, n) = (float)s; }
+    std::vector<float> bias(N + 32, 0.5f);
+    amx_kernel::Matmul<int8_t, int8_t> fc(true, false);
+    PP::BiasGeluStore<int8_t, (PP::Steps)(PP::DEQUANT | PP::BIAS | PP::QUANT)> pp(C, bias.data());
+    pp.set_deq_scale(0.25f);
+    pp.set_q_scale(4.0f);
+    fc(A, B, pp);
+    bool ok = true;
+    for (int m = 0; m < M; m++) for (int n = 0; n < N; n++) {
+        float v = (acc(m, n) * 0.25f + 0.5f) * 4.0f;   // exact in fp32 for these inputs
+        int q = (int)std::nearbyint(v); q = q > 127 ? 127 : (q < -128 ? -128 : q);
+        if (q != (int)C(m, n)) ok = false; }
+    report("int8 dequant+bias+quant -> int8", M, K, N, ok);
+}
+
+static void matvec() {
+    const int shapes[][2] = {{901, 80}, {901, 96}, {256, 128}, {64, 160}};
+    for (auto& s : shapes) {
+        int M = s[0], K = s[1];
+        tensor2D<bfloat16> A(M, K), b(1, K);
+        std::vector<float> c(M), c2(M), c0(M);
+        for (int m = 0; m < M; m++) { double t = 0; for (int k = 0; k < K; k++) t += (double)(float)A(m, k) * (double)(float)b(0, k); c0[m] = (float)t; }
+        amx_kernel::MatmulVector<bfloat16, bfloat16> mv;
+        mv(A, &b(0, 0), c.data());
+        amx_kernel::GemAvB g;
+        g(A, &b(0, 0), c2.data());
+        report("MatmulVector / GemAvB", M, K, 1, c == c0 && c2 == c0);
+    }
+}
+
+static void mlp() {
+    int M = 32, K = 256, N = 512;
+    tensor2D<bfloat16> x(M, K), gate(N, K), up(N, K), down(K, N), out(M, K);
+    AMX_MLP::MLP m;
+    m.setup(&gate(0, 0), &up(0, 0), &down(0, 0), K, N);
+    m.run(reinterpret_cast<uint8_t*>(&x(0, 0)), x.stride, M, &out(0, 0), out.stride);
+    std::vector<float> act((size_t)M * N);
+    for (int i = 0; i < M; i++) for (int n = 0; n < N; n++) {
+        float g = 0, u = 0;
+        for (int k = 0; k < K; k++) { g += (float)x(i, k) * (float)gate(n, k); u += (float)x(i, k) * (float)up(n, k); }
+        act[(size_t)i * N + n] = (float)bfloat16(g / (1.0f + std::exp(-g)) * u); }
+    double max_ref = 0, max_err = 0;
+    for (int i = 0; i < M; i++) for (int j = 0; j < K; j++) {
+        double s = 0; for (int n = 0; n < N; n++) s += (double)act[(size_t)i * N + n] * (double)(float)down(j, n);
+        max_ref = std::fmax(max_ref, std::fabs(s)); max_err = std::fmax(max_err, std::fabs(s - (double)(float)out(i, j))); }
+    report("fused MLP (err/max <= 1e-2)", M, K, N, max_err <= 1e-2 * max_ref);
+}
+
+static void errors() {
+    tensor2D<bfloat16> A(4, 64), B(32, 64);   // K mismatch
+    tensor2D<float> C(4, 64);
+    amx_kernel::Matmul<bfloat16, bfloat16> fc(true, false);
+    bool threw = false;
+    try { fc(A, B, PP::BiasGeluStore<float, PP::NONE>(C)); } catch (const std::runtime_error&) { threw = true; }
+    report("shape mismatch throws", 4, 64, 64, threw);
+}
+
+int main() {
+    std::srand(0);
+    all_shapes<int8_t, amx_kernel::Matmul<int8_t, int8_t>, PP::NONE>("int8 NONE");
+    all_shapes<bfloat16, amx_kernel::Matmul<bfloat16, bfloat16>, PP::NONE>("bf16 NONE");
+    all_shapes<bfloat16, amx_kernel::Matmul<bfloat16, int8_t, float>, PP::DEQUANT>("bf16 x int8-compressed DEQUANT");
+    column_split();
+    bias_gelu();
+    quant_out();
+    matvec();
+    mlp();
+    errors();
+    std::printf("%s: %d failure(s)\n", g_fail ? "FAIL" : "PASS", g_fail);
+    return g_fail ? 1 : 0;
+}
