@@ -339,6 +339,10 @@ def run_ours(args, w, M, name):
                           "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                        "frac": gbs / peaks["hbm_gbs"], "peak_source": peaks["source"]}}
 
+    # ---- the other single-GPU configurations of the reference's list, as extra keys (not the headline) ----
+    if world == 1 and "configs" in args.legs:
+        line["other_configs"] = other_configs(torch, capi, dev, peaks)
+
     # ---- CPU baseline beside it (rank 0, 1 GPU only) ----
     if rank == 0 and world == 1 and "cpu" in args.legs:
         try:
@@ -355,6 +359,89 @@ def run_ours(args, w, M, name):
         dist.destroy_process_group()
 
 
+def other_configs(torch, capi, dev, peaks):
+    """Single bf16 Linear (M=256, +bias, fp32 out), int8-weight decode GEMV (K=4096, N in {4096, 11008}, M in
+    {1, 4, 16}), int8 GEMM 2048x4096x4096 with quantised post-ops.  Each case rotates over enough independently packed
+    weight sets to exceed L2 several times and is timed as one CUDA graph (kernels of a few microseconds)."""
+    out = {}
+    side = torch.cuda.Stream()
+    g = torch.Generator(device=dev); g.manual_seed(1002)
+
+    def timed_graph(launch_all, n_launch, reps=5):
+        with torch.cuda.stream(side):
+            s = side.cuda_stream
+            launch_all(s); side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                launch_all(torch.cuda.current_stream().cuda_stream)
+            graph.replay(); torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                graph.replay()
+            e1.record(); torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e-3 / reps / n_launch
+
+    # config 1: A[256,4096] x B[4096,4096] + bias -> fp32
+    M, K, N = 256, 4096, 4096
+    A = (torch.rand((M, K), generator=g, device=dev) * 2 - 1).to(torch.bfloat16)
+    bias = torch.randn(N, generator=g, device=dev)
+    C = torch.empty((M, N), dtype=torch.float32, device=dev)
+    ws = []
+    for _ in range(16):
+        B = (torch.rand((K, N), generator=g, device=dev) * 2 - 1).to(torch.bfloat16)
+        ws.append(capi.Weight(B.data_ptr(), capi.BF16, K, N, N * 2, False)); del B
+    ep = capi.make_epilogue(C.data_ptr(), N * 4, capi.F32, capi.STEP_BIAS, bias.data_ptr())
+    t = timed_graph(lambda s: [w.matmul(A.data_ptr(), capi.BF16, M, K, K * 2, ep, stream=s) for w in ws], len(ws))
+    nbytes = M * K * 2 + K * N * 2 + M * N * 4 + N * 4
+    out["bf16_linear_256x4096x4096_bias_f32"] = {"us": t * 1e6, "tflops": 2.0 * M * K * N / t / 1e12,
+                                                   "gbs": nbytes / t / 1e9, "hbm_frac": nbytes / t / 1e9 / peaks["hbm_gbs"],
+                                                   "weight_sets": len(ws)}
+    del ws
+    # config 3: int8-weight decode GEMV
+    K = 4096
+    for N in (4096, 11008):
+        nset = int(600e6 / (K * N)) + 1
+        ws, keep = [], []
+        for _ in range(nset):
+            B = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev, generator=g)
+            sc = torch.rand(N, generator=g, device=dev) * 0.019 + 0.001
+            ws.append(capi.Weight(B.data_ptr(), capi.S8, K, N, K, True, capi.PACK_INT8_CHANNEL, sc.data_ptr())); del B
+        for M in (1, 4, 16):
+            x = torch.randn((M, K), generator=g, device=dev).to(torch.bfloat16)
+            C = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+            ep = capi.make_epilogue(C.data_ptr(), N * 2, capi.BF16, capi.STEP_DEQUANT)
+            t = timed_graph(lambda s: [w.matmul(x.data_ptr(), capi.BF16, M, K, K * 2, ep, stream=s) for w in ws], nset)
+            nbytes = K * N + N * 4 + M * (K + N) * 2
+            out["int8w_gemv_M%d_4096x%d" % (M, N)] = {"us": t * 1e6, "gbs": nbytes / t / 1e9,
+                                                      "hbm_frac": nbytes / t / 1e9 / peaks["hbm_gbs"], "weight_sets": nset}
+        del ws
+    # config 4: int8 x int8 GEMM with quantised post-ops
+    M, K, N = 2048, 4096, 4096
+    A = torch.randint(-128, 128, (M, K), dtype=torch.int8, device=dev, generator=g)
+    ws = []
+    for _ in range(8):
+        B = torch.randint(-128, 128, (K, N), dtype=torch.int8, device=dev, generator=g)
+        ws.append(capi.Weight(B.data_ptr(), capi.S8, K, N, N, False)); del B
+    sB = torch.rand(N, generator=g, device=dev) * 0.049 + 0.001
+    bias = torch.randn(N, generator=g, device=dev)
+    C32 = torch.empty((M, N), dtype=torch.int32, device=dev)
+    Cf = torch.empty((M, N), dtype=torch.float32, device=dev)
+    C8 = torch.empty((M, N), dtype=torch.int8, device=dev)
+    cases = {
+        "raw_int32": capi.make_epilogue(C32.data_ptr(), N * 4, capi.S32),
+        "dequant_bias_f32": capi.make_epilogue(Cf.data_ptr(), N * 4, capi.F32, capi.STEP_DEQUANT | capi.STEP_BIAS,
+                                               bias.data_ptr(), 0.02, sB.data_ptr()),
+        "dequant_bias_requant_s8": capi.make_epilogue(C8.data_ptr(), N, capi.S8,
+                                                      capi.STEP_DEQUANT | capi.STEP_BIAS | capi.STEP_QUANT,
+                                                      bias.data_ptr(), 0.02, sB.data_ptr(), 0.05),
+    }
+    for name, ep in cases.items():
+        t = timed_graph(lambda s: [w.matmul(A.data_ptr(), capi.S8, M, K, K, ep, stream=s) for w in ws], len(ws))
+        out["int8_gemm_2048x4096x4096_" + name] = {"us": t * 1e6, "tops": 2.0 * M * K * N / t / 1e12}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -365,8 +452,8 @@ def main():
     ap.add_argument("--M", type=int, default=None)
     ap.add_argument("--chunk-rows", type=int, default=1024)
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--legs", default="kernel,e2e,decode,cpu",
-                    help="optional legs after the main timed loop (comma list of kernel,e2e,decode,cpu; '' = none)")
+    ap.add_argument("--legs", default="kernel,e2e,decode,configs,cpu",
+                    help="optional legs after the main timed loop (comma list of kernel,e2e,decode,configs,cpu; '' = none)")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1:

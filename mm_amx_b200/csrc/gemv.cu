@@ -35,6 +35,7 @@ constexpr int ROWS_PER_CTA = WARPS * ROWS_PER_WARP;  // 128
 constexpr int KB_BYTES = 64;                          // one K block = 64 bytes of a weight row
 constexpr int KB_PER_ITER = 2;                        // K blocks per pipeline stage
 constexpr int CHUNK_K = 1024;                         // activation elements staged per chunk
+constexpr int PF_DIST = 12;                           // pipeline stages prefetched into L2 ahead of the register stages
 
 struct GemvParams {
     const unsigned char* W;  // packed weights
@@ -198,15 +199,34 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemv_kernel(const GemvParams p)
         }
     };
 
+    // L2 prefetch of the rows of this warp, one row per lane, one pipeline stage (128 bytes per row) per call
+    const unsigned char* pf_row;
+    {
+        int r = warp_row0 + lane;
+        r = r < p.N_pad ? r : p.N_pad - 1;
+        pf_row = p.W + (long long)r * p.ldw;
+    }
+    auto prefetch_l2 = [&](int it) {
+        if (it < it_end && (it + 1) * KB_PER_ITER <= p.n_kb)
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pf_row + (long long)it * KB_PER_ITER * KB_BYTES),
+                         "n"(KB_PER_ITER * KB_BYTES)
+                         : "memory");
+    };
+
     // The weights do not depend on the kernel that precedes this one in the stream, the activations may: start the
-    // weight stream, let the next kernel in the stream begin its own, then wait for the predecessor's results.
+    // weight stream (two stages into registers, PF_DIST more into L2), let the next kernel in the stream begin its
+    // own, then wait for the predecessor's results.
     issue(0, it_begin);
     issue(1, it_begin + 1);
+#pragma unroll 1
+    for (int d = 2; d < 2 + PF_DIST; d++) prefetch_l2(it_begin + d);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int it = it_begin; it < it_end; it += 2) {
         const int it_in_chunk = (it - it_begin) % ITERS_PER_CHUNK;   // even: ITERS_PER_CHUNK is even
         if (it_in_chunk == 0) stage_x(it);
+        prefetch_l2(it + 2 + PF_DIST);
+        prefetch_l2(it + 3 + PF_DIST);
         multiply(0, it_in_chunk);
         issue(0, it + 2);
         if (it + 1 < it_end) multiply(1, it_in_chunk + 1);
