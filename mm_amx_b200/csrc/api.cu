@@ -281,7 +281,7 @@ int b200fc_weight_pack(const void* B, int dtypeB, int K, int N, int64_t ldb, int
                 w.compressed = true;
                 w.deq_scale = mx / 127;  // dequant_scale_B = max / 127 (kernels_amx.hpp:1373)
             } else {
-                rc = launch_pack(src.p, dtypeB, K, N, src.ld, transposeB, w, s);
+                rc = launch_pack(src.p, dtypeB, K, N, src.ld, transposeB, w, pack_mode == B200FC_PACK_INT8_CHANNEL, s);
                 if (!rc && pack_mode == B200FC_PACK_INT8_CHANNEL) {
                     w.compressed = true;
                     w.deq_scale = 1.0f;
@@ -323,9 +323,21 @@ int b200fc_weight_unpack(const b200fc_weight_t* h, void* dst, int64_t ld_bytes, 
     if (!h || !dst) { set_error("weight_unpack: null pointer"); return B200FC_ERR_INVALID; }
     const Weight& w = h->w;
     const int es = elem_size(w.dtype);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (w.compressed) {  // stored offset-binary: hand back two's complement
+        void* tmp = nullptr;
+        B200FC_CUDA(cudaMalloc(&tmp, (size_t)w.N * w.K));
+        int rc = launch_flip_copy2d(w.data, w.K_pad, tmp, w.K, w.N, w.K, s);
+        cudaError_t e = rc ? cudaSuccess : cudaMemcpy2DAsync(dst, (size_t)ld_bytes, tmp, (size_t)w.K, (size_t)w.K, (size_t)w.N, cudaMemcpyDefault, s);
+        cudaStreamSynchronize(s);
+        cudaFree(tmp);
+        if (rc) return rc;
+        B200FC_CUDA(e);
+        return B200FC_OK;
+    }
     B200FC_CUDA(cudaMemcpy2DAsync(dst, (size_t)ld_bytes, w.data, (size_t)w.K_pad * es, (size_t)w.K * es, (size_t)w.N,
-                                  cudaMemcpyDefault, (cudaStream_t)stream));
-    B200FC_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+                                  cudaMemcpyDefault, s));
+    B200FC_CUDA(cudaStreamSynchronize(s));
     return B200FC_OK;
 }
 
@@ -421,7 +433,7 @@ int b200fc_mlp_create(const void* gate, const void* up, const void* down, int K,
         if (!rc) rc = alloc_weight(m.gate_up, K, 2 * Ns, B200FC_BF16);
         if (!rc) rc = alloc_weight(m.down, Ns, K, B200FC_BF16);
         if (!rc) rc = launch_pack_gate_up(sg.p, su.p, sg.ld, K, Ns, m.gate_up, s);
-        if (!rc) rc = launch_pack(sd.p, B200FC_BF16, Ns, K, sd.ld, 1, m.down, s);
+        if (!rc) rc = launch_pack(sd.p, B200FC_BF16, Ns, K, sd.ld, 1, m.down, false, s);
         if (!rc && cudaStreamSynchronize(s) != cudaSuccess) { rc = cuda_fail(cudaGetLastError(), "mlp_create sync"); }
     }
     if (rc) { free_weight(&m.gate_up); free_weight(&m.down); delete h; return rc; }

@@ -20,7 +20,7 @@ struct Weight {
     int K = 0, N = 0;
     int K_pad = 0, N_pad = 0;
     int dtype = B200FC_BF16;        // stored element type: BF16, S8, U8
-    bool compressed = false;        // int8 weights used with bf16 activations
+    bool compressed = false;        // int8 weights used with bf16 activations; stored offset-binary (value + 128)
     float deq_scale = 1.0f;         // per-tensor dequant scale of compressed weights
     void* data = nullptr;           // [N_pad, K_pad]
     float* scale_per_oc = nullptr;  // optional [N_pad] per-output-channel dequant scales
@@ -76,7 +76,9 @@ int matmul_device(const Weight& w, Weight* w_mut, const void* A, int dtypeA, int
 
 // ---- launchers -------------------------------------------------------------------------------------------------
 // pack.cu
-int launch_pack(const void* B_dev, int dtypeB, int K, int N, int64_t ldb, int transposeB, Weight& w, cudaStream_t s);
+int launch_pack(const void* B_dev, int dtypeB, int K, int N, int64_t ldb, int transposeB, Weight& w, bool offset_binary,
+                cudaStream_t s);
+int launch_flip_copy2d(const void* src, int64_t lds, void* dst, int64_t ldd, int rows, int cols, cudaStream_t s);
 int launch_pack_gate_up(const void* gate, const void* up, int64_t ld_bytes, int K, int rows, Weight& w, cudaStream_t s);
 int launch_quant_pack(const void* B_dev, int K, int N, int64_t ldb, int transposeB, Weight& w, float* absmax_dev,
                       cudaStream_t s);

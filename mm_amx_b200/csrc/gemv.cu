@@ -13,14 +13,18 @@
 //   ahead of their use and two stages stay in flight, so a warp always has 8 KB outstanding.
 //   The loaded registers ARE the A fragments of mma.sync.m16n8k16 (weights as the 16-row operand, the <= 16
 //   activation rows as the 8-column operand): K is permuted identically for both operands, which is free because
-//   a dot product does not care about the order of its terms per MMA slot.  int8 weights are widened to bf16 in
-//   registers (exact) right before the MMA — the "dequantise next to the consumer" idea of the reference's ping-pong
-//   buffer, without the buffer.  A SIMT dot product cannot keep up with HBM3e at M = 16 (16 FMAs per weight byte), the
+//   a dot product does not care about the order of its terms per MMA slot.  Compressed (int8) weights are widened in
+//   registers right before the MMA — the "dequantise next to the consumer" idea of the reference's ping-pong
+//   buffer, without the buffer.  They are stored offset-binary (v + 128) so that one byte permute builds the fp16
+//   number 1024 + v + 128 and one subtraction leaves v: one instruction per weight.  fp16 (not bf16) because only
+//   its 10-bit mantissa holds all 8 bits; the activations are therefore converted to fp16 per staged chunk, after
+//   an exact power-of-two scaling per row that keeps them inside the fp16 range.  A SIMT dot product cannot keep up with HBM3e at M = 16 (16 FMAs per weight byte), the
 //   tensor-core path can; at M = 1 the seven unused columns cost nothing.
 //   Activations are staged in shared memory in chunks of 1024 K elements (padded rows, conflict-free 16-byte reads).
 //   Split-K: S CTAs of a thread-block cluster share a row range and split K; partial sums meet in distributed shared
 //   memory and are added in rank order (deterministic), then the post-ops run and C is stored.
 #include <cooperative_groups.h>
+#include <cuda_fp16.h>
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -35,7 +39,6 @@ constexpr int ROWS_PER_CTA = WARPS * ROWS_PER_WARP;  // 128
 constexpr int KB_BYTES = 64;                          // one K block = 64 bytes of a weight row
 constexpr int KB_PER_ITER = 2;                        // K blocks per pipeline stage
 constexpr int CHUNK_K = 1024;                         // activation elements staged per chunk
-constexpr int PF_DIST = 12;                           // pipeline stages prefetched into L2 ahead of the register stages
 
 struct GemvParams {
     const unsigned char* W;  // packed weights
@@ -67,12 +70,21 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// two int8 (bytes `sel` of w) -> bf16x2, exact.  0x4300 | (b & 0x7f) is the bf16 128 + (b & 0x7f); subtracting
-// 128 (sign clear) or 256 (sign set: 0x4300 | 0x80 = 0x4380 = 256.0) gives the two's-complement value.
-__device__ __forceinline__ unsigned s8x2_to_bf16x2(unsigned w, unsigned sel) {
-    unsigned p = __byte_perm(w, 0x43434343u, sel);
-    unsigned hi = p & 0x437f437fu, lo = p & 0x43804380u;
-    __nv_bfloat162 r = __hsub2(*(__nv_bfloat162*)&hi, *(__nv_bfloat162*)&lo);
+__device__ __forceinline__ void mma_f16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                        unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Two compressed weights (bytes `sel` of w, stored offset-binary: u = v + 128) -> f16x2 holding v exactly, in two
+// instructions: 0x6400 | u is the fp16 number 1024 + u (u fits the 10-bit mantissa), minus 1152 leaves v.
+__device__ __forceinline__ unsigned u8x2_to_f16x2(unsigned w, unsigned sel) {
+    unsigned p = __byte_perm(w, 0x64646464u, sel);
+    const __half2 off = __floats2half2_rn(1152.0f, 1152.0f);
+    __half2 r = __hsub2(*(__half2*)&p, off);
     return *(unsigned*)&r;
 }
 
@@ -120,6 +132,9 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemv_kernel(const GemvParams p)
             for (int i = 0; i < 4; i++) acc[rb][nt][i] = 0.0f;
 
     const bool x_vec = (((uintptr_t)p.X & 15) == 0) && ((p.ldx & 15) == 0);
+    int cur_e[NT][2];  // compressed weights: power-of-two scale of the staged activations, per token of this thread
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) cur_e[nt][0] = cur_e[nt][1] = 0;
 
     // One pipeline stage = KB_PER_ITER K blocks of the warp's four rows (8 x 16-byte loads per thread).  Two stages
     // are kept in flight: the loads of stage i+1 are issued before stage i is multiplied.
@@ -136,30 +151,98 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemv_kernel(const GemvParams p)
                     wbuf[buf][rb][h][j] = in ? ld_stream(wrow[rb][h] + (long long)(kb0 + j) * KB_BYTES) : make_uint4(0, 0, 0, 0);
         }
     };
-    auto stage_x = [&](int it) {
-        // stage the activation chunk that starts at iteration `it`
-        const int chunk_k0 = it * KB_PER_ITER * KB_ELEMS;
-        __syncthreads();  // everyone is done with the previous chunk
-        const int k_need = it_end * KB_PER_ITER * KB_ELEMS;  // nothing beyond this split's K range is read
-        for (int u = threadIdx.x; u < MP * (CHUNK_K / 8); u += blockDim.x) {
-            const int row = u / (CHUNK_K / 8), k = chunk_k0 + (u % (CHUNK_K / 8)) * 8;
-            if (k >= k_need) continue;
-            uint4 v = make_uint4(0, 0, 0, 0);  // zero beyond M rows / K columns: padded weights are zero there
-            if (row < p.M && k < p.K) {
-                const unsigned char* src = p.X + (long long)row * p.ldx + (long long)k * 2;
-                if (x_vec && k + 8 <= p.K) {
-                    v = *(const uint4*)src;
-                } else {
-                    unsigned short e[8];
+    // one 16-byte unit (8 bf16) of activation row `row` at K element k; zero beyond M rows / K columns (the padded
+    // weights are zero there, the activations must not be garbage)
+    auto load_x_unit = [&](int row, int k) -> uint4 {
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < p.M && k < p.K) {
+            const unsigned char* src = p.X + (long long)row * p.ldx + (long long)k * 2;
+            if (x_vec && k + 8 <= p.K) {
+                v = *(const uint4*)src;
+            } else {
+                unsigned short e[8];
 #pragma unroll
-                    for (int q = 0; q < 8; q++) e[q] = (k + q < p.K) ? ((const unsigned short*)src)[q] : (unsigned short)0;
-                    v.x = e[0] | ((unsigned)e[1] << 16); v.y = e[2] | ((unsigned)e[3] << 16);
-                    v.z = e[4] | ((unsigned)e[5] << 16); v.w = e[6] | ((unsigned)e[7] << 16);
+                for (int q = 0; q < 8; q++) e[q] = (k + q < p.K) ? ((const unsigned short*)src)[q] : (unsigned short)0;
+                v.x = e[0] | ((unsigned)e[1] << 16); v.y = e[2] | ((unsigned)e[3] << 16);
+                v.z = e[4] | ((unsigned)e[5] << 16); v.w = e[6] | ((unsigned)e[7] << 16);
+            }
+        }
+        return v;
+    };
+    // Stages the activation chunk that starts at iteration `it`: CHUNK_K elements of MP rows, one 16-byte unit per
+    // thread and row.  bf16 weights: the bf16 activations are copied as they are.  Compressed weights: the tensor
+    // core multiplies fp16 x fp16 there, so each row of the chunk is scaled by a power of two that puts its largest
+    // magnitude at 2^13 (exact; fp16 keeps the 8-bit significand of bf16) and converted to fp16; the accumulators
+    // carry the scale (cur_e) and are rescaled when it changes.
+    auto stage_x = [&](int it) {
+        const int chunk_k0 = it * KB_PER_ITER * KB_ELEMS;
+        const int k = chunk_k0 + threadIdx.x * 8;
+        const bool need = k < it_end * KB_PER_ITER * KB_ELEMS;  // nothing beyond this split's K range is read
+        __syncthreads();  // everyone is done with the previous chunk
+        if constexpr (W8) {
+            unsigned* smax = (unsigned*)(smem + MP * XROW);       // [MP][WARPS] largest |bits| seen per row and warp
+            int* sexp = (int*)(smem + MP * XROW + MP * WARPS * 4); // [MP] scale exponent of the row
+#pragma unroll 1
+            for (int row = 0; row < MP; row++) {
+                unsigned m = 0;
+                if (need) {
+                    const uint4 v = load_x_unit(row, k);
+                    const unsigned w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int q = 0; q < 4; q++) m = max(m, max(w4[q] & 0x7fffu, (w4[q] >> 16) & 0x7fffu));
+                }
+                m = __reduce_max_sync(0xffffffffu, m);
+                if (lane == 0) smax[row * WARPS + warp] = m;
+            }
+            __syncthreads();
+#pragma unroll 1
+            for (int row = 0; row < MP; row++) {
+                unsigned m = 0;
+#pragma unroll
+                for (int q = 0; q < WARPS; q++) m = max(m, smax[row * WARPS + q]);
+                int field = (int)(m >> 7);                 // biased exponent of the largest magnitude (bf16 layout)
+                field = field < 1 ? 1 : field;
+                int e = field - 127 - 13;
+                e = e < -126 ? -126 : e;
+                if (threadIdx.x == 0) sexp[row] = e;
+                if (need) {
+                    const float sc = __int_as_float((127 - e) << 23);  // 2^-e
+                    const uint4 v = load_x_unit(row, k);
+                    const unsigned w4[4] = {v.x, v.y, v.z, v.w};
+                    unsigned o[4];
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        __half2 h = __floats2half2_rn(__uint_as_float(w4[q] << 16) * sc,
+                                                      __uint_as_float(w4[q] & 0xffff0000u) * sc);
+                        o[q] = *(unsigned*)&h;
+                    }
+                    *(uint4*)(smem + row * XROW + threadIdx.x * 16) = make_uint4(o[0], o[1], o[2], o[3]);
                 }
             }
-            *(uint4*)(smem + row * XROW + (u % (CHUNK_K / 8)) * 16) = v;
+        } else {
+#pragma unroll 1
+            for (int row = 0; row < MP; row++)
+                if (need) *(uint4*)(smem + row * XROW + threadIdx.x * 16) = load_x_unit(row, k);
         }
         __syncthreads();
+        if constexpr (W8) {
+            // bring the running sums to the new chunk's scale: acc holds sum * 2^-cur_e
+            const int* sexp = (const int*)(smem + MP * XROW + MP * WARPS * 4);
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const int e0 = sexp[nt * 8 + 2 * t], e1 = sexp[nt * 8 + 2 * t + 1];
+                if (cur_e[nt][0] != e0 || cur_e[nt][1] != e1) {
+#pragma unroll
+                    for (int rb = 0; rb < 2; rb++) {
+                        acc[rb][nt][0] = scalbnf(acc[rb][nt][0], cur_e[nt][0] - e0);
+                        acc[rb][nt][2] = scalbnf(acc[rb][nt][2], cur_e[nt][0] - e0);
+                        acc[rb][nt][1] = scalbnf(acc[rb][nt][1], cur_e[nt][1] - e1);
+                        acc[rb][nt][3] = scalbnf(acc[rb][nt][3], cur_e[nt][1] - e1);
+                    }
+                    cur_e[nt][0] = e0; cur_e[nt][1] = e1;
+                }
+            }
+        }
     };
     auto multiply = [&](int buf, int it_in_chunk) {
 #pragma unroll
@@ -186,53 +269,49 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemv_kernel(const GemvParams p)
                 for (int q = 0; q < MMA_PER_LOAD; q++) {
                     unsigned a0, a1, a2, a3;
                     if constexpr (W8) {
-                        a0 = s8x2_to_bf16x2(wa[q], 0x4140); a2 = s8x2_to_bf16x2(wa[q], 0x4342);
-                        a1 = s8x2_to_bf16x2(wb[q], 0x4140); a3 = s8x2_to_bf16x2(wb[q], 0x4342);
+                        a0 = u8x2_to_f16x2(wa[q], 0x4140); a2 = u8x2_to_f16x2(wa[q], 0x4342);
+                        a1 = u8x2_to_f16x2(wb[q], 0x4140); a3 = u8x2_to_f16x2(wb[q], 0x4342);
                     } else {
                         a0 = wa[2 * q]; a2 = wa[2 * q + 1];
                         a1 = wb[2 * q]; a3 = wb[2 * q + 1];
                     }
 #pragma unroll
-                    for (int nt = 0; nt < NT; nt++) mma_bf16(acc[rb][nt], a0, a1, a2, a3, xb[nt][2 * q], xb[nt][2 * q + 1]);
+                    for (int nt = 0; nt < NT; nt++) {
+                        if constexpr (W8) mma_f16(acc[rb][nt], a0, a1, a2, a3, xb[nt][2 * q], xb[nt][2 * q + 1]);
+                        else mma_bf16(acc[rb][nt], a0, a1, a2, a3, xb[nt][2 * q], xb[nt][2 * q + 1]);
+                    }
                 }
             }
         }
     };
 
-    // L2 prefetch of the rows of this warp, one row per lane, one pipeline stage (128 bytes per row) per call
-    const unsigned char* pf_row;
-    {
-        int r = warp_row0 + lane;
-        r = r < p.N_pad ? r : p.N_pad - 1;
-        pf_row = p.W + (long long)r * p.ldw;
-    }
-    auto prefetch_l2 = [&](int it) {
-        if (it < it_end && (it + 1) * KB_PER_ITER <= p.n_kb)
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pf_row + (long long)it * KB_PER_ITER * KB_BYTES),
-                         "n"(KB_PER_ITER * KB_BYTES)
-                         : "memory");
-    };
-
     // The weights do not depend on the kernel that precedes this one in the stream, the activations may: start the
-    // weight stream (two stages into registers, PF_DIST more into L2), let the next kernel in the stream begin its
-    // own, then wait for the predecessor's results.
+    // weight stream (two stages into registers), let the next kernel in the stream begin its own, then wait for
+    // the predecessor's results.
     issue(0, it_begin);
     issue(1, it_begin + 1);
-#pragma unroll 1
-    for (int d = 2; d < 2 + PF_DIST; d++) prefetch_l2(it_begin + d);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int it = it_begin; it < it_end; it += 2) {
         const int it_in_chunk = (it - it_begin) % ITERS_PER_CHUNK;   // even: ITERS_PER_CHUNK is even
         if (it_in_chunk == 0) stage_x(it);
-        prefetch_l2(it + 2 + PF_DIST);
-        prefetch_l2(it + 3 + PF_DIST);
         multiply(0, it_in_chunk);
         issue(0, it + 2);
         if (it + 1 < it_end) multiply(1, it_in_chunk + 1);
         issue(1, it + 3);
     }
 
+    if constexpr (W8) {
+#pragma unroll
+        for (int rb = 0; rb < 2; rb++)
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                acc[rb][nt][0] = scalbnf(acc[rb][nt][0], cur_e[nt][0]);
+                acc[rb][nt][2] = scalbnf(acc[rb][nt][2], cur_e[nt][0]);
+                acc[rb][nt][1] = scalbnf(acc[rb][nt][1], cur_e[nt][1]);
+                acc[rb][nt][3] = scalbnf(acc[rb][nt][3], cur_e[nt][1]);
+            }
+    }
     // ---- partial tile -> shared memory: part[token][row] ----
     __syncthreads();
     float* part = (float*)smem;
@@ -286,7 +365,7 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemv_kernel(const GemvParams p)
 template <bool W8, int NT>
 int launch_variant(const GemvParams& p, int row_ctas, cudaStream_t s) {
     constexpr int XROW = CHUNK_K * 2 + (W8 ? 16 : 64);
-    constexpr int SMEM = 8 * NT * XROW;
+    constexpr int SMEM = 8 * NT * XROW + (W8 ? 8 * NT * (WARPS + 1) * 4 : 0);
     static_assert(SMEM >= ROWS_PER_CTA * 8 * NT * 4, "partial tile must fit the staging buffer");
     static bool attr_done = false;
     if (!attr_done) {

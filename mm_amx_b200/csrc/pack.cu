@@ -36,7 +36,7 @@ __device__ __forceinline__ typename DstT<MODE>::type convert(typename SrcT<MODE>
 // grid: (K_pad / TILE, N_pad / TILE), block: (TILE, 4)
 template <int MODE>
 __global__ void pack_kernel(const void* __restrict__ src_, long long lds, int K, int N, int transposeB,
-                            void* __restrict__ dst_, int K_pad, const float* __restrict__ absmax) {
+                            void* __restrict__ dst_, int K_pad, const float* __restrict__ absmax, int flip) {
     using S = typename SrcT<MODE>::type;
     using D = typename DstT<MODE>::type;
     __shared__ S tile[TILE][TILE + 2];
@@ -46,12 +46,14 @@ __global__ void pack_kernel(const void* __restrict__ src_, long long lds, int K,
     if constexpr (MODE == QUANT8) qscale = __fdiv_rn(127.0f, *absmax);
     const char* src = (const char*)src_;
     D* dst = (D*)dst_;
+    // compressed weights are stored offset-binary (value + 128, padding included): see gemv.cu
+    const D fl = (D)(flip ? 0x80 : 0);
     if (transposeB) {
         for (int r = ty; r < TILE; r += blockDim.y) {
             int n = n0 + r, k = k0 + tx;
             S v = 0;
             if (n < N && k < K) v = *(const S*)(src + (long long)n * lds + (long long)k * sizeof(S));
-            dst[(long long)n * K_pad + k] = convert<MODE>(v, qscale);
+            dst[(long long)n * K_pad + k] = convert<MODE>(v, qscale) ^ fl;
         }
     } else {
         for (int r = ty; r < TILE; r += blockDim.y) {
@@ -63,7 +65,7 @@ __global__ void pack_kernel(const void* __restrict__ src_, long long lds, int K,
         __syncthreads();
         for (int r = ty; r < TILE; r += blockDim.y) {
             int n = n0 + r, k = k0 + tx;
-            dst[(long long)n * K_pad + k] = convert<MODE>(tile[tx][r], qscale);
+            dst[(long long)n * K_pad + k] = convert<MODE>(tile[tx][r], qscale) ^ fl;
         }
     }
 }
@@ -102,8 +104,8 @@ __global__ void absmax_kernel(const void* __restrict__ src_, long long lds, int 
     if ((threadIdx.x & 31) == 0) atomicMax(out_bits, __float_as_uint(m));
 }
 
-// int8 [N_pad, K_pad] -> bf16 [N_pad, dst_K_pad] (exact: |v| <= 128 fits the 8-bit significand of bf16);
-// i8_to_bf16_Kx32, include/kernels_amx.hpp:490-506.  16 elements per thread.
+// compressed weights (offset-binary int8) [N_pad, K_pad] -> bf16 [N_pad, dst_K_pad] (exact: |v| <= 128 fits the
+// 8-bit significand of bf16); i8_to_bf16_Kx32, include/kernels_amx.hpp:490-506.  16 elements per thread.
 __global__ void dequant_bf16_kernel(const signed char* __restrict__ src, int K_pad, long long total16,
                                     unsigned short* __restrict__ dst, int dst_K_pad) {
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -112,10 +114,10 @@ __global__ void dequant_bf16_kernel(const signed char* __restrict__ src, int K_p
     long long n = i / per_row;
     int k = (int)(i % per_row) * 16;
     int4 v = *(const int4*)(src + n * K_pad + k);
-    const signed char* b = (const signed char*)&v;
+    const unsigned char* b = (const unsigned char*)&v;
     __align__(16) unsigned short o[16];
 #pragma unroll
-    for (int j = 0; j < 16; j++) o[j] = f32_to_bf16_bits((float)b[j]);
+    for (int j = 0; j < 16; j++) o[j] = f32_to_bf16_bits((float)((int)b[j] - 128));
     int4* d = (int4*)(dst + n * dst_K_pad + k);
     d[0] = *(int4*)&o[0];
     d[1] = *(int4*)&o[8];
@@ -128,6 +130,13 @@ __global__ void copy2d_kernel(const char* __restrict__ src, long long lds, char*
     for (int r = blockIdx.x; r < rows; r += gridDim.x)
         for (int c = threadIdx.x; c < dst_row_bytes; c += blockDim.x)
             dst[(long long)r * ldd + c] = c < row_bytes ? src[(long long)r * lds + c] : (char)0;
+}
+
+// dst[r, c] = src[r, c] ^ 0x80: offset-binary <-> two's complement, row-wise with independent strides
+__global__ void flip_copy2d_kernel(const unsigned char* __restrict__ src, long long lds, unsigned char* __restrict__ dst,
+                                   long long ldd, int rows, int cols) {
+    for (int r = blockIdx.x; r < rows; r += gridDim.x)
+        for (int c = threadIdx.x; c < cols; c += blockDim.x) dst[(long long)r * ldd + c] = src[(long long)r * lds + c] ^ 0x80;
 }
 
 __global__ void add_round_bf16_kernel(const float* __restrict__ a, const float* __restrict__ b,
@@ -145,12 +154,13 @@ __global__ void fill_kernel(int4* __restrict__ p, long long n16, int v) {
 
 }  // namespace
 
-int launch_pack(const void* B, int dtypeB, int K, int N, int64_t ldb, int transposeB, Weight& w, cudaStream_t s) {
+int launch_pack(const void* B, int dtypeB, int K, int N, int64_t ldb, int transposeB, Weight& w, bool offset_binary,
+                cudaStream_t s) {
     dim3 grid((w.K_pad + TILE - 1) / TILE, w.N_pad / TILE), block(TILE, 4);
     if (dtypeB == B200FC_BF16)
-        pack_kernel<PLAIN16><<<grid, block, 0, s>>>(B, ldb, K, N, transposeB, w.data, w.K_pad, nullptr);
+        pack_kernel<PLAIN16><<<grid, block, 0, s>>>(B, ldb, K, N, transposeB, w.data, w.K_pad, nullptr, 0);
     else
-        pack_kernel<PLAIN8><<<grid, block, 0, s>>>(B, ldb, K, N, transposeB, w.data, w.K_pad, nullptr);
+        pack_kernel<PLAIN8><<<grid, block, 0, s>>>(B, ldb, K, N, transposeB, w.data, w.K_pad, nullptr, offset_binary ? 1 : 0);
     count_launch();
     B200FC_CUDA(cudaGetLastError());
     return B200FC_OK;
@@ -178,7 +188,7 @@ int launch_absmax(const void* B, int rows, int cols, int64_t ldb, float* absmax_
 int launch_quant_pack(const void* B, int K, int N, int64_t ldb, int transposeB, Weight& w, float* absmax_dev,
                       cudaStream_t s) {
     dim3 grid((w.K_pad + TILE - 1) / TILE, w.N_pad / TILE), block(TILE, 4);
-    pack_kernel<QUANT8><<<grid, block, 0, s>>>(B, ldb, K, N, transposeB, w.data, w.K_pad, absmax_dev);
+    pack_kernel<QUANT8><<<grid, block, 0, s>>>(B, ldb, K, N, transposeB, w.data, w.K_pad, absmax_dev, 1);
     count_launch();
     B200FC_CUDA(cudaGetLastError());
     return B200FC_OK;
@@ -199,6 +209,14 @@ int launch_copy2d(const void* src, int64_t lds, void* dst, int64_t ldd, int rows
                   cudaStream_t s) {
     int grid = rows < 2368 ? rows : 2368;
     copy2d_kernel<<<grid, 256, 0, s>>>((const char*)src, lds, (char*)dst, ldd, rows, row_bytes, dst_row_bytes);
+    count_launch();
+    B200FC_CUDA(cudaGetLastError());
+    return B200FC_OK;
+}
+
+int launch_flip_copy2d(const void* src, int64_t lds, void* dst, int64_t ldd, int rows, int cols, cudaStream_t s) {
+    int grid = rows < 2368 ? rows : 2368;
+    flip_copy2d_kernel<<<grid, 256, 0, s>>>((const unsigned char*)src, lds, (unsigned char*)dst, ldd, rows, cols);
     count_launch();
     B200FC_CUDA(cudaGetLastError());
     return B200FC_OK;

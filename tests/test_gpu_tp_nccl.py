@@ -1,0 +1,60 @@
+"""GPU, needs >= 2 devices: the tensor-parallel MLP over NCCL, one process per GPU, against the CPU oracle.
+
+Skipped on a single-GPU box (the sharding arithmetic itself is covered there by
+test_gpu_mlp.py::test_mlp_tensor_parallel_shards and, on CPU, by test_tp_gloo.py)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.gpu
+
+
+def worker(rank, world, port_no, results):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port_no)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from mm_amx_b200 import tp
+    from oracle import port
+    torch.manual_seed(0)
+    K, N = 512, 1024
+    gate = (torch.randn(N, K) * 0.02).to(torch.bfloat16)
+    up = (torch.randn(N, K) * 0.02).to(torch.bfloat16)
+    down = (torch.randn(K, N) * 0.02).to(torch.bfloat16)
+    bits = lambda t: t.contiguous().cpu().view(torch.int16).numpy().view(np.uint16)
+    local = tp.CudaLocalMLP(gate, up, down, rank, world)
+    errs = []
+    for M, pdt, chunk in [(3, torch.float32, 0), (16, torch.bfloat16, 0), (300, torch.float32, 0),
+                          (300, torch.bfloat16, 128)]:
+        x = torch.randn(M, K).to(torch.bfloat16)
+        ref = port.mlp(bits(x), bits(gate), bits(up), bits(down))
+        ref_f = (ref.astype(np.uint32) << 16).view(np.float32)
+        m = tp.TensorParallelMLP(local, K, partial_dtype=pdt, chunk_rows=chunk)
+        out = m.forward(x.cuda())
+        torch.cuda.synchronize()
+        got = (bits(out).astype(np.uint32) << 16).view(np.float32)
+        errs.append(float(np.abs(got - ref_f).max() / np.abs(ref_f).max()))
+    results[rank] = errs
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_tensor_parallel_mlp_nccl():
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    mgr = mp.Manager()
+    results = mgr.dict()
+    port_no = 29700 + (os.getpid() % 2000)
+    mp.spawn(worker, args=(world, port_no, results), nprocs=world, join=True)
+    assert len(results) == world
+    for r in range(world):
+        assert max(results[r]) < 1e-2, results[r]
