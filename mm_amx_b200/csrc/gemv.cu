@@ -20,8 +20,7 @@
 //   its 10-bit mantissa holds all 8 bits; the activations are therefore converted to fp16 per staged chunk, after
 //   an exact power-of-two scaling per row that keeps them inside the fp16 range.  A SIMT dot product cannot keep up with HBM3e at M = 16 (16 FMAs per weight byte), the
 //   tensor-core path can; at M = 1 the seven unused columns cost nothing.
-//   Activations are staged in shared memory in chunks of 1024 K elements (padded rows, conflict-free 16-byte reads),
-//   double buffered: the next chunk is fetched piecewise while the current one is multiplied.
+//   Activations are staged in shared memory in chunks of 1024 K elements (padded rows, conflict-free 16-byte reads).
 //   Split-K: S CTAs of a thread-block cluster share a row range and split K; partial sums meet in distributed shared
 //   memory and are added in rank order (deterministic), then the post-ops run and C is stored.
 #include <cooperative_groups.h>
@@ -97,7 +96,7 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemv_kernel(const GemvParams p)
     constexpr int ITERS_PER_CHUNK = CHUNK_K / (KB_ELEMS * KB_PER_ITER);
     constexpr int MMA_PER_LOAD = W8 ? 4 : 2;
 
-    extern __shared__ __align__(16) unsigned char smem[];   // two activation buffers; later reused for the partial tile
+    extern __shared__ __align__(16) unsigned char smem[];   // MP * XROW bytes; later reused for the partial tile
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -133,10 +132,9 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemv_kernel(const GemvParams p)
             for (int i = 0; i < 4; i++) acc[rb][nt][i] = 0.0f;
 
     const bool x_vec = (((uintptr_t)p.X & 15) == 0) && ((p.ldx & 15) == 0);
-    unsigned char* const xbuf0 = smem;                       // two staging buffers for activation chunks
-    unsigned char* const xbuf1 = smem + MP * XROW;
-    unsigned* const smax = (unsigned*)(smem + 2 * MP * XROW);  // [MP][WARPS], compressed weights only
-    int* const sexp = (int*)(smem + 2 * MP * XROW + MP * WARPS * 4);  // [MP] power-of-two scale per activation row
+    int cur_e[NT][2];  // compressed weights: power-of-two scale of the staged activations, per token of this thread
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) cur_e[nt][0] = cur_e[nt][1] = 0;
 
     // One pipeline stage = KB_PER_ITER K blocks of the warp's four rows (8 x 16-byte loads per thread).  Two stages
     // are kept in flight: the loads of stage i+1 are issued before stage i is multiplied.
@@ -171,24 +169,82 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemv_kernel(const GemvParams p)
         }
         return v;
     };
-    // Writes one staged unit.  bf16 weights: the bf16 activations are copied as they are.  Compressed weights: the
-    // tensor core multiplies fp16 x fp16 there, so the row is scaled by its power of two (sexp) and converted to fp16
-    // (exact: fp16 keeps the 8-bit significand of bf16, the scaling keeps the row inside the fp16 range).
-    auto store_x_unit = [&](unsigned char* buf, int row, uint4 v) {
+    // Stages the activation chunk that starts at iteration `it`: CHUNK_K elements of MP rows, one 16-byte unit per
+    // thread and row.  bf16 weights: the bf16 activations are copied as they are.  Compressed weights: the tensor
+    // core multiplies fp16 x fp16 there, so each row of the chunk is scaled by a power of two that puts its largest
+    // magnitude at 2^13 (exact; fp16 keeps the 8-bit significand of bf16) and converted to fp16; the accumulators
+    // carry the scale (cur_e) and are rescaled when it changes.
+    auto stage_x = [&](int it) {
+        const int chunk_k0 = it * KB_PER_ITER * KB_ELEMS;
+        const int k = chunk_k0 + threadIdx.x * 8;
+        const bool need = k < it_end * KB_PER_ITER * KB_ELEMS;  // nothing beyond this split's K range is read
+        __syncthreads();  // everyone is done with the previous chunk
         if constexpr (W8) {
-            const float sc = __int_as_float((127 - sexp[row]) << 23);  // 2^-e
-            const unsigned w4[4] = {v.x, v.y, v.z, v.w};
-            unsigned o[4];
+            unsigned* smax = (unsigned*)(smem + MP * XROW);       // [MP][WARPS] largest |bits| seen per row and warp
+            int* sexp = (int*)(smem + MP * XROW + MP * WARPS * 4); // [MP] scale exponent of the row
+#pragma unroll 1
+            for (int row = 0; row < MP; row++) {
+                unsigned m = 0;
+                if (need) {
+                    const uint4 v = load_x_unit(row, k);
+                    const unsigned w4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-            for (int q = 0; q < 4; q++) {
-                __half2 h = __floats2half2_rn(__uint_as_float(w4[q] << 16) * sc, __uint_as_float(w4[q] & 0xffff0000u) * sc);
-                o[q] = *(unsigned*)&h;
+                    for (int q = 0; q < 4; q++) m = max(m, max(w4[q] & 0x7fffu, (w4[q] >> 16) & 0x7fffu));
+                }
+                m = __reduce_max_sync(0xffffffffu, m);
+                if (lane == 0) smax[row * WARPS + warp] = m;
             }
-            v = make_uint4(o[0], o[1], o[2], o[3]);
+            __syncthreads();
+#pragma unroll 1
+            for (int row = 0; row < MP; row++) {
+                unsigned m = 0;
+#pragma unroll
+                for (int q = 0; q < WARPS; q++) m = max(m, smax[row * WARPS + q]);
+                int field = (int)(m >> 7);                 // biased exponent of the largest magnitude (bf16 layout)
+                field = field < 1 ? 1 : field;
+                int e = field - 127 - 13;
+                e = e < -126 ? -126 : e;
+                if (threadIdx.x == 0) sexp[row] = e;
+                if (need) {
+                    const float sc = __int_as_float((127 - e) << 23);  // 2^-e
+                    const uint4 v = load_x_unit(row, k);
+                    const unsigned w4[4] = {v.x, v.y, v.z, v.w};
+                    unsigned o[4];
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        __half2 h = __floats2half2_rn(__uint_as_float(w4[q] << 16) * sc,
+                                                      __uint_as_float(w4[q] & 0xffff0000u) * sc);
+                        o[q] = *(unsigned*)&h;
+                    }
+                    *(uint4*)(smem + row * XROW + threadIdx.x * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+            }
+        } else {
+#pragma unroll 1
+            for (int row = 0; row < MP; row++)
+                if (need) *(uint4*)(smem + row * XROW + threadIdx.x * 16) = load_x_unit(row, k);
         }
-        *(uint4*)(buf + row * XROW + threadIdx.x * 16) = v;
+        __syncthreads();
+        if constexpr (W8) {
+            // bring the running sums to the new chunk's scale: acc holds sum * 2^-cur_e
+            const int* sexp = (const int*)(smem + MP * XROW + MP * WARPS * 4);
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const int e0 = sexp[nt * 8 + 2 * t], e1 = sexp[nt * 8 + 2 * t + 1];
+                if (cur_e[nt][0] != e0 || cur_e[nt][1] != e1) {
+#pragma unroll
+                    for (int rb = 0; rb < 2; rb++) {
+                        acc[rb][nt][0] = scalbnf(acc[rb][nt][0], cur_e[nt][0] - e0);
+                        acc[rb][nt][2] = scalbnf(acc[rb][nt][2], cur_e[nt][0] - e0);
+                        acc[rb][nt][1] = scalbnf(acc[rb][nt][1], cur_e[nt][1] - e1);
+                        acc[rb][nt][3] = scalbnf(acc[rb][nt][3], cur_e[nt][1] - e1);
+                    }
+                    cur_e[nt][0] = e0; cur_e[nt][1] = e1;
+                }
+            }
+        }
     };
-    auto multiply = [&](int buf, const unsigned char* xbuf, int it_in_chunk) {
+    auto multiply = [&](int buf, int it_in_chunk) {
 #pragma unroll
         for (int j = 0; j < KB_PER_ITER; j++) {
             // activation fragments of this K block: per row, the bytes matching this thread's weight bytes
@@ -196,7 +252,7 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemv_kernel(const GemvParams p)
             unsigned xb[NT][W8 ? 8 : 4];
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
-                const unsigned char* xs = xbuf + (nt * 8 + g) * XROW + xoff;
+                const unsigned char* xs = smem + (nt * 8 + g) * XROW + xoff;
                 uint4 a = *(const uint4*)xs;
                 xb[nt][0] = a.x; xb[nt][1] = a.y; xb[nt][2] = a.z; xb[nt][3] = a.w;
                 if constexpr (W8) {
@@ -236,95 +292,25 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemv_kernel(const GemvParams p)
     issue(1, it_begin + 1);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-
-    const int k_begin = it_begin * KB_PER_ITER * KB_ELEMS, k_end = it_end * KB_PER_ITER * KB_ELEMS;
-    if constexpr (W8) {
-        // per-row power-of-two scale over this split's K range: largest magnitude -> 2^13
-        for (int row = 0; row < MP; row++) {
-            unsigned m = 0;
-            if (row < p.M)
-                for (int k = k_begin + threadIdx.x * 8; k < k_end && k < p.K; k += blockDim.x * 8) {
-                    const uint4 v = load_x_unit(row, k);
-                    const unsigned w4[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                    for (int q = 0; q < 4; q++) m = max(m, max(w4[q] & 0x7fffu, (w4[q] >> 16) & 0x7fffu));
-                }
-            m = __reduce_max_sync(0xffffffffu, m);
-            if (lane == 0) smax[row * WARPS + warp] = m;
-        }
-        __syncthreads();
-        if (threadIdx.x < MP) {
-            unsigned m = 0;
-#pragma unroll
-            for (int q = 0; q < WARPS; q++) m = max(m, smax[threadIdx.x * WARPS + q]);
-            int field = (int)(m >> 7);  // biased exponent of the largest magnitude (bf16 layout)
-            field = field < 1 ? 1 : field;
-            int e = field - 127 - 13;
-            sexp[threadIdx.x] = e < -126 ? -126 : e;
-        }
-        __syncthreads();
-    }
-    // first chunk: staged by everybody, synchronously
-    for (int row = 0; row < MP; row++) {
-        const int k = k_begin + threadIdx.x * 8;
-        if (k < k_end) store_x_unit(xbuf0, row, load_x_unit(row, k));
-    }
-    __syncthreads();
-
-    // Main loop.  While chunk c is multiplied, every thread stages its share of chunk c + 1 into the other buffer:
-    // RPI rows per pipeline stage, loaded one stage ahead of their conversion / store, so the L2 latency of the
-    // activations never stalls the weight stream.
-    constexpr int RPI = (MP + ITERS_PER_CHUNK - 1) / ITERS_PER_CHUNK;
-    uint4 xpre[RPI];
-    int pre_row = -1;          // first row held in xpre, -1 = nothing pending
-    int next_row = 0;          // next row of the following chunk to fetch
-    int chunk_k0 = k_begin;    // first K element of the current chunk
-    const unsigned char* xcur = xbuf0;
-    unsigned char* xnext = xbuf1;
-    auto stage_step = [&]() {
-        if (pre_row >= 0) {
-#pragma unroll
-            for (int r = 0; r < RPI; r++)
-                if (pre_row + r < MP) store_x_unit(xnext, pre_row + r, xpre[r]);
-            pre_row = -1;
-        }
-        const int k = chunk_k0 + CHUNK_K + threadIdx.x * 8;
-        if (next_row < MP && chunk_k0 + CHUNK_K < k_end) {
-#pragma unroll
-            for (int r = 0; r < RPI; r++) xpre[r] = (next_row + r < MP && k < k_end) ? load_x_unit(next_row + r, k) : make_uint4(0, 0, 0, 0);
-            pre_row = next_row;
-            next_row += RPI;
-        }
-    };
     for (int it = it_begin; it < it_end; it += 2) {
         const int it_in_chunk = (it - it_begin) % ITERS_PER_CHUNK;   // even: ITERS_PER_CHUNK is even
-        if (it_in_chunk == 0 && it != it_begin) {
-            stage_step();      // flush what is still pending for the chunk that starts now
-            __syncthreads();   // the next buffer is complete, nobody reads the previous one any more
-            const unsigned char* tmp = xcur; xcur = xnext; xnext = (unsigned char*)tmp;
-            chunk_k0 += CHUNK_K;
-            next_row = 0;
-        }
-        stage_step();
-        multiply(0, xcur, it_in_chunk);
+        if (it_in_chunk == 0) stage_x(it);
+        multiply(0, it_in_chunk);
         issue(0, it + 2);
-        stage_step();
-        if (it + 1 < it_end) multiply(1, xcur, it_in_chunk + 1);
+        if (it + 1 < it_end) multiply(1, it_in_chunk + 1);
         issue(1, it + 3);
     }
 
-    if constexpr (W8) {  // undo the power-of-two scaling of the activations
+    if constexpr (W8) {
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++) {
-            const int e0 = sexp[nt * 8 + 2 * t], e1 = sexp[nt * 8 + 2 * t + 1];
+        for (int rb = 0; rb < 2; rb++)
 #pragma unroll
-            for (int rb = 0; rb < 2; rb++) {
-                acc[rb][nt][0] = scalbnf(acc[rb][nt][0], e0);
-                acc[rb][nt][2] = scalbnf(acc[rb][nt][2], e0);
-                acc[rb][nt][1] = scalbnf(acc[rb][nt][1], e1);
-                acc[rb][nt][3] = scalbnf(acc[rb][nt][3], e1);
+            for (int nt = 0; nt < NT; nt++) {
+                acc[rb][nt][0] = scalbnf(acc[rb][nt][0], cur_e[nt][0]);
+                acc[rb][nt][2] = scalbnf(acc[rb][nt][2], cur_e[nt][0]);
+                acc[rb][nt][1] = scalbnf(acc[rb][nt][1], cur_e[nt][1]);
+                acc[rb][nt][3] = scalbnf(acc[rb][nt][3], cur_e[nt][1]);
             }
-        }
     }
     // ---- partial tile -> shared memory: part[token][row] ----
     __syncthreads();
@@ -379,7 +365,7 @@ __global__ void __launch_bounds__(WARPS * 32, 4) gemv_kernel(const GemvParams p)
 template <bool W8, int NT>
 int launch_variant(const GemvParams& p, int row_ctas, cudaStream_t s) {
     constexpr int XROW = CHUNK_K * 2 + (W8 ? 16 : 64);
-    constexpr int SMEM = 2 * 8 * NT * XROW + 8 * NT * (WARPS + 1) * 4;
+    constexpr int SMEM = 8 * NT * XROW + (W8 ? 8 * NT * (WARPS + 1) * 4 : 0);
     static_assert(SMEM >= ROWS_PER_CTA * 8 * NT * 4, "partial tile must fit the staging buffer");
     static bool attr_done = false;
     if (!attr_done) {
