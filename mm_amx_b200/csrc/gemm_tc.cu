@@ -18,6 +18,7 @@
 // Every mbarrier wait is bounded: when one runs out, the CTA raises an abort flag, all roles fall through to the
 // common exit (TMEM is freed there) and the kernel stores an error code for the host.
 #include <cuda.h>
+#include <cstdlib>
 #include "common.cuh"
 
 namespace b200fc {
@@ -397,6 +398,224 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
+// ---- the 2-CTA kernel ---------------------------------------------------------------------------------------------
+// A pair of CTAs (a cluster of two, on neighbouring SMs) computes one 256 (M) x BN tile with cta_group::2 MMAs.
+// Each CTA stages its own 128 rows of A and only HALF of the weight rows of the tile (BN / 2), so a stage is
+// 16 KB + BN/2 * 128 B instead of 16 KB + BN * 128 B: a third fewer operand bytes cross L2 -> shared memory per flop,
+// which is what bounds the 1-CTA kernel.  The leader CTA (cluster rank 0) issues the MMAs for both; its TMEM and
+// the peer's each hold the 128 x BN accumulator rows of their own half of M.
+//   full[s]       lives in the leader: one arrive.expect_tx by the leader's producer for the bytes of BOTH CTAs;
+//                 the peer's TMA loads complete_tx on the leader's barrier (cta_group::2 loads, no multicast).
+//   empty[s]      one per CTA, released by the leader's tcgen05.commit multicast to both CTAs.
+//   acc_full[b]   one per CTA, same multicast commit after the last K slab.
+//   acc_empty[b]  lives in the leader, 8 arrivals: the four epilogue warps of each CTA (the peer's arrive remotely).
+// Cluster barriers bracket the kernel so that neither CTA touches the other's barriers before they exist or
+// after it has exited.  All mbarrier waits are bounded as in the 1-CTA kernel.
+template <int BN> struct Cfg2 {
+    static constexpr int STAGES = BN == 256 ? 6 : 8;
+    static constexpr int A_BYTES = BM * SLAB_BYTES;
+    static constexpr int B_BYTES = (BN / 2) * SLAB_BYTES;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int TMEM_COLS = 2 * BN;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+__device__ __forceinline__ unsigned cluster_ctarank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ unsigned mapa_rank(unsigned addr, unsigned rank) {
+    unsigned r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_remote(unsigned cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(unsigned dst, const CUtensorMap* map, unsigned leader_bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(leader_bar), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((unsigned short)3)
+                 : "memory");
+}
+template <bool I8>
+__device__ __forceinline__ void tc_mma_pair(unsigned d_tmem, unsigned long long adesc, unsigned long long bdesc,
+                                            unsigned idesc, unsigned accumulate) {
+    if constexpr (I8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+
+template <int BN, bool I8>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                const GemmParams p) {
+    using C = Cfg2<BN>;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned long long* bars = (unsigned long long*)(smem + C::STAGES * C::STAGE_BYTES);
+    const unsigned bar_full = smem_u32(bars);
+    const unsigned bar_empty = smem_u32(bars + C::STAGES);
+    const unsigned bar_acc_full = smem_u32(bars + 2 * C::STAGES);
+    const unsigned bar_acc_empty = smem_u32(bars + 2 * C::STAGES + 2);
+    unsigned* tmem_holder = (unsigned*)(bars + 2 * C::STAGES + 4);
+    volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int num_tiles = p.tiles_m * p.tiles_n;  // tiles of 256 x BN
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < C::STAGES; i++) {
+            mbar_init(bar_full + 8 * i, 1);
+            mbar_init(bar_empty + 8 * i, 1);
+        }
+        for (int i = 0; i < 2; i++) {
+            mbar_init(bar_acc_full + 8 * i, 1);
+            mbar_init(bar_acc_empty + 8 * i, 8);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
+                     "r"((unsigned)C::TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // both CTAs' barriers exist before anyone signals them
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (one per CTA) ----------------
+        if (lane == 0) {
+            int stage = 0;
+            unsigned phase = 0;
+            bool ok = true;
+            const unsigned leader_full = mapa_rank(bar_full, 0);
+            for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+                const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+                const int row_a = tm * (2 * BM) + (int)rank * BM;
+                const int row_w = p.n0 + tn * BN + (int)rank * (BN / 2);
+                for (int ks = 0; ks < p.k_slabs; ks++) {
+                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag)) { ok = false; break; }
+                    if (leader) mbar_expect_tx(bar_full + 8 * stage, 2 * C::STAGE_BYTES);
+                    const unsigned sa = smem_u32(smem + stage * C::STAGE_BYTES);
+                    const int kx = ks * (I8 ? SLAB_BYTES : SLAB_BYTES / 2);
+                    tma_load_2d_pair(sa, &map_a, leader_full + 8 * stage, kx, row_a);
+                    tma_load_2d_pair(sa + C::A_BYTES, &map_w, leader_full + 8 * stage, kx, row_w);
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader CTA only) ----------------
+        if (leader) {
+            int stage = 0;
+            unsigned phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, it++) {
+                const int ab = it & 1;
+                const unsigned acc_phase = (unsigned)(it >> 1) & 1;
+                if (!mbar_wait(bar_acc_empty + 8 * ab, acc_phase ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const unsigned d_tmem = tmem_base + (unsigned)(ab * BN);
+                for (int ks = 0; ks < p.k_slabs; ks++) {
+                    if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    if (lane == 0) {
+                        const unsigned sa = smem_u32(smem + stage * C::STAGE_BYTES);
+                        const unsigned long long adesc = make_smem_desc(sa);
+                        const unsigned long long bdesc = make_smem_desc(sa + C::A_BYTES);
+#pragma unroll
+                        for (int k = 0; k < SLAB_BYTES / MMA_K_BYTES; k++)
+                            tc_mma_pair<I8>(d_tmem, adesc + (unsigned long long)(k * (MMA_K_BYTES >> 4)),
+                                            bdesc + (unsigned long long)(k * (MMA_K_BYTES >> 4)), p.idesc,
+                                            (unsigned)((ks | k) != 0));
+                        tc_commit_pair(bar_empty + 8 * stage);
+                        if (ks == p.k_slabs - 1) tc_commit_pair(bar_acc_full + 8 * ab);
+                    }
+                    __syncwarp();
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else {
+        // ---------------- epilogue warps (both CTAs, own 128 rows) ----------------
+        const int quarter = warp & 3;
+        int it = 0;
+        bool ok = true;
+        const unsigned leader_acc_empty = mapa_rank(bar_acc_empty, 0);
+        for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, it++) {
+            const int ab = it & 1;
+            const unsigned acc_phase = (unsigned)(it >> 1) & 1;
+            const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+            if (!mbar_wait(bar_acc_full + 8 * ab, acc_phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const int m = tm * (2 * BM) + (int)rank * BM + quarter * 32 + lane;
+            const bool row_ok = m < p.M;
+            const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(ab * BN);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c++) {
+                const int n = p.n0 + tn * BN + c * 32;
+                if (n >= p.n1) break;
+                unsigned r[32];
+                tc_ld32(taddr + (unsigned)(c * 32), r);
+                tc_wait_ld();
+                epilogue_chunk(r, m, n, p, row_ok);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(leader_acc_empty + 8 * ab);
+        }
+    }
+
+    // ---------------- common exit ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) {
+            atomicExch(p.status, 2);
+            const unsigned long long t0 = globaltimer();
+            while (globaltimer() - t0 < 200000ull) { }
+        }
+        __syncthreads();
+    }
+    cluster_sync_all();  // the peer may still be signalling this CTA's barriers until here
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)C::TMEM_COLS)
+                     : "memory");
+    }
+}
+
 // ---- host side -----------------------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -432,7 +651,7 @@ int make_map(CUtensorMap* map, const void* base, bool i8, uint64_t k_elems, uint
 
 // tcgen05 instruction descriptor (dense, K-major A and B, M = 128): accumulator format bits [4,6), A format [7,10),
 // B format [10,13), N >> 3 at [17,23), M >> 4 at [24,29).
-unsigned make_idesc(bool i8, bool a_signed, bool b_signed, int bn) {
+unsigned make_idesc(bool i8, bool a_signed, bool b_signed, int bn, int mma_m = BM) {
     unsigned d = 0;
     if (i8) {
         d |= 2u << 4;                       // int32 accumulator
@@ -444,7 +663,7 @@ unsigned make_idesc(bool i8, bool a_signed, bool b_signed, int bn) {
         d |= 1u << 10;
     }
     d |= (unsigned)(bn >> 3) << 17;
-    d |= (unsigned)(BM >> 4) << 24;
+    d |= (unsigned)(mma_m >> 4) << 24;
     return d;
 }
 
@@ -474,6 +693,34 @@ int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& p
     count_launch();
     B200FC_CUDA(cudaGetLastError());
     return B200FC_OK;
+}
+
+template <int BN, bool I8>
+int launch_cfg2(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& p, cudaStream_t s) {
+    using C = Cfg2<BN>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        B200FC_CUDA(cudaFuncSetAttribute(gemm_tc2_kernel<BN, I8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         C::SMEM_BYTES));
+        attr_done = true;
+    }
+    int tiles = p.tiles_m * p.tiles_n;
+    int pairs = num_sms() / 2;
+    if (tiles < pairs) pairs = tiles;
+    gemm_tc2_kernel<BN, I8><<<2 * pairs, NUM_THREADS, C::SMEM_BYTES, s>>>(ma, mw, p);
+    count_launch();
+    B200FC_CUDA(cudaGetLastError());
+    return B200FC_OK;
+}
+
+// 0 = choose by shape, 1 = force the 1-CTA kernel, 2 = force the 2-CTA kernel (B200FC_GEMM_CTAS, for experiments)
+int forced_ctas() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("B200FC_GEMM_CTAS");
+        v = e ? atoi(e) : 0;
+    }
+    return v;
 }
 
 }  // namespace
@@ -517,6 +764,18 @@ int launch_gemm_tc(const void* W_data, int w_dtype, int W_K_pad, int W_N_pad, co
     CUtensorMap ma, mw;
     int rc = make_map(&ma, A, i8, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BM);
     if (rc) return rc;
+    // 2-CTA tiles (256 x 256 per CTA pair) when there are at least two 128-row blocks of M and enough tiles
+    const bool pair_ok = (forced_ctas() == 2) || (forced_ctas() == 0 && M > BM && nspan > 128);
+    if (pair_ok) {
+        const int bn2 = 256;
+        p.tiles_m = (M + 2 * BM - 1) / (2 * BM);
+        p.tiles_n = (nspan + bn2 - 1) / bn2;
+        p.idesc = make_idesc(i8, dtypeA == B200FC_S8, w_dtype == B200FC_S8, bn2, 2 * BM);
+        rc = make_map(&mw, W_data, i8, (uint64_t)W_K_pad, (uint64_t)W_N_pad, (uint64_t)W_K_pad * (i8 ? 1 : 2),
+                      (uint32_t)(bn2 / 2));
+        if (rc) return rc;
+        return i8 ? launch_cfg2<256, true>(ma, mw, p, s) : launch_cfg2<256, false>(ma, mw, p, s);
+    }
     rc = make_map(&mw, W_data, i8, (uint64_t)W_K_pad, (uint64_t)W_N_pad, (uint64_t)W_K_pad * (i8 ? 1 : 2), (uint32_t)bn);
     if (rc) return rc;
     if (bn == 256) return i8 ? launch_cfg<256, true>(ma, mw, p, s) : launch_cfg<256, false>(ma, mw, p, s);
