@@ -445,6 +445,11 @@ int b200fc_mlp_free(b200fc_mlp_t* h) {
     if (!h) return B200FC_OK;
     free_weight(&h->m.gate_up); free_weight(&h->m.down);
     cudaFree(h->m.act); cudaFree(h->m.stage_x); cudaFree(h->m.stage_o);
+    for (int i = 0; i < 3; i++) if (h->m.pipe_streams[i]) cudaStreamDestroy(h->m.pipe_streams[i]);
+    if (h->m.ev_fork) cudaEventDestroy(h->m.ev_fork);
+    if (h->m.ev_join) cudaEventDestroy(h->m.ev_join);
+    for (cudaEvent_t e : h->m.ev_in) cudaEventDestroy(e);
+    for (cudaEvent_t e : h->m.ev_out) cudaEventDestroy(e);
     delete h;
     return B200FC_OK;
 }
@@ -487,10 +492,59 @@ int b200fc_mlp_run_host(b200fc_mlp_t* h, const void* x, int64_t ldx, int M, void
     int rc = grow(&m.stage_x, &m.stage_x_bytes, row * M, s);
     if (!rc) rc = grow(&m.stage_o, &m.stage_o_bytes, row * M, s);
     if (rc) return rc;
-    B200FC_CUDA(cudaMemcpy2DAsync(m.stage_x, row, x, (size_t)ldx, row, (size_t)M, cudaMemcpyHostToDevice, s));
-    rc = mlp_run_device(m, m.stage_x, (int64_t)row, M, m.stage_o, B200FC_BF16, (int64_t)row, s);
+    if (M < 1024) {
+        B200FC_CUDA(cudaMemcpy2DAsync(m.stage_x, row, x, (size_t)ldx, row, (size_t)M, cudaMemcpyHostToDevice, s));
+        rc = mlp_run_device(m, m.stage_x, (int64_t)row, M, m.stage_o, B200FC_BF16, (int64_t)row, s);
+        if (rc) return rc;
+        B200FC_CUDA(cudaMemcpy2DAsync(out, (size_t)ldo, m.stage_o, row, row, (size_t)M, cudaMemcpyDeviceToHost, s));
+        return check_kernel_status(s);
+    }
+    // Large batches: rows are independent, so the batch is cut into chunks of 512 rows that flow through three
+    // streams — host-to-device copy, compute, device-to-host copy — and the PCIe transfers of neighbouring chunks
+    // overlap the tensor-core work (the copy engines are full duplex).
+    const int chunk = 512;
+    const int n_chunks = (M + chunk - 1) / chunk;
+    if (!m.pipe_streams[0]) {
+        for (int i = 0; i < 3; i++) B200FC_CUDA(cudaStreamCreateWithFlags(&m.pipe_streams[i], cudaStreamNonBlocking));
+        B200FC_CUDA(cudaEventCreateWithFlags(&m.ev_fork, cudaEventDisableTiming));
+        B200FC_CUDA(cudaEventCreateWithFlags(&m.ev_join, cudaEventDisableTiming));
+    }
+    while ((int)m.ev_in.size() < n_chunks) {
+        cudaEvent_t a, b;
+        B200FC_CUDA(cudaEventCreateWithFlags(&a, cudaEventDisableTiming));
+        B200FC_CUDA(cudaEventCreateWithFlags(&b, cudaEventDisableTiming));
+        m.ev_in.push_back(a); m.ev_out.push_back(b);
+    }
+    rc = grow(&m.act, &m.act_bytes, (size_t)M * m.Ns * 2, s);
     if (rc) return rc;
-    B200FC_CUDA(cudaMemcpy2DAsync(out, (size_t)ldo, m.stage_o, row, row, (size_t)M, cudaMemcpyDeviceToHost, s));
+    m.act_rows = M;
+    cudaStream_t s_in = m.pipe_streams[0], s_cmp = m.pipe_streams[1], s_out = m.pipe_streams[2];
+    B200FC_CUDA(cudaEventRecord(m.ev_fork, s));
+    for (int i = 0; i < 3; i++) B200FC_CUDA(cudaStreamWaitEvent(m.pipe_streams[i], m.ev_fork, 0));
+    for (int c = 0; c < n_chunks; c++) {
+        const int r0 = c * chunk, rows = (M - r0 < chunk) ? (M - r0) : chunk;
+        char* xs = (char*)m.stage_x + (size_t)r0 * row;
+        char* os = (char*)m.stage_o + (size_t)r0 * row;
+        char* as = (char*)m.act + (size_t)r0 * m.Ns * 2;
+        B200FC_CUDA(cudaMemcpy2DAsync(xs, row, (const char*)x + (size_t)r0 * ldx, (size_t)ldx, row, (size_t)rows,
+                                      cudaMemcpyHostToDevice, s_in));
+        B200FC_CUDA(cudaEventRecord(m.ev_in[c], s_in));
+        B200FC_CUDA(cudaStreamWaitEvent(s_cmp, m.ev_in[c], 0));
+        b200fc_epilogue_t e1 = {};
+        e1.steps = B200FC_STEP_SILU_MUL; e1.out_dtype = B200FC_BF16; e1.C = as; e1.ldc_bytes = (int64_t)m.Ns * 2;
+        rc = matmul_device(m.gate_up, nullptr, xs, B200FC_BF16, rows, m.K, (int64_t)row, 0, 2 * m.Ns, &e1, s_cmp);
+        if (rc) return rc;
+        b200fc_epilogue_t e2 = {};
+        e2.steps = 0; e2.out_dtype = B200FC_BF16; e2.C = os; e2.ldc_bytes = (int64_t)row;
+        rc = matmul_device(m.down, nullptr, as, B200FC_BF16, rows, m.Ns, (int64_t)m.Ns * 2, 0, m.K, &e2, s_cmp);
+        if (rc) return rc;
+        B200FC_CUDA(cudaEventRecord(m.ev_out[c], s_cmp));
+        B200FC_CUDA(cudaStreamWaitEvent(s_out, m.ev_out[c], 0));
+        B200FC_CUDA(cudaMemcpy2DAsync((char*)out + (size_t)r0 * ldo, (size_t)ldo, os, row, row, (size_t)rows,
+                                      cudaMemcpyDeviceToHost, s_out));
+    }
+    B200FC_CUDA(cudaEventRecord(m.ev_join, s_out));
+    B200FC_CUDA(cudaStreamWaitEvent(s, m.ev_join, 0));
     return check_kernel_status(s);
 }
 

@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <vector>
 #include "../../include/b200fc.h"
 
 namespace b200fc {
@@ -54,6 +55,10 @@ struct Mlp {
     int act_rows = 0;                               // rows of the last gate_up
     void* stage_x = nullptr; size_t stage_x_bytes = 0;
     void* stage_o = nullptr; size_t stage_o_bytes = 0;
+    // host-buffer entry point, large batches: copy-in / compute / copy-out streams and their events
+    cudaStream_t pipe_streams[3] = {nullptr, nullptr, nullptr};
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    std::vector<cudaEvent_t> ev_in, ev_out;
 };
 
 // error plumbing (api.cu)

@@ -101,6 +101,23 @@ def test_mlp_host_entry_point():
     assert H.rel_to_max(bf16_to_f32(out), bf16_to_f32(ref)) < 1e-2
 
 
+def test_mlp_host_entry_point_large_batch_is_pipelined():
+    """M >= 1024 goes through the chunked copy / compute / copy pipeline; rows must land where they belong."""
+    rng = np.random.default_rng(4)
+    M, K, N = 1100, 256, 512
+    x, gate, up, down = make_mlp_inputs(rng, M, K, N)
+    mlp = capi.Mlp(gate.ctypes.data, up.ctypes.data, down.ctypes.data, K, N)
+    out = np.zeros((M, K + 8), np.uint16)[:, :K]          # strided host output
+    xs = np.zeros((M, K + 16), np.uint16)[:, :K]; xs[:] = x  # strided host input
+    mlp.run_host(xs.ctypes.data, xs.strides[0], M, out.ctypes.data, out.strides[0])
+    ref = port.mlp(x, gate, up, down)
+    assert H.rel_to_max(bf16_to_f32(np.ascontiguousarray(out)), bf16_to_f32(ref)) < 1e-2
+    dx = H.Dev(x); dout = H.Dev(shape=(M, K), dtype=np.uint16)
+    mlp.run(dx.ptr, dx.ld, M, dout.ptr, dout.ld)
+    capi.sync_check()
+    assert np.array_equal(dout.numpy(), np.ascontiguousarray(out))   # same kernels row by row
+
+
 # MatmulVector known-answer shapes: main.cpp:884-885 (M=901, K=80 / 96), test_qk.cpp:486-487 (M=256, K=128)
 @pytest.mark.parametrize("M,K", [(901, 80), (901, 96), (256, 128), (64, 160), (64, 192), (7, 33), (1000, 4096)])
 def test_matvec(M, K):
