@@ -57,16 +57,22 @@ int check_kernel_status(cudaStream_t s) {
     return B200FC_OK;
 }
 
-// Per-(device, stream) scratch for re-strided activations.  Work on one stream is ordered, so one buffer per stream
-// is enough; it only grows.
 struct Scratch { void* p = nullptr; size_t bytes = 0; };
-static std::map<std::pair<int, cudaStream_t>, Scratch> g_scratch;
+struct ScratchKey {
+    int dev; cudaStream_t s; int slot;
+    bool operator<(const ScratchKey& o) const {
+        if (dev != o.dev) return dev < o.dev;
+        if (s != o.s) return s < o.s;
+        return slot < o.slot;
+    }
+};
+static std::map<ScratchKey, Scratch> g_scratch;
 
-static int get_scratch(size_t bytes, cudaStream_t s, void** out) {
+int get_stream_scratch(size_t bytes, cudaStream_t s, int slot, void** out) {
     int dev = 0;
     cudaGetDevice(&dev);
     std::lock_guard<std::mutex> lk(g_mu);
-    Scratch& sc = g_scratch[{dev, s}];
+    Scratch& sc = g_scratch[ScratchKey{dev, s, slot}];
     if (sc.bytes < bytes) {
         if (sc.p) { cudaStreamSynchronize(s); cudaFree(sc.p); sc.p = nullptr; sc.bytes = 0; }
         B200FC_CUDA(cudaMalloc(&sc.p, bytes));
@@ -75,6 +81,7 @@ static int get_scratch(size_t bytes, cudaStream_t s, void** out) {
     *out = sc.p;
     return B200FC_OK;
 }
+static int get_scratch(size_t bytes, cudaStream_t s, void** out) { return get_stream_scratch(bytes, s, 0, out); }
 
 static int grow(void** p, size_t* have, size_t need, cudaStream_t s) {
     if (*have >= need) return B200FC_OK;

@@ -67,6 +67,9 @@ int cuda_fail(cudaError_t e, const char* what);
 void count_launch(int n = 1);
 int* kernel_status_word();  // device int, 0 = OK; kernels store a non-zero code when a bounded wait runs out
 int check_kernel_status(cudaStream_t s);  // synchronises and reads it
+// growing device scratch owned by (device, stream, slot): work on one stream is ordered, so kernels launched on it
+// may share it; slot 0 = re-strided activations, slot 1 = stream-K partial tiles
+int get_stream_scratch(size_t bytes, cudaStream_t s, int slot, void** out);
 
 #define B200FC_CUDA(call)                                                   \
     do {                                                                    \
