@@ -490,10 +490,15 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const unsigned rank = cluster_ctarank();
     const bool leader = rank == 0;
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-    // Stream-K: the work is the sequence of (tile, K slab) units, tiles of 256 x BN in m-fastest order; every pair
-    // takes an equal contiguous share, so the last wave is as full as the others whatever the tile count.
-    const long long total_units = (long long)p.tiles_m * p.tiles_n * p.k_slabs;
-    const long long u_begin = total_units * pair / num_pairs, u_end = total_units * (pair + 1) / num_pairs;
+    // Work distribution.  Tiles are 256 x BN, numbered m-fastest.  Whole waves are handed out round-robin (pair p
+    // takes tiles p, p + P, ...), so the pairs running together work on neighbouring tiles and share the same weight
+    // slab in L2.  The tiles of the last, partial wave are cut along K instead (stream-K): their (tile, K slab)
+    // units are split evenly over all pairs, so the tail keeps every SM busy whatever the tile count.
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int full_waves = num_tiles / num_pairs;
+    const int dp_tiles = full_waves * num_pairs;
+    const long long sk_units = (long long)(num_tiles - dp_tiles) * p.k_slabs;
+    const long long u_begin = sk_units * pair / num_pairs, u_end = sk_units * (pair + 1) / num_pairs;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < C::STAGES; i++) {
@@ -526,9 +531,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             unsigned phase = 0;
             bool ok = true;
             const unsigned leader_full = mapa_rank(bar_full, 0);
-            for (long long u = u_begin; u < u_end && ok;) {
-                const int tile = (int)(u / p.k_slabs), k0 = (int)(u % p.k_slabs);
-                const int k1 = (int)min((long long)p.k_slabs, k0 + (u_end - u));
+            auto segment = [&](int tile, int k0, int k1) {
                 const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
                 const int row_a = tm * (2 * BM) + (int)rank * BM;
                 const int row_w = p.n0 + tn * BN + (int)rank * (BN / 2);
@@ -541,6 +544,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     tma_load_2d_pair(sa + C::A_BYTES, &map_w, leader_full + 8 * stage, kx, row_w);
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
+            };
+            for (int i = 0; i < full_waves && ok; i++) segment(pair + i * num_pairs, 0, p.k_slabs);
+            for (long long u = u_begin; u < u_end && ok;) {
+                const int k0 = (int)(u % p.k_slabs);
+                const int k1 = (int)min((long long)p.k_slabs, k0 + (u_end - u));
+                segment(dp_tiles + (int)(u / p.k_slabs), k0, k1);
                 u += k1 - k0;
             }
         }
@@ -551,12 +560,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             unsigned phase = 0;
             int it = 0;
             bool ok = true;
-            for (long long u = u_begin; u < u_end && ok; it++) {
-                const int k0 = (int)(u % p.k_slabs);
-                const int k1 = (int)min((long long)p.k_slabs, k0 + (u_end - u));
+            auto segment = [&](int k0, int k1) {
                 const int ab = it & 1;
                 const unsigned acc_phase = (unsigned)(it >> 1) & 1;
-                if (!mbar_wait(bar_acc_empty + 8 * ab, acc_phase ^ 1, abort_flag)) { ok = false; break; }
+                it++;
+                if (!mbar_wait(bar_acc_empty + 8 * ab, acc_phase ^ 1, abort_flag)) { ok = false; return; }
                 tc_fence_after();
                 const unsigned d_tmem = tmem_base + (unsigned)(ab * BN);
                 for (int ks = k0; ks < k1; ks++) {
@@ -577,6 +585,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     __syncwarp();
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
+            };
+            for (int i = 0; i < full_waves && ok; i++) segment(0, p.k_slabs);
+            for (long long u = u_begin; u < u_end && ok;) {
+                const int k0 = (int)(u % p.k_slabs);
+                const int k1 = (int)min((long long)p.k_slabs, k0 + (u_end - u));
+                segment(k0, k1);
                 u += k1 - k0;
             }
         }
@@ -587,14 +601,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         bool ok = true;
         const unsigned leader_acc_empty = mapa_rank(bar_acc_empty, 0);
         const int row_in_cta = quarter * 32 + lane;
-        for (long long u = u_begin; u < u_end && ok; it++) {
-            const int tile = (int)(u / p.k_slabs), k0 = (int)(u % p.k_slabs);
-            const int k1 = (int)min((long long)p.k_slabs, k0 + (u_end - u));
-            u += k1 - k0;
+        auto segment = [&](int tile, int k0, int k1) {
             const int ab = it & 1;
             const unsigned acc_phase = (unsigned)(it >> 1) & 1;
+            it++;
             const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-            if (!mbar_wait(bar_acc_full + 8 * ab, acc_phase, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(bar_acc_full + 8 * ab, acc_phase, abort_flag)) { ok = false; return; }
             tc_fence_after();
             const int m = tm * (2 * BM) + (int)rank * BM + row_in_cta;
             const bool row_ok = m < p.M;
@@ -621,8 +633,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 // Owner of the tile.  If its range ends inside the tile, the following pairs hold the rest of K.
                 int n_contrib = 0;
                 if (k1 < p.k_slabs) {
-                    const long long tile_end = (long long)(tile + 1) * p.k_slabs;
-                    for (int q = pair + 1; q < num_pairs && total_units * q / num_pairs < tile_end; q++) n_contrib++;
+                    const long long tile_end = (long long)(tile - dp_tiles + 1) * p.k_slabs;  // in stream-K units
+                    for (int q = pair + 1; q < num_pairs && sk_units * q / num_pairs < tile_end; q++) n_contrib++;
                     for (int q = pair + 1; q <= pair + n_contrib && ok; q++) {
                         const int* cnt = p.sk_count + q * 2 + rank;
                         const unsigned long long t0 = globaltimer();
@@ -663,6 +675,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_remote(leader_acc_empty + 8 * ab);
+        };
+        for (int i = 0; i < full_waves && ok; i++) segment(pair + i * num_pairs, 0, p.k_slabs);
+        for (long long u = u_begin; u < u_end && ok;) {
+            const int k0 = (int)(u % p.k_slabs);
+            const int k1 = (int)min((long long)p.k_slabs, k0 + (u_end - u));
+            segment(dp_tiles + (int)(u / p.k_slabs), k0, k1);
+            u += k1 - k0;
         }
     }
 
@@ -778,6 +797,7 @@ int launch_cfg2(const CUtensorMap& ma, const CUtensorMap& mw, GemmParams p, cuda
     const long long units = (long long)p.tiles_m * p.tiles_n * p.k_slabs;
     long long pairs = num_sms() / 2;
     if (units / 8 < pairs) pairs = units / 8 > 1 ? units / 8 : 1;
+    if (pairs < (long long)p.tiles_m * p.tiles_n && pairs < num_sms() / 2) pairs = num_sms() / 2;
     // scratch of this stream: one parked accumulator tile per pair + arrival counters (cleared before every launch)
     const size_t partial_bytes = (size_t)pairs * 2 * BM * BN * 4;
     void* scratch = nullptr;
