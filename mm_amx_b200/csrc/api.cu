@@ -499,17 +499,17 @@ int b200fc_mlp_run_host(b200fc_mlp_t* h, const void* x, int64_t ldx, int M, void
     int rc = grow(&m.stage_x, &m.stage_x_bytes, row * M, s);
     if (!rc) rc = grow(&m.stage_o, &m.stage_o_bytes, row * M, s);
     if (rc) return rc;
-    if (M < 1024) {
+    if (M < 2048) {
         B200FC_CUDA(cudaMemcpy2DAsync(m.stage_x, row, x, (size_t)ldx, row, (size_t)M, cudaMemcpyHostToDevice, s));
         rc = mlp_run_device(m, m.stage_x, (int64_t)row, M, m.stage_o, B200FC_BF16, (int64_t)row, s);
         if (rc) return rc;
         B200FC_CUDA(cudaMemcpy2DAsync(out, (size_t)ldo, m.stage_o, row, row, (size_t)M, cudaMemcpyDeviceToHost, s));
         return check_kernel_status(s);
     }
-    // Large batches: rows are independent, so the batch is cut into chunks of 512 rows that flow through three
+    // Large batches: rows are independent, so the batch is cut into chunks of 1024 rows that flow through three
     // streams — host-to-device copy, compute, device-to-host copy — and the PCIe transfers of neighbouring chunks
     // overlap the tensor-core work (the copy engines are full duplex).
-    const int chunk = 512;
+    const int chunk = 1024;  // 4 x 256-row tiles per column block: keeps the GEMM waves full
     const int n_chunks = (M + chunk - 1) / chunk;
     if (!m.pipe_streams[0]) {
         for (int i = 0; i < 3; i++) B200FC_CUDA(cudaStreamCreateWithFlags(&m.pipe_streams[i], cudaStreamNonBlocking));

@@ -49,10 +49,6 @@ struct GemmParams {
     int vec_ok;
     Epilogue ep;
     int* status;
-    // stream-K (2-CTA kernel): partial accumulator slots [pairs][2][128][256] (fp32 / int32 bits) and arrival counters
-    // [pairs][2], both in scratch that belongs to the stream
-    unsigned* sk_partial;
-    int* sk_count;
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------------------------
@@ -490,15 +486,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const unsigned rank = cluster_ctarank();
     const bool leader = rank == 0;
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-    // Work distribution.  Tiles are 256 x BN, numbered m-fastest.  Whole waves are handed out round-robin (pair p
-    // takes tiles p, p + P, ...), so the pairs running together work on neighbouring tiles and share the same weight
-    // slab in L2.  The tiles of the last, partial wave are cut along K instead (stream-K): their (tile, K slab)
-    // units are split evenly over all pairs, so the tail keeps every SM busy whatever the tile count.
-    const int num_tiles = p.tiles_m * p.tiles_n;
-    const int full_waves = num_tiles / num_pairs;
-    const int dp_tiles = full_waves * num_pairs;
-    const long long sk_units = (long long)(num_tiles - dp_tiles) * p.k_slabs;
-    const long long u_begin = sk_units * pair / num_pairs, u_end = sk_units * (pair + 1) / num_pairs;
+    const int num_tiles = p.tiles_m * p.tiles_n;  // tiles of 256 x BN
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < C::STAGES; i++) {
@@ -531,11 +519,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             unsigned phase = 0;
             bool ok = true;
             const unsigned leader_full = mapa_rank(bar_full, 0);
-            auto segment = [&](int tile, int k0, int k1) {
+            for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
                 const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
                 const int row_a = tm * (2 * BM) + (int)rank * BM;
                 const int row_w = p.n0 + tn * BN + (int)rank * (BN / 2);
-                for (int ks = k0; ks < k1; ks++) {
+                for (int ks = 0; ks < p.k_slabs; ks++) {
                     if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag)) { ok = false; break; }
                     if (leader) mbar_expect_tx(bar_full + 8 * stage, 2 * C::STAGE_BYTES);
                     const unsigned sa = smem_u32(smem + stage * C::STAGE_BYTES);
@@ -544,13 +532,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     tma_load_2d_pair(sa + C::A_BYTES, &map_w, leader_full + 8 * stage, kx, row_w);
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
-            };
-            for (int i = 0; i < full_waves && ok; i++) segment(pair + i * num_pairs, 0, p.k_slabs);
-            for (long long u = u_begin; u < u_end && ok;) {
-                const int k0 = (int)(u % p.k_slabs);
-                const int k1 = (int)min((long long)p.k_slabs, k0 + (u_end - u));
-                segment(dp_tiles + (int)(u / p.k_slabs), k0, k1);
-                u += k1 - k0;
             }
         }
     } else if (warp == 1) {
@@ -560,14 +541,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             unsigned phase = 0;
             int it = 0;
             bool ok = true;
-            auto segment = [&](int k0, int k1) {
+            for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, it++) {
                 const int ab = it & 1;
                 const unsigned acc_phase = (unsigned)(it >> 1) & 1;
-                it++;
-                if (!mbar_wait(bar_acc_empty + 8 * ab, acc_phase ^ 1, abort_flag)) { ok = false; return; }
+                if (!mbar_wait(bar_acc_empty + 8 * ab, acc_phase ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const unsigned d_tmem = tmem_base + (unsigned)(ab * BN);
-                for (int ks = k0; ks < k1; ks++) {
+                for (int ks = 0; ks < p.k_slabs; ks++) {
                     if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     if (lane == 0) {
@@ -578,20 +558,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         for (int k = 0; k < SLAB_BYTES / MMA_K_BYTES; k++)
                             tc_mma_pair<I8>(d_tmem, adesc + (unsigned long long)(k * (MMA_K_BYTES >> 4)),
                                             bdesc + (unsigned long long)(k * (MMA_K_BYTES >> 4)), p.idesc,
-                                            (unsigned)(((ks - k0) | k) != 0));
+                                            (unsigned)((ks | k) != 0));
                         tc_commit_pair(bar_empty + 8 * stage);
-                        if (ks == k1 - 1) tc_commit_pair(bar_acc_full + 8 * ab);
+                        if (ks == p.k_slabs - 1) tc_commit_pair(bar_acc_full + 8 * ab);
                     }
                     __syncwarp();
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
-            };
-            for (int i = 0; i < full_waves && ok; i++) segment(0, p.k_slabs);
-            for (long long u = u_begin; u < u_end && ok;) {
-                const int k0 = (int)(u % p.k_slabs);
-                const int k1 = (int)min((long long)p.k_slabs, k0 + (u_end - u));
-                segment(k0, k1);
-                u += k1 - k0;
             }
         }
     } else {
@@ -600,88 +573,27 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         int it = 0;
         bool ok = true;
         const unsigned leader_acc_empty = mapa_rank(bar_acc_empty, 0);
-        const int row_in_cta = quarter * 32 + lane;
-        auto segment = [&](int tile, int k0, int k1) {
+        for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, it++) {
             const int ab = it & 1;
             const unsigned acc_phase = (unsigned)(it >> 1) & 1;
-            it++;
             const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-            if (!mbar_wait(bar_acc_full + 8 * ab, acc_phase, abort_flag)) { ok = false; return; }
+            if (!mbar_wait(bar_acc_full + 8 * ab, acc_phase, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            const int m = tm * (2 * BM) + (int)rank * BM + row_in_cta;
+            const int m = tm * (2 * BM) + (int)rank * BM + quarter * 32 + lane;
             const bool row_ok = m < p.M;
             const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(ab * BN);
-            if (k0 != 0) {
-                // This pair holds a middle or final part of the tile's K range: park the raw accumulators in its
-                // slot and announce them.  (A pair meets such a segment only as the first of its range, so the
-                // pair that owns the tile — the one that started it at K = 0 — finds them waiting.)
-                unsigned* slot = p.sk_partial + (((size_t)pair * 2 + rank) * BM + row_in_cta) * BN;
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; c++) {
-                    if (p.n0 + tn * BN + c * 32 >= p.n1) break;
-                    unsigned r[32];
-                    tc_ld32(taddr + (unsigned)(c * 32), r);
-                    tc_wait_ld();
-                    uint4* dst = (uint4*)(slot + c * 32);
-#pragma unroll
-                    for (int j = 0; j < 8; j++) dst[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-                }
-                __threadfence();
-                __syncwarp();
-                if (lane == 0) atomicAdd(p.sk_count + pair * 2 + rank, 1);
-            } else {
-                // Owner of the tile.  If its range ends inside the tile, the following pairs hold the rest of K.
-                int n_contrib = 0;
-                if (k1 < p.k_slabs) {
-                    const long long tile_end = (long long)(tile - dp_tiles + 1) * p.k_slabs;  // in stream-K units
-                    for (int q = pair + 1; q < num_pairs && sk_units * q / num_pairs < tile_end; q++) n_contrib++;
-                    for (int q = pair + 1; q <= pair + n_contrib && ok; q++) {
-                        const int* cnt = p.sk_count + q * 2 + rank;
-                        const unsigned long long t0 = globaltimer();
-                        while (true) {
-                            int v;
-                            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
-                            if (v >= 4) break;
-                            if (*abort_flag) { ok = false; break; }
-                            if (globaltimer() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; ok = false; break; }
-                        }
-                    }
-                }
-#pragma unroll 1
-                for (int c = 0; c < BN / 32 && ok; c++) {
-                    const int n = p.n0 + tn * BN + c * 32;
-                    if (n >= p.n1) break;
-                    unsigned r[32];
-                    tc_ld32(taddr + (unsigned)(c * 32), r);
-                    tc_wait_ld();
-                    for (int q = pair + 1; q <= pair + n_contrib; q++) {  // fixed order: deterministic sums
-                        const uint4* src = (const uint4*)(p.sk_partial + (((size_t)q * 2 + rank) * BM + row_in_cta) * BN + c * 32);
-#pragma unroll
-                        for (int j = 0; j < 8; j++) {
-                            const uint4 v = src[j];
-                            if (p.acc_is_int) {
-                                r[4 * j] += v.x; r[4 * j + 1] += v.y; r[4 * j + 2] += v.z; r[4 * j + 3] += v.w;
-                            } else {
-                                r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + __uint_as_float(v.x));
-                                r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + __uint_as_float(v.y));
-                                r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + __uint_as_float(v.z));
-                                r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + __uint_as_float(v.w));
-                            }
-                        }
-                    }
-                    epilogue_chunk(r, m, n, p, row_ok);
-                }
+            for (int c = 0; c < BN / 32; c++) {
+                const int n = p.n0 + tn * BN + c * 32;
+                if (n >= p.n1) break;
+                unsigned r[32];
+                tc_ld32(taddr + (unsigned)(c * 32), r);
+                tc_wait_ld();
+                epilogue_chunk(r, m, n, p, row_ok);
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_remote(leader_acc_empty + 8 * ab);
-        };
-        for (int i = 0; i < full_waves && ok; i++) segment(pair + i * num_pairs, 0, p.k_slabs);
-        for (long long u = u_begin; u < u_end && ok;) {
-            const int k0 = (int)(u % p.k_slabs);
-            const int k1 = (int)min((long long)p.k_slabs, k0 + (u_end - u));
-            segment(dp_tiles + (int)(u / p.k_slabs), k0, k1);
-            u += k1 - k0;
         }
     }
 
@@ -784,7 +696,7 @@ int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& p
 }
 
 template <int BN, bool I8>
-int launch_cfg2(const CUtensorMap& ma, const CUtensorMap& mw, GemmParams p, cudaStream_t s) {
+int launch_cfg2(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& p, cudaStream_t s) {
     using C = Cfg2<BN>;
     static bool attr_done = false;
     if (!attr_done) {
@@ -792,21 +704,10 @@ int launch_cfg2(const CUtensorMap& ma, const CUtensorMap& mw, GemmParams p, cuda
                                          C::SMEM_BYTES));
         attr_done = true;
     }
-    // every pair gets an equal share of the (tile, K slab) units, but at least 8 slabs so that tiny problems are
-    // not shredded into partial tiles
-    const long long units = (long long)p.tiles_m * p.tiles_n * p.k_slabs;
-    long long pairs = num_sms() / 2;
-    if (units / 8 < pairs) pairs = units / 8 > 1 ? units / 8 : 1;
-    if (pairs < (long long)p.tiles_m * p.tiles_n && pairs < num_sms() / 2) pairs = num_sms() / 2;
-    // scratch of this stream: one parked accumulator tile per pair + arrival counters (cleared before every launch)
-    const size_t partial_bytes = (size_t)pairs * 2 * BM * BN * 4;
-    void* scratch = nullptr;
-    int rc = get_stream_scratch(partial_bytes + 1024, s, 1, &scratch);
-    if (rc) return rc;
-    p.sk_partial = (unsigned*)scratch;
-    p.sk_count = (int*)((char*)scratch + partial_bytes);
-    B200FC_CUDA(cudaMemsetAsync(p.sk_count, 0, (size_t)pairs * 2 * sizeof(int), s));
-    gemm_tc2_kernel<BN, I8><<<(unsigned)(2 * pairs), NUM_THREADS, C::SMEM_BYTES, s>>>(ma, mw, p);
+    int tiles = p.tiles_m * p.tiles_n;
+    int pairs = num_sms() / 2;
+    if (tiles < pairs) pairs = tiles;
+    gemm_tc2_kernel<BN, I8><<<2 * pairs, NUM_THREADS, C::SMEM_BYTES, s>>>(ma, mw, p);
     count_launch();
     B200FC_CUDA(cudaGetLastError());
     return B200FC_OK;
@@ -853,7 +754,6 @@ int launch_gemm_tc(const void* W_data, int w_dtype, int W_K_pad, int W_N_pad, co
     p.acc_is_int = i8 ? 1 : 0;
     p.ep = ep;
     p.status = kernel_status_word();
-    p.sk_partial = nullptr; p.sk_count = nullptr;
     int es = ep.out_dtype == B200FC_F32 || ep.out_dtype == B200FC_S32 ? 4 : (ep.out_dtype == B200FC_BF16 ? 2 : 1);
     if (ep.steps & B200FC_STEP_SILU_MUL)
         p.vec_ok = (((uintptr_t)ep.C & 15) == 0 && (ep.ldc & 15) == 0 && (n0 % 32) == 0) ? 1 : 0;
@@ -865,9 +765,7 @@ int launch_gemm_tc(const void* W_data, int w_dtype, int W_K_pad, int W_N_pad, co
     int rc = make_map(&ma, A, i8, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BM);
     if (rc) return rc;
     // 2-CTA tiles (256 x 256 per CTA pair) when there are at least two 128-row blocks of M and enough tiles
-    // ... or when the 1-CTA kernel would leave most SMs without a tile (the 2-CTA kernel splits K across pairs)
-    const bool few_tiles = tiles_m * ((nspan + 255) / 256) < num_sms() / 2 && K >= 2048;
-    const bool pair_ok = (forced_ctas() == 2) || (forced_ctas() == 0 && nspan > 128 && (M > BM || few_tiles));
+    const bool pair_ok = (forced_ctas() == 2) || (forced_ctas() == 0 && M > BM && nspan > 128);
     if (pair_ok) {
         const int bn2 = 256;
         p.tiles_m = (M + 2 * BM - 1) / (2 * BM);

@@ -102,9 +102,9 @@ def test_mlp_host_entry_point():
 
 
 def test_mlp_host_entry_point_large_batch_is_pipelined():
-    """M >= 1024 goes through the chunked copy / compute / copy pipeline; rows must land where they belong."""
+    """M >= 2048 goes through the chunked copy / compute / copy pipeline; rows must land where they belong."""
     rng = np.random.default_rng(4)
-    M, K, N = 1100, 256, 512
+    M, K, N = 2300, 256, 512
     x, gate, up, down = make_mlp_inputs(rng, M, K, N)
     mlp = capi.Mlp(gate.ctypes.data, up.ctypes.data, down.ctypes.data, K, N)
     out = np.zeros((M, K + 8), np.uint16)[:, :K]          # strided host output
