@@ -36,8 +36,8 @@ WORKLOADS = {
     "llama70b_mlp": dict(H=8192, I=28672, M=4096),
 }
 # DRAM traffic of one gate/up GEMM launch (dram__bytes_read.sum + dram__bytes_write.sum), from the ncu capture
-# summarised in profiles/ (file named there); None until a capture exists for the workload.
-NCU_TRAFFIC_BYTES = {"llama7b_mlp": 231.05e6, "llama70b_mlp": None}  # profiles/gemm_tc_kernel_llama7b_mlp_M2048.md
+# summarised in the profiles/ file named beside it; None where no capture exists for the workload.
+NCU_TRAFFIC_BYTES = {"llama7b_mlp": 233.73e6, "llama70b_mlp": None}  # profiles/gemm_tc2_kernel_llama7b_mlp_M2048.md
 
 
 def measured_peaks():
@@ -256,7 +256,7 @@ def run_ours(args, w, M, name):
       k_ms = k0.elapsed_time(k1) / args.steps
       k_flops = 4.0 * M * H * Is
       achieved = k_flops / (k_ms * 1e-3) / 1e12
-      roofline = {"kernel": "gemm_tc_kernel (gate/up projection + SiLU*up epilogue)", "bound": "tensor",
+      roofline = {"kernel": "gemm_tc2_kernel (gate/up projection + SiLU*up epilogue)", "bound": "tensor",
                 "achieved": achieved, "peak": peaks["bf16_burst"], "unit": "TFLOP/s",
                 "frac": achieved / peaks["bf16_burst"],
                 "peak_source": peaks["source"] + " (cuBLAS bf16 burst figure: the kernel is timed alone, in a loop "
