@@ -99,6 +99,9 @@ int launch_fill(void* p, size_t bytes, cudaStream_t s);
 // gemv.cu: M <= 16, bf16 activations, bf16 or int8 weights
 int launch_gemv(const Weight& w, const void* A, int M, int K, int64_t lda, int n0, int n1, const Epilogue& ep,
                 cudaStream_t s);
+// gemv_tma.cu: the same operation with the weights streamed by TMA through a shared-memory ring
+int launch_gemv_tma(const Weight& w, const void* A, int M, int K, int64_t lda, int n0, int n1, const Epilogue& ep,
+                    cudaStream_t s);
 // gemm_tc.cu: tcgen05 GEMM, bf16 x bf16 -> fp32 or 8-bit x 8-bit -> int32
 int launch_gemm_tc(const void* W_data, int w_dtype, int W_K_pad, int W_N_pad, const void* A, int dtypeA, int M, int K,
                    int64_t lda, int n0, int n1, const Epilogue& ep, cudaStream_t s);

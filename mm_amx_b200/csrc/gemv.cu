@@ -25,6 +25,7 @@
 //   memory and are added in rank order (deterministic), then the post-ops run and C is stored.
 #include <cooperative_groups.h>
 #include <cuda_fp16.h>
+#include <cstdlib>
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -395,8 +396,19 @@ int launch_variant(const GemvParams& p, int row_ctas, cudaStream_t s) {
 
 }  // namespace
 
+// B200FC_GEMV=regs selects the register-streaming kernel of this file, anything else the TMA-ring kernel (gemv_tma.cu)
+static bool use_register_kernel() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("B200FC_GEMV");
+        v = (e && e[0] == 'r') ? 1 : 0;
+    }
+    return v == 1;
+}
+
 int launch_gemv(const Weight& w, const void* A, int M, int K, int64_t lda, int n0, int n1, const Epilogue& ep,
                 cudaStream_t s) {
+    if (!use_register_kernel()) return launch_gemv_tma(w, A, M, K, lda, n0, n1, ep, s);
     if (M < 1 || M > 16) { set_error("gemv: M must be in [1, 16]"); return B200FC_ERR_INVALID; }
     if (w.dtype == B200FC_U8) { set_error("gemv: unsigned 8-bit weights are not supported with bf16 activations"); return B200FC_ERR_UNSUPPORTED; }
     if (n1 <= n0) return B200FC_OK;
