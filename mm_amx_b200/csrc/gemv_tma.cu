@@ -6,8 +6,8 @@
 // reach the multipliers.  Registers can hold only ~8 KB of weights in flight per warp, which leaves an SM short of
 // the bytes in flight that 6.5 TB/s of HBM need.  Here one producer warp per CTA streams 16 KB stages (128 weight
 // rows x 128 bytes of K, one 2-D TMA box with 128-byte swizzle) into a ring of 4-5 stages; with two CTAs per SM
-// about 160 KB are in flight per SM and the stream never stops while the four consumer warps stage activations,
-// widen int8 weights or reduce.  Consumers copy their 32 rows of a stage from shared memory into registers
+// about 160 KB are in flight per SM and the stream never stops while the eight consumer warps stage activations,
+// widen int8 weights or reduce.  Consumers copy their 16 rows of a stage from shared memory into registers
 // (conflict-free through the swizzle), release the stage, and run the same mma.sync path as gemv.cu.
 //   full[s]  : TMA complete_tx + one arrive.expect_tx by the producer        empty[s] : one arrive per consumer warp
 // All mbarrier waits are bounded; on a time-out the CTA raises an abort flag, every role leaves its loop, the kernel
@@ -23,8 +23,8 @@ namespace b200fc {
 
 namespace {
 
-constexpr int CWARPS = 4;                       // consumer warps
-constexpr int ROWS_PER_WARP = 32;
+constexpr int CWARPS = 8;                       // consumer warps
+constexpr int ROWS_PER_WARP = 16;
 constexpr int ROWS_PER_CTA = CWARPS * ROWS_PER_WARP;  // 128
 constexpr int STAGE_K_BYTES = 128;              // bytes of K per row and stage (one swizzle atom)
 constexpr int STAGE_BYTES = ROWS_PER_CTA * STAGE_K_BYTES;  // 16 KB
@@ -162,9 +162,10 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
     // the next kernel in the stream may start its own weight stream now
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    float acc[2][NT][4];
+    constexpr int RB = ROWS_PER_WARP / 16;  // 16-row MMA blocks per warp
+    float acc[RB][NT][4];
 #pragma unroll
-    for (int rb = 0; rb < 2; rb++)
+    for (int rb = 0; rb < RB; rb++)
 #pragma unroll
         for (int nt = 0; nt < NT; nt++)
 #pragma unroll
@@ -231,25 +232,35 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
             }
             consumer_sync();
         }
+        // Stages CHUNK_K activation elements of all MP rows: 128 sixteen-byte units per row, the 256 consumer
+        // threads take two rows per pass.  All loads of a thread are issued before the first is converted / stored.
+        constexpr int UNITS = CHUNK_K / 8;                    // 128
+        constexpr int ROWS_PER_PASS = CWARPS * 32 / UNITS;    // 2
+        constexpr int PASSES = MP / ROWS_PER_PASS;
+        const int unit = ctid % UNITS, row0 = ctid / UNITS;
         auto stage_x = [&](int it) {
-            const int k = it * KE + ctid * 8;
+            const int k = it * KE + unit * 8;
             consumer_sync();  // everyone is done with the previous chunk
             if (k < k_end) {
-#pragma unroll 1
-                for (int row = 0; row < MP; row++) {
-                    uint4 v = load_x_unit(row, k);
+                uint4 v[PASSES];
+#pragma unroll
+                for (int i = 0; i < PASSES; i++) v[i] = load_x_unit(row0 + i * ROWS_PER_PASS, k);
+#pragma unroll
+                for (int i = 0; i < PASSES; i++) {
+                    const int row = row0 + i * ROWS_PER_PASS;
+                    uint4 o4 = v[i];
                     if constexpr (W8) {
                         const float sc = __int_as_float((127 - sexp[row]) << 23);
-                        const unsigned w4[4] = {v.x, v.y, v.z, v.w};
+                        const unsigned w4[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
                         unsigned o[4];
 #pragma unroll
                         for (int q = 0; q < 4; q++) {
                             __half2 h = __floats2half2_rn(__uint_as_float(w4[q] << 16) * sc, __uint_as_float(w4[q] & 0xffff0000u) * sc);
                             o[q] = *(unsigned*)&h;
                         }
-                        v = make_uint4(o[0], o[1], o[2], o[3]);
+                        o4 = make_uint4(o[0], o[1], o[2], o[3]);
                     }
-                    *(uint4*)(xbuf + row * XROW + ctid * 16) = v;
+                    *(uint4*)(xbuf + row * XROW + unit * 16) = o4;
                 }
             }
             consumer_sync();
@@ -265,10 +276,10 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
             const int it_in_chunk = (it - it_begin) % STAGES_PER_CHUNK;
             if (it_in_chunk == 0) stage_x(it);
             if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) { ok = false; break; }
-            uint4 w[2][2][2];
+            uint4 w[RB][2][2];
             const unsigned char* sbase = smem + stage * STAGE_BYTES;
 #pragma unroll
-            for (int rb = 0; rb < 2; rb++)
+            for (int rb = 0; rb < RB; rb++)
 #pragma unroll
                 for (int h = 0; h < 2; h++)
 #pragma unroll
@@ -294,7 +305,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
                     }
                 }
 #pragma unroll
-                for (int rb = 0; rb < 2; rb++) {
+                for (int rb = 0; rb < RB; rb++) {
                     const unsigned wa[4] = {w[rb][0][j].x, w[rb][0][j].y, w[rb][0][j].z, w[rb][0][j].w};
                     const unsigned wb[4] = {w[rb][1][j].x, w[rb][1][j].y, w[rb][1][j].z, w[rb][1][j].w};
 #pragma unroll
@@ -321,7 +332,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
             for (int nt = 0; nt < NT; nt++) {
                 const int e0 = sexp[nt * 8 + 2 * t], e1 = sexp[nt * 8 + 2 * t + 1];
 #pragma unroll
-                for (int rb = 0; rb < 2; rb++) {
+                for (int rb = 0; rb < RB; rb++) {
                     acc[rb][nt][0] = scalbnf(acc[rb][nt][0], e0);
                     acc[rb][nt][2] = scalbnf(acc[rb][nt][2], e0);
                     acc[rb][nt][1] = scalbnf(acc[rb][nt][1], e1);
@@ -336,7 +347,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
     float* part = (float*)xbuf;
     if (warp < CWARPS) {
 #pragma unroll
-        for (int rb = 0; rb < 2; rb++)
+        for (int rb = 0; rb < RB; rb++)
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
                 const int row = warp * ROWS_PER_WARP + rb * 16 + g, tok = nt * 8 + 2 * t;
