@@ -116,7 +116,9 @@ __device__ __forceinline__ unsigned u8x2_to_f16x2(unsigned w, unsigned sel) {
 template <bool W8, int NT> struct Layout {
     static constexpr int STAGES = NT == 1 ? 5 : 4;
     static constexpr int MP = 8 * NT;
-    static constexpr int XROW = CHUNK_K * 2 + 16;   // bytes per staged activation row
+    // bytes per staged activation row; the pad makes rows g and g + 1 fall into different bank halves for the
+    // access pattern of each variant (see the fragment loads in the kernel)
+    static constexpr int XROW = CHUNK_K * 2 + (W8 ? 64 : 16);
     static constexpr int RING = STAGES * STAGE_BYTES;
     static constexpr int X_OFF = RING;
     static constexpr int AUX_OFF = X_OFF + MP * XROW;          // smax [MP][CWARPS], sexp [MP]
@@ -260,7 +262,10 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
                         }
                         o4 = make_uint4(o[0], o[1], o[2], o[3]);
                     }
-                    *(uint4*)(xbuf + row * XROW + unit * 16) = o4;
+                    // compressed weights: the 16 units of a stage are stored transposed as a 4 x 4 grid, so that the
+                    // four lanes t of a fragment load (units 4t + i) touch four neighbouring 16-byte slots
+                    const int slot = W8 ? ((unit & ~15) | ((unit & 3) << 2) | ((unit >> 2) & 3)) : unit;
+                    *(uint4*)(xbuf + row * XROW + slot * 16) = o4;
                 }
             }
             consumer_sync();
@@ -292,7 +297,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
 #pragma unroll
             for (int j = 0; j < 2; j++) {
                 // activations matching this thread's weight bytes: K elements [(2t + j) * (W8 ? 16 : 8), ...) of the stage
-                const int xoff = (it_in_chunk * KE + (2 * t + j) * (W8 ? 16 : 8)) * 2;
+                const int xoff = W8 ? it_in_chunk * KE * 2 + (8 * j + t) * 16 : (it_in_chunk * KE + (2 * t + j) * 8) * 2;
                 unsigned xb[NT][W8 ? 8 : 4];
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
@@ -300,7 +305,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
                     uint4 a = *(const uint4*)xs;
                     xb[nt][0] = a.x; xb[nt][1] = a.y; xb[nt][2] = a.z; xb[nt][3] = a.w;
                     if constexpr (W8) {
-                        uint4 b = *(const uint4*)(xs + 16);
+                        uint4 b = *(const uint4*)(xs + 64);  // unit 4t + 2j + 1 sits four slots further
                         xb[nt][4] = b.x; xb[nt][5] = b.y; xb[nt][6] = b.z; xb[nt][7] = b.w;
                     }
                 }
