@@ -7,7 +7,8 @@
 // the bytes in flight that 6.5 TB/s of HBM need.  Here one producer warp per CTA streams 16 KB stages (128 weight
 // rows x 128 bytes of K, one 2-D TMA box with 128-byte swizzle) into a ring of 4-5 stages; with two CTAs per SM
 // about 160 KB are in flight per SM and the stream never stops while the eight consumer warps stage activations,
-// widen int8 weights or reduce.  Consumers copy their 16 rows of a stage from shared memory into registers
+// widen int8 weights or reduce.  Consumers copy their share of a stage (32 rows x 64 bytes of K: activation
+// fragments are reused over two 16-row MMA blocks, which halves the shared-memory reads per weight) into registers
 // (conflict-free through the swizzle), release the stage, and run the same mma.sync path as gemv.cu.
 //   full[s]  : TMA complete_tx + one arrive.expect_tx by the producer        empty[s] : one arrive per consumer warp
 // All mbarrier waits are bounded; on a time-out the CTA raises an abort flag, every role leaves its loop, the kernel
@@ -24,8 +25,8 @@ namespace b200fc {
 namespace {
 
 constexpr int CWARPS = 8;                       // consumer warps
-constexpr int ROWS_PER_WARP = 16;
-constexpr int ROWS_PER_CTA = CWARPS * ROWS_PER_WARP;  // 128
+constexpr int ROWS_PER_WARP = 32;               // a warp owns 32 rows x one 64-byte half of every stage
+constexpr int ROWS_PER_CTA = (CWARPS / 2) * ROWS_PER_WARP;  // 128
 constexpr int STAGE_K_BYTES = 128;              // bytes of K per row and stage (one swizzle atom)
 constexpr int STAGE_BYTES = ROWS_PER_CTA * STAGE_K_BYTES;  // 16 KB
 constexpr int CHUNK_K = 1024;                   // activation elements staged per chunk
@@ -275,27 +276,26 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
         unsigned phase = 0;
         // byte offsets of this thread's 16-byte pieces inside a stage: rows (rb, h) -> warp*32 + rb*16 + h*8 + g,
         // logical chunk 2t + j, physical chunk = logical ^ (row & 7) = logical ^ g
-        const int row_base = warp * ROWS_PER_WARP + g;
+        const int rg = warp >> 1, kh = warp & 1;       // row group (32 rows) and K half (64 bytes) of this warp
+        const int row_base = rg * ROWS_PER_WARP + g;
         bool ok = true;
         for (int it = it_begin; it < it_end && ok; it++) {
             const int it_in_chunk = (it - it_begin) % STAGES_PER_CHUNK;
             if (it_in_chunk == 0) stage_x(it);
             if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) { ok = false; break; }
-            uint4 w[RB][2][2];
+            uint4 w[RB][2];
             const unsigned char* sbase = smem + stage * STAGE_BYTES;
 #pragma unroll
             for (int rb = 0; rb < RB; rb++)
 #pragma unroll
                 for (int h = 0; h < 2; h++)
-#pragma unroll
-                    for (int j = 0; j < 2; j++)
-                        w[rb][h][j] = *(const uint4*)(sbase + (row_base + rb * 16 + h * 8) * STAGE_K_BYTES + (((2 * t + j) ^ g) << 4));
+                    w[rb][h] = *(const uint4*)(sbase + (row_base + rb * 16 + h * 8) * STAGE_K_BYTES + (((2 * t + kh) ^ g) << 4));
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty + 8 * stage);
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
 
-#pragma unroll
-            for (int j = 0; j < 2; j++) {
+            {
+                const int j = kh;
                 // activations matching this thread's weight bytes: K elements [(2t + j) * (W8 ? 16 : 8), ...) of the stage
                 const int xoff = W8 ? it_in_chunk * KE * 2 + (8 * j + t) * 16 : (it_in_chunk * KE + (2 * t + j) * 8) * 2;
                 unsigned xb[NT][W8 ? 8 : 4];
@@ -311,8 +311,8 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
                 }
 #pragma unroll
                 for (int rb = 0; rb < RB; rb++) {
-                    const unsigned wa[4] = {w[rb][0][j].x, w[rb][0][j].y, w[rb][0][j].z, w[rb][0][j].w};
-                    const unsigned wb[4] = {w[rb][1][j].x, w[rb][1][j].y, w[rb][1][j].z, w[rb][1][j].w};
+                    const unsigned wa[4] = {w[rb][0].x, w[rb][0].y, w[rb][0].z, w[rb][0].w};
+                    const unsigned wb[4] = {w[rb][1].x, w[rb][1].y, w[rb][1].z, w[rb][1].w};
 #pragma unroll
                     for (int q = 0; q < MMA_PER_LOAD; q++) {
                         unsigned a0, a1, a2, a3;
@@ -347,19 +347,22 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
         }
     }
 
-    // ---- partial tile -> shared memory (over the activation buffer): part[token][row] ----
+    // ---- partial tiles -> shared memory (over the activation buffer): part[K half][token][row] ----
     __syncthreads();
     float* part = (float*)xbuf;
+    constexpr int PART_HALF = MP * ROWS_PER_CTA;  // floats per K half
     if (warp < CWARPS) {
+        const int rg = warp >> 1, kh = warp & 1;
 #pragma unroll
         for (int rb = 0; rb < RB; rb++)
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
-                const int row = warp * ROWS_PER_WARP + rb * 16 + g, tok = nt * 8 + 2 * t;
-                part[tok * ROWS_PER_CTA + row] = acc[rb][nt][0];
-                part[(tok + 1) * ROWS_PER_CTA + row] = acc[rb][nt][1];
-                part[tok * ROWS_PER_CTA + row + 8] = acc[rb][nt][2];
-                part[(tok + 1) * ROWS_PER_CTA + row + 8] = acc[rb][nt][3];
+                const int row = rg * ROWS_PER_WARP + rb * 16 + g, tok = nt * 8 + 2 * t;
+                float* pp = part + kh * PART_HALF;
+                pp[tok * ROWS_PER_CTA + row] = acc[rb][nt][0];
+                pp[(tok + 1) * ROWS_PER_CTA + row] = acc[rb][nt][1];
+                pp[tok * ROWS_PER_CTA + row + 8] = acc[rb][nt][2];
+                pp[(tok + 1) * ROWS_PER_CTA + row + 8] = acc[rb][nt][3];
             }
     }
     if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, 3);
@@ -378,8 +381,8 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
             float gsum = 0.0f, usum = 0.0f;
             for (int q = 0; q < S; q++) {
                 const float* rp = S > 1 ? cluster.map_shared_rank(part, q) : part;
-                gsum += rp[tok * ROWS_PER_CTA + grow];
-                usum += rp[tok * ROWS_PER_CTA + grow + 16];
+                gsum += rp[tok * ROWS_PER_CTA + grow] + rp[PART_HALF + tok * ROWS_PER_CTA + grow];
+                usum += rp[tok * ROWS_PER_CTA + grow + 16] + rp[PART_HALF + tok * ROWS_PER_CTA + grow + 16];
             }
             if (cta_row0 + grow + 16 < p.n1) {
                 unsigned short* crow = (unsigned short*)((char*)ep.C + (long long)tok * ep.ldc);
@@ -389,7 +392,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
             float sum = 0.0f;
             for (int q = 0; q < S; q++) {
                 const float* rp = S > 1 ? cluster.map_shared_rank(part, q) : part;
-                sum += rp[tok * ROWS_PER_CTA + orow];
+                sum += rp[tok * ROWS_PER_CTA + orow] + rp[PART_HALF + tok * ROWS_PER_CTA + orow];
             }
             const int n = cta_row0 + orow;
             if (n < p.n1) store_scalar(postop_scalar(sum, n, ep), tok, n, ep);
@@ -417,7 +420,7 @@ EncodeTiledFn encode_fn() {
 template <bool W8, int NT>
 int launch_variant(const CUtensorMap& map, const Params& p, int row_ctas, cudaStream_t s) {
     using L = Layout<W8, NT>;
-    static_assert(L::MP * L::XROW >= ROWS_PER_CTA * L::MP * 4, "partial tile must fit the activation buffer");
+    static_assert(L::MP * L::XROW >= 2 * ROWS_PER_CTA * L::MP * 4, "partial tiles must fit the activation buffer");
     static bool attr_done = false;
     if (!attr_done) {
         B200FC_CUDA(cudaFuncSetAttribute(gemv_tma_kernel<W8, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM));
