@@ -208,68 +208,84 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
             }
             return v;
         };
-        if constexpr (W8) {
-            // one power-of-two scale per activation row over this split's K range: largest magnitude -> 2^13, so the
-            // row fits fp16 (the compressed-weight MMA is fp16 x fp16); exact, undone on the accumulators at the end
-            for (int row = 0; row < MP; row++) {
-                unsigned m = 0;
-                if (row < p.M)
-                    for (int k = k_begin + ctid * 8; k < k_end && k < p.K; k += CWARPS * 32 * 8) {
-                        const uint4 v = load_x_unit(row, k);
-                        const unsigned w4[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                        for (int q = 0; q < 4; q++) m = max(m, max(w4[q] & 0x7fffu, (w4[q] >> 16) & 0x7fffu));
-                    }
-                m = __reduce_max_sync(0xffffffffu, m);
-                if (lane == 0) smax[row * CWARPS + warp] = m;
-            }
-            consumer_sync();
-            if (ctid < MP) {
-                unsigned m = 0;
-#pragma unroll
-                for (int q = 0; q < CWARPS; q++) m = max(m, smax[ctid * CWARPS + q]);
-                int field = (int)(m >> 7);
-                field = field < 1 ? 1 : field;
-                int e = field - 127 - 13;
-                sexp[ctid] = e < -126 ? -126 : e;
-            }
-            consumer_sync();
-        }
         // Stages CHUNK_K activation elements of all MP rows: 128 sixteen-byte units per row, the 256 consumer
         // threads take two rows per pass.  All loads of a thread are issued before the first is converted / stored.
         constexpr int UNITS = CHUNK_K / 8;                    // 128
         constexpr int ROWS_PER_PASS = CWARPS * 32 / UNITS;    // 2
         constexpr int PASSES = MP / ROWS_PER_PASS;
         const int unit = ctid % UNITS, row0 = ctid / UNITS;
+        // Compressed weights multiply fp16 x fp16, so every staged chunk is scaled per activation row by the power
+        // of two that puts the row's largest magnitude (within the chunk) at 2^13 and converted to fp16: exact, since
+        // fp16 keeps the 8-bit significand of bf16.  The accumulators carry the row's current scale (cur_e) and are
+        // rescaled when a new chunk brings a different one; the scale is undone after the last stage.
+        int cur_e[NT][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) cur_e[nt][0] = cur_e[nt][1] = 0;
         auto stage_x = [&](int it) {
             const int k = it * KE + unit * 8;
+            const bool need = k < k_end;
             consumer_sync();  // everyone is done with the previous chunk
-            if (k < k_end) {
-                uint4 v[PASSES];
+            uint4 v[PASSES];
 #pragma unroll
-                for (int i = 0; i < PASSES; i++) v[i] = load_x_unit(row0 + i * ROWS_PER_PASS, k);
+            for (int i = 0; i < PASSES; i++) v[i] = need ? load_x_unit(row0 + i * ROWS_PER_PASS, k) : make_uint4(0, 0, 0, 0);
+            if constexpr (W8) {
 #pragma unroll
                 for (int i = 0; i < PASSES; i++) {
-                    const int row = row0 + i * ROWS_PER_PASS;
-                    uint4 o4 = v[i];
-                    if constexpr (W8) {
-                        const float sc = __int_as_float((127 - sexp[row]) << 23);
-                        const unsigned w4[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
-                        unsigned o[4];
+                    const unsigned w4[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+                    unsigned m = 0;
 #pragma unroll
-                        for (int q = 0; q < 4; q++) {
-                            __half2 h = __floats2half2_rn(__uint_as_float(w4[q] << 16) * sc, __uint_as_float(w4[q] & 0xffff0000u) * sc);
-                            o[q] = *(unsigned*)&h;
-                        }
-                        o4 = make_uint4(o[0], o[1], o[2], o[3]);
-                    }
-                    // compressed weights: the 16 units of a stage are stored transposed as a 4 x 4 grid, so that the
-                    // four lanes t of a fragment load (units 4t + i) touch four neighbouring 16-byte slots
-                    const int slot = W8 ? ((unit & ~15) | ((unit & 3) << 2) | ((unit >> 2) & 3)) : unit;
-                    *(uint4*)(xbuf + row * XROW + slot * 16) = o4;
+                    for (int q = 0; q < 4; q++) m = max(m, max(w4[q] & 0x7fffu, (w4[q] >> 16) & 0x7fffu));
+                    m = __reduce_max_sync(0xffffffffu, m);
+                    if (lane == 0) smax[(row0 + i * ROWS_PER_PASS) * CWARPS + warp] = m;   // 4 of the 8 slots per row
                 }
+                consumer_sync();
+            }
+#pragma unroll
+            for (int i = 0; i < PASSES; i++) {
+                const int row = row0 + i * ROWS_PER_PASS;
+                uint4 o4 = v[i];
+                if constexpr (W8) {
+                    // the four warps that hold this row: warps 4 * row0 .. 4 * row0 + 3
+                    unsigned m = 0;
+#pragma unroll
+                    for (int q = 0; q < 4; q++) m = max(m, smax[row * CWARPS + row0 * 4 + q]);
+                    int field = (int)(m >> 7);          // biased exponent of the largest magnitude (bf16 layout)
+                    field = field < 1 ? 1 : field;
+                    int e = field - 127 - 13;
+                    e = e < -126 ? -126 : e;
+                    if (unit == 0) sexp[row] = e;
+                    const float sc = __int_as_float((127 - e) << 23);  // 2^-e
+                    const unsigned w4[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+                    unsigned o[4];
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        __half2 h = __floats2half2_rn(__uint_as_float(w4[q] << 16) * sc, __uint_as_float(w4[q] & 0xffff0000u) * sc);
+                        o[q] = *(unsigned*)&h;
+                    }
+                    o4 = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+                // compressed weights: the 16 units of a stage are stored transposed as a 4 x 4 grid, so that the
+                // four lanes t of a fragment load (units 4t + i) touch four neighbouring 16-byte slots
+                const int slot = W8 ? ((unit & ~15) | ((unit & 3) << 2) | ((unit >> 2) & 3)) : unit;
+                if (need) *(uint4*)(xbuf + row * XROW + slot * 16) = o4;
             }
             consumer_sync();
+            if constexpr (W8) {
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const int e0 = sexp[nt * 8 + 2 * t], e1 = sexp[nt * 8 + 2 * t + 1];
+                    if (cur_e[nt][0] != e0 || cur_e[nt][1] != e1) {
+#pragma unroll
+                        for (int rb = 0; rb < RB; rb++) {
+                            acc[rb][nt][0] = scalbnf(acc[rb][nt][0], cur_e[nt][0] - e0);
+                            acc[rb][nt][2] = scalbnf(acc[rb][nt][2], cur_e[nt][0] - e0);
+                            acc[rb][nt][1] = scalbnf(acc[rb][nt][1], cur_e[nt][1] - e1);
+                            acc[rb][nt][3] = scalbnf(acc[rb][nt][3], cur_e[nt][1] - e1);
+                        }
+                        cur_e[nt][0] = e0; cur_e[nt][1] = e1;
+                    }
+                }
+            }
         };
 
         int stage = 0;
@@ -334,16 +350,14 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
         }
         if constexpr (W8) {
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++) {
-                const int e0 = sexp[nt * 8 + 2 * t], e1 = sexp[nt * 8 + 2 * t + 1];
+            for (int nt = 0; nt < NT; nt++)
 #pragma unroll
                 for (int rb = 0; rb < RB; rb++) {
-                    acc[rb][nt][0] = scalbnf(acc[rb][nt][0], e0);
-                    acc[rb][nt][2] = scalbnf(acc[rb][nt][2], e0);
-                    acc[rb][nt][1] = scalbnf(acc[rb][nt][1], e1);
-                    acc[rb][nt][3] = scalbnf(acc[rb][nt][3], e1);
+                    acc[rb][nt][0] = scalbnf(acc[rb][nt][0], cur_e[nt][0]);
+                    acc[rb][nt][2] = scalbnf(acc[rb][nt][2], cur_e[nt][0]);
+                    acc[rb][nt][1] = scalbnf(acc[rb][nt][1], cur_e[nt][1]);
+                    acc[rb][nt][3] = scalbnf(acc[rb][nt][3], cur_e[nt][1]);
                 }
-            }
         }
     }
 
