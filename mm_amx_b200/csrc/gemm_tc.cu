@@ -49,6 +49,10 @@ struct GemmParams {
     int vec_ok;
     Epilogue ep;
     int* status;
+    // split-K (2-CTA kernel): work item = (tile, split); with splits > 1 the epilogue stores raw accumulators into
+    // slab `split` of a workspace ([splits][M][row pitch]) and a second kernel reduces and runs the post-ops
+    int splits;
+    long long split_stride;  // bytes between workspace slabs
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------------------------
@@ -146,10 +150,11 @@ __device__ __forceinline__ unsigned long long make_smem_desc(unsigned smem_addr)
 }
 
 // ---- epilogue on 32 consecutive columns of one output row ------------------------------------------------------------
-__device__ __forceinline__ void epilogue_chunk(const unsigned (&r)[32], int m, int n, const GemmParams& p, bool row_ok) {
+__device__ __forceinline__ void epilogue_chunk(const unsigned (&r)[32], int m, int n, const GemmParams& p, bool row_ok,
+                                               long long c_offset = 0) {
     const Epilogue& ep = p.ep;
     if (!row_ok) return;
-    char* crow = (char*)ep.C + (long long)m * ep.ldc;
+    char* crow = (char*)ep.C + c_offset + (long long)m * ep.ldc;
     if (ep.out_dtype == B200FC_S32) {  // raw accumulators
         if (p.vec_ok && n + 32 <= p.n1) {
             int4* dst = (int4*)(crow + (long long)n * 4);
@@ -487,6 +492,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const bool leader = rank == 0;
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
     const int num_tiles = p.tiles_m * p.tiles_n;  // tiles of 256 x BN
+    const int num_items = num_tiles * p.splits;   // (tile, K split) work items
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < C::STAGES; i++) {
@@ -519,11 +525,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             unsigned phase = 0;
             bool ok = true;
             const unsigned leader_full = mapa_rank(bar_full, 0);
-            for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+            for (int item = pair; item < num_items && ok; item += num_pairs) {
+                const int tile = item % num_tiles, split = item / num_tiles;
+                const int ks0 = p.k_slabs * split / p.splits, ks1 = p.k_slabs * (split + 1) / p.splits;
                 const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
                 const int row_a = tm * (2 * BM) + (int)rank * BM;
                 const int row_w = p.n0 + tn * BN + (int)rank * (BN / 2);
-                for (int ks = 0; ks < p.k_slabs; ks++) {
+                for (int ks = ks0; ks < ks1; ks++) {
                     if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag)) { ok = false; break; }
                     if (leader) mbar_expect_tx(bar_full + 8 * stage, 2 * C::STAGE_BYTES);
                     const unsigned sa = smem_u32(smem + stage * C::STAGE_BYTES);
@@ -541,13 +549,15 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             unsigned phase = 0;
             int it = 0;
             bool ok = true;
-            for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, it++) {
+            for (int item = pair; item < num_items && ok; item += num_pairs, it++) {
+                const int split = item / num_tiles;
+                const int ks0 = p.k_slabs * split / p.splits, ks1 = p.k_slabs * (split + 1) / p.splits;
                 const int ab = it & 1;
                 const unsigned acc_phase = (unsigned)(it >> 1) & 1;
                 if (!mbar_wait(bar_acc_empty + 8 * ab, acc_phase ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const unsigned d_tmem = tmem_base + (unsigned)(ab * BN);
-                for (int ks = 0; ks < p.k_slabs; ks++) {
+                for (int ks = ks0; ks < ks1; ks++) {
                     if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     if (lane == 0) {
@@ -558,9 +568,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         for (int k = 0; k < SLAB_BYTES / MMA_K_BYTES; k++)
                             tc_mma_pair<I8>(d_tmem, adesc + (unsigned long long)(k * (MMA_K_BYTES >> 4)),
                                             bdesc + (unsigned long long)(k * (MMA_K_BYTES >> 4)), p.idesc,
-                                            (unsigned)((ks | k) != 0));
+                                            (unsigned)(((ks - ks0) | k) != 0));
                         tc_commit_pair(bar_empty + 8 * stage);
-                        if (ks == p.k_slabs - 1) tc_commit_pair(bar_acc_full + 8 * ab);
+                        if (ks == ks1 - 1) tc_commit_pair(bar_acc_full + 8 * ab);
                     }
                     __syncwarp();
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
@@ -573,7 +583,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         int it = 0;
         bool ok = true;
         const unsigned leader_acc_empty = mapa_rank(bar_acc_empty, 0);
-        for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, it++) {
+        for (int item = pair; item < num_items && ok; item += num_pairs, it++) {
+            const int tile = item % num_tiles, split = item / num_tiles;
+            const long long c_offset = (long long)split * p.split_stride;
             const int ab = it & 1;
             const unsigned acc_phase = (unsigned)(it >> 1) & 1;
             const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
@@ -589,7 +601,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 unsigned r[32];
                 tc_ld32(taddr + (unsigned)(c * 32), r);
                 tc_wait_ld();
-                epilogue_chunk(r, m, n, p, row_ok);
+                epilogue_chunk(r, m, n, p, row_ok, c_offset);
             }
             tc_fence_before();
             __syncwarp();
@@ -613,6 +625,39 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)C::TMEM_COLS)
                      : "memory");
+    }
+}
+
+// ---- split-K reduction + post-ops ------------------------------------------------------------------------------------
+// ws holds `splits` slabs of raw accumulators ([M][pitch], column index = global n - n0).  Each thread sums one output
+// element over the slabs in slab order (deterministic) and runs the ordinary post-ops / SiLU pairing on it.
+__global__ void splitk_reduce_kernel(const unsigned* __restrict__ ws, long long slab_elems, int pitch, int splits, int M,
+                                     int n0, int n1, int acc_is_int, const Epilogue ep) {
+    const bool silu = (ep.steps & B200FC_STEP_SILU_MUL) != 0;
+    const int cols = silu ? (n1 - n0) / 2 : (n1 - n0);
+    const long long total = (long long)M * cols;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int m = (int)(i / cols), c = (int)(i % cols);
+        const unsigned* row = ws + (long long)m * pitch;
+        if (silu) {
+            const int gcol = 32 * (c >> 4) + (c & 15);
+            float gsum = 0.0f, usum = 0.0f;
+            for (int q = 0; q < splits; q++) {
+                gsum += __uint_as_float(row[q * slab_elems + gcol]);
+                usum += __uint_as_float(row[q * slab_elems + gcol + 16]);
+            }
+            unsigned short* crow = (unsigned short*)((char*)ep.C + (long long)m * ep.ldc);
+            crow[(n0 >> 1) + c] = f32_to_bf16_bits(silu_f(gsum) * usum);
+        } else if (acc_is_int) {
+            int sum = 0;
+            for (int q = 0; q < splits; q++) sum += (int)row[q * slab_elems + c];
+            if (ep.out_dtype == B200FC_S32) ((int*)((char*)ep.C + (long long)m * ep.ldc))[n0 + c] = sum;
+            else store_scalar(postop_scalar((float)sum, n0 + c, ep), m, n0 + c, ep);
+        } else {
+            float sum = 0.0f;
+            for (int q = 0; q < splits; q++) sum += __uint_as_float(row[q * slab_elems + c]);
+            store_scalar(postop_scalar(sum, n0 + c, ep), m, n0 + c, ep);
+        }
     }
 }
 
@@ -696,7 +741,7 @@ int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& p
 }
 
 template <int BN, bool I8>
-int launch_cfg2(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& p, cudaStream_t s) {
+int launch_cfg2(const CUtensorMap& ma, const CUtensorMap& mw, GemmParams p, cudaStream_t s) {
     using C = Cfg2<BN>;
     static bool attr_done = false;
     if (!attr_done) {
@@ -704,12 +749,52 @@ int launch_cfg2(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& 
                                          C::SMEM_BYTES));
         attr_done = true;
     }
-    int tiles = p.tiles_m * p.tiles_n;
-    int pairs = num_sms() / 2;
-    if (tiles < pairs) pairs = tiles;
+    const int tiles = p.tiles_m * p.tiles_n;
+    const int max_pairs = num_sms() / 2;
+    // Too few tiles to occupy the GPU (small M): split K so that every pair has work; the raw partial accumulators go
+    // through a workspace of this stream and a second kernel sums them in order and runs the post-ops.
+    int splits = 1;
+    if (tiles * 2 <= max_pairs && p.k_slabs >= 16) {
+        splits = max_pairs / tiles;
+        if (splits > 8) splits = 8;
+        if (splits > p.k_slabs / 8) splits = p.k_slabs / 8;
+        if (splits < 1) splits = 1;
+    }
+    p.splits = splits;
+    p.split_stride = 0;
+    const Epilogue final_ep = p.ep;
+    const int final_vec = p.vec_ok;
+    int pitch = 0;
+    if (splits > 1) {
+        const int nspan = p.n1 - p.n0;
+        pitch = (nspan + 3) / 4 * 4;
+        const size_t slab = (size_t)p.M * pitch * 4;
+        void* ws = nullptr;
+        int rc = get_stream_scratch(slab * splits, s, 1, &ws);
+        if (rc) return rc;
+        p.split_stride = (long long)slab;
+        p.ep.steps = 0;
+        p.ep.out_dtype = I8 ? B200FC_S32 : B200FC_F32;
+        p.ep.C = (char*)ws - (long long)p.n0 * 4;   // the kernel indexes columns by the global n
+        p.ep.ldc = (long long)pitch * 4;
+        p.vec_ok = (p.n0 % 4) == 0 ? 1 : 0;
+    }
+    int items = tiles * splits;
+    int pairs = items < max_pairs ? items : max_pairs;
     gemm_tc2_kernel<BN, I8><<<2 * pairs, NUM_THREADS, C::SMEM_BYTES, s>>>(ma, mw, p);
     count_launch();
     B200FC_CUDA(cudaGetLastError());
+    if (splits > 1) {
+        const long long total = (long long)p.M * (p.n1 - p.n0);
+        long long blocks = (total + 255) / 256;
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, s>>>((const unsigned*)((char*)p.ep.C + (long long)p.n0 * 4),
+                                                             (long long)p.M * pitch, pitch, splits, p.M, p.n0, p.n1,
+                                                             p.acc_is_int, final_ep);
+        count_launch();
+        B200FC_CUDA(cudaGetLastError());
+    }
+    (void)final_vec;
     return B200FC_OK;
 }
 
@@ -754,6 +839,7 @@ int launch_gemm_tc(const void* W_data, int w_dtype, int W_K_pad, int W_N_pad, co
     p.acc_is_int = i8 ? 1 : 0;
     p.ep = ep;
     p.status = kernel_status_word();
+    p.splits = 1; p.split_stride = 0;
     int es = ep.out_dtype == B200FC_F32 || ep.out_dtype == B200FC_S32 ? 4 : (ep.out_dtype == B200FC_BF16 ? 2 : 1);
     if (ep.steps & B200FC_STEP_SILU_MUL)
         p.vec_ok = (((uintptr_t)ep.C & 15) == 0 && (ep.ldc & 15) == 0 && (n0 % 32) == 0) ? 1 : 0;
@@ -765,7 +851,9 @@ int launch_gemm_tc(const void* W_data, int w_dtype, int W_K_pad, int W_N_pad, co
     int rc = make_map(&ma, A, i8, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BM);
     if (rc) return rc;
     // 2-CTA tiles (256 x 256 per CTA pair) when there are at least two 128-row blocks of M and enough tiles
-    const bool pair_ok = (forced_ctas() == 2) || (forced_ctas() == 0 && M > BM && nspan > 128);
+    // ... or when the 1-CTA kernel would leave most SMs without a tile while K is long (the 2-CTA launcher splits K)
+    const bool few_tiles = tiles_m * ((nspan + 255) / 256) * 2 <= num_sms() / 2 && K >= 2048;
+    const bool pair_ok = (forced_ctas() == 2) || (forced_ctas() == 0 && nspan > 128 && (M > BM || few_tiles));
     if (pair_ok) {
         const int bn2 = 256;
         p.tiles_m = (M + 2 * BM - 1) / (2 * BM);

@@ -129,6 +129,26 @@ def test_s8_postops(M):
                 assert (ref == 127).any() or (ref == -128).any() or True
 
 
+@pytest.mark.parametrize("M,K,N", [(100, 4096, 512), (256, 4096, 1024), (64, 2304, 300), (17, 8192, 256)])
+def test_split_k_shapes_exact(M, K, N):
+    """few output tiles and a long K: the GEMM splits K over CTA pairs and reduces in a second kernel"""
+    rng = np.random.default_rng(M + K + N)
+    A = H.two_valued_bf16(rng, (M, K)); B = H.two_valued_bf16(rng, (K, N))
+    bias = (rng.integers(-8, 9, N) * 0.25).astype(np.float32)
+    w = H.pack(B)
+    got = H.run_matmul(w, A, capi.F32, steps=capi.STEP_BIAS, bias=bias)
+    assert np.array_equal(got, port.postops(port.gemm_bf16(A, B), port.BIAS, port.F32, bias=bias))
+    got = H.run_matmul(w, A, capi.F32, n0=32, n1=N - 7)
+    assert np.array_equal(got[:, 32:N - 7], port.gemm_bf16(A, B)[:, 32:N - 7])
+    Ai = rng.integers(-128, 128, (M, K), dtype=np.int8); Bi = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    wi = H.pack(Bi)
+    acc = port.gemm_i8(Ai, Bi)
+    assert np.array_equal(H.run_matmul(wi, Ai, capi.S32), acc)
+    got8 = H.run_matmul(wi, Ai, capi.S8, steps=capi.STEP_DEQUANT | capi.STEP_QUANT, deq_scale=0.001, q_scale=2.0)
+    ref8 = port.postops(acc, port.DEQUANT | port.QUANT, port.S8, deq_scale=0.001, q_scale=2.0)
+    assert np.abs(got8.astype(np.int32) - ref8.astype(np.int32)).max() <= 1
+
+
 def test_column_range_and_sentinel():
     """n0/n1 compute a column sub-range only (Matmul::operator() n0, n1; kernels_amx.hpp:1169-1178)."""
     rng = np.random.default_rng(5)

@@ -90,6 +90,17 @@ def test_mlp_tensor_parallel_shards(M, tp):
     assert H.rel_to_max(bf16_to_f32(got), bf16_to_f32(ref)) < 1e-2
 
 
+def test_mlp_long_k_few_tiles():
+    """M just above the decode limit with a long K: both GEMMs take the split-K route (SiLU pairing in the reduction)"""
+    rng = np.random.default_rng(77)
+    M, K, N = 40, 2048, 4096
+    x, gate, up, down = make_mlp_inputs(rng, M, K, N)
+    ref, ref_act = port.mlp(x, gate, up, down, want_act=True)
+    got, act = run_mlp(x, gate, up, down)
+    assert H.rel_to_max(bf16_to_f32(act), bf16_to_f32(ref_act)) < 1e-2
+    assert H.rel_to_max(bf16_to_f32(got), bf16_to_f32(ref)) < 1e-2
+
+
 def test_mlp_host_entry_point():
     rng = np.random.default_rng(3)
     M, K, N = 24, 256, 512
