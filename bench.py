@@ -206,9 +206,14 @@ def run_ours(args, w, M, name):
                 dt = capi.F32 if oo.dtype == torch.float32 else capi.BF16
                 mlp.run_partial(xx.data_ptr(), H * 2, xx.shape[0], oo.data_ptr(), dt, oo.stride(0) * oo.element_size(),
                                 torch.cuda.current_stream().cuda_stream)
-        tpm = tp.TensorParallelMLP(Local(), H, partial_dtype=torch.bfloat16, chunk_rows=args.chunk_rows)
-        def step():
-            tpm.forward(x, out)
+        if args.tp_mode == "fused":
+            fused = tp.FusedTensorParallelMLP(mlp, H, M)
+            def step():
+                fused.forward(x)
+        else:
+            tpm = tp.TensorParallelMLP(Local(), H, partial_dtype=torch.bfloat16, chunk_rows=args.chunk_rows)
+            def step():
+                tpm.forward(x, out)
 
     def barrier():
         if world > 1:
@@ -268,7 +273,7 @@ def run_ours(args, w, M, name):
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": name, "M": M, "hidden": H, "intermediate": I,
-                       "parallelism": "tp%d" % world if world > 1 else "single GPU",
+                       "parallelism": ("tp%d (%s all-reduce)" % (world, args.tp_mode)) if world > 1 else "single GPU",
                        "cold": "weights (%.0f MB per GPU) larger than the 126 MB L2" % (weight_bytes(w) / world / 1e6)},
             "gpu_launches": launches, "roofline": roofline}
 
@@ -451,6 +456,9 @@ def main():
     ap.add_argument("--workload", default=None, choices=[None] + list(WORKLOADS))
     ap.add_argument("--M", type=int, default=None)
     ap.add_argument("--chunk-rows", type=int, default=1024)
+    ap.add_argument("--tp-mode", default="nccl", choices=["nccl", "fused"],
+                    help="N > 1: 'nccl' = all-reduce in row chunks overlapping the GEMMs, 'fused' = in-switch reduction "
+                         "from the down-projection epilogue (multimem.red)")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--legs", default="kernel,e2e,decode,configs,cpu",
                     help="optional legs after the main timed loop (comma list of kernel,e2e,decode,configs,cpu; '' = none)")

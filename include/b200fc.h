@@ -133,6 +133,13 @@ int b200fc_mlp_run_partial(b200fc_mlp_t* mlp, const void* x, int64_t ldx_bytes, 
  * Linear::run, :648-704): gate_up writes the internal [M, N/tp] bf16 activation, down consumes it. */
 int b200fc_mlp_gate_up(b200fc_mlp_t* mlp, const void* x, int64_t ldx_bytes, int M, void* stream);
 int b200fc_mlp_down(b200fc_mlp_t* mlp, int M, void* out, int out_dtype, int64_t ldo_bytes, void* stream);
+/* Down projection fused with the tensor-parallel all-reduce (no reference counterpart; the reference's pairwise
+ * split-K reduce, tests/amx-mlp.cpp:656-683, is its single-process ancestor).  `multicast_out` is an NVLink
+ * multicast (NVLS) mapping of the [M, K] output that every rank of the group has bound, e.g. the multicast_ptr of a
+ * torch symmetric-memory buffer; the GEMM epilogue adds this rank's contribution into ALL replicas with
+ * multimem.red, so no separate collective runs.  The caller zeroes the replicas and separates steps with a
+ * cross-rank barrier (see mm_amx_b200/tp.py).  Needs M > 16; split-K shapes are not supported. */
+int b200fc_mlp_down_reduce(b200fc_mlp_t* mlp, int M, void* multicast_out, int out_dtype, int64_t ldo_bytes, void* stream);
 /* x and out in HOST memory; copies, runs, copies back, synchronises. */
 int b200fc_mlp_run_host(b200fc_mlp_t* mlp, const void* x, int64_t ldx_bytes, int M, void* out, int64_t ldo_bytes,
                         void* stream);

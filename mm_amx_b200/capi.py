@@ -46,6 +46,7 @@ SIGNATURES = {
     "b200fc_mlp_run_partial": (c_int, [c_void_p, c_void_p, c_i64, c_int, c_void_p, c_int, c_i64, c_void_p]),
     "b200fc_mlp_gate_up": (c_int, [c_void_p, c_void_p, c_i64, c_int, c_void_p]),
     "b200fc_mlp_down": (c_int, [c_void_p, c_int, c_void_p, c_int, c_i64, c_void_p]),
+    "b200fc_mlp_down_reduce": (c_int, [c_void_p, c_int, c_void_p, c_int, c_i64, c_void_p]),
     "b200fc_mlp_run_host": (c_int, [c_void_p, c_void_p, c_i64, c_int, c_void_p, c_i64, c_void_p]),
     "b200fc_mlp_run_decode_static": (c_int, [c_void_p, c_void_p, c_i64, c_int, c_void_p, c_int, c_i64, c_void_p]),
     "b200fc_mlp_decode_static_capacity": (c_i64, []),
@@ -163,6 +164,9 @@ class Mlp:
 
     def down(self, M, out_ptr, out_dtype, ldo_bytes, stream=None):
         check(lib().b200fc_mlp_down(self.h, M, out_ptr, out_dtype, ldo_bytes, stream))
+
+    def down_reduce(self, M, multicast_ptr, out_dtype, ldo_bytes, stream=None):
+        check(lib().b200fc_mlp_down_reduce(self.h, M, multicast_ptr, out_dtype, ldo_bytes, stream))
 
     def run_host(self, x_ptr, ldx_bytes, M, out_ptr, ldo_bytes, stream=None):
         check(lib().b200fc_mlp_run_host(self.h, x_ptr, ldx_bytes, M, out_ptr, ldo_bytes, stream))

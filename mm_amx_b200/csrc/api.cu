@@ -137,6 +137,8 @@ static int to_device(const void* src, int64_t ld, int rows, size_t row_bytes, cu
     return B200FC_OK;
 }
 
+static thread_local int g_mc_reduce = 0;  // set around one matmul_device call by mlp_down_device
+
 static int validate_epilogue(const b200fc_epilogue_t* ep, bool int_acc) {
     if (!ep || !ep->C) { set_error("epilogue / C is null"); return B200FC_ERR_INVALID; }
     const int s = ep->steps;
@@ -174,6 +176,8 @@ int matmul_device(const Weight& w, Weight* w_mut, const void* A, int dtypeA, int
     ep.steps = ep_in->steps; ep.out_dtype = ep_in->out_dtype; ep.C = ep_in->C; ep.ldc = ep_in->ldc_bytes;
     ep.bias = ep_in->bias; ep.deq_scale = ep_in->deq_scale; ep.deq_per_oc = ep_in->deq_scale_per_oc;
     ep.q_scale = ep_in->q_scale; ep.q_per_oc = ep_in->q_scale_per_oc;
+    ep.mc_reduce = g_mc_reduce;
+    if (ep.mc_reduce && M <= 16) { set_error("multicast-reduce output needs the tensor-core path (M > 16)"); return B200FC_ERR_UNSUPPORTED; }
     if (w.compressed) {
         if (!(ep.steps & B200FC_STEP_DEQUANT)) { set_error("matmul: compressed weights need STEP_DEQUANT"); return B200FC_ERR_INVALID; }
         ep.deq_scale = w.deq_scale;          // the weight's scale replaces the caller's (kernels_amx.hpp:1379)
@@ -224,12 +228,15 @@ static int mlp_gate_up_device(Mlp& m, const void* x, int64_t ldx, int M, cudaStr
     return matmul_device(m.gate_up, nullptr, x, B200FC_BF16, M, m.K, ldx, 0, 2 * m.Ns, &e1, s);
 }
 
-static int mlp_down_device(Mlp& m, int M, void* out, int out_dtype, int64_t ldo, cudaStream_t s) {
+static int mlp_down_device(Mlp& m, int M, void* out, int out_dtype, int64_t ldo, cudaStream_t s, int mc_reduce = 0) {
     if (M < 0 || M > m.act_rows) { set_error("mlp_down: no activation of %d rows (gate_up ran %d)", M, m.act_rows); return B200FC_ERR_INVALID; }
     if (M == 0) return B200FC_OK;
     b200fc_epilogue_t e2 = {};
     e2.steps = 0; e2.out_dtype = out_dtype; e2.C = out; e2.ldc_bytes = ldo;
-    return matmul_device(m.down, nullptr, m.act, B200FC_BF16, M, m.Ns, (int64_t)m.Ns * 2, 0, m.K, &e2, s);
+    g_mc_reduce = mc_reduce;
+    int rc = matmul_device(m.down, nullptr, m.act, B200FC_BF16, M, m.Ns, (int64_t)m.Ns * 2, 0, m.K, &e2, s);
+    g_mc_reduce = 0;
+    return rc;
 }
 
 static int mlp_run_device(Mlp& m, const void* x, int64_t ldx, int M, void* out, int out_dtype, int64_t ldo, cudaStream_t s) {
@@ -488,6 +495,13 @@ int b200fc_mlp_down(b200fc_mlp_t* h, int M, void* out, int out_dtype, int64_t ld
     if (!h || !out) { set_error("mlp_down: null pointer"); return B200FC_ERR_INVALID; }
     if (out_dtype != B200FC_F32 && out_dtype != B200FC_BF16) { set_error("mlp_down: out_dtype must be f32 or bf16"); return B200FC_ERR_INVALID; }
     return mlp_down_device(h->m, M, out, out_dtype, ldo, (cudaStream_t)stream);
+}
+
+int b200fc_mlp_down_reduce(b200fc_mlp_t* h, int M, void* multicast_out, int out_dtype, int64_t ldo, void* stream) {
+    if (!h || !multicast_out) { set_error("mlp_down_reduce: null pointer"); return B200FC_ERR_INVALID; }
+    if (out_dtype != B200FC_F32 && out_dtype != B200FC_BF16) { set_error("mlp_down_reduce: out_dtype must be f32 or bf16"); return B200FC_ERR_INVALID; }
+    if (M <= 16) { set_error("mlp_down_reduce: needs M > 16 (decode-shaped batches use mlp_run_partial + an all-reduce)"); return B200FC_ERR_UNSUPPORTED; }
+    return mlp_down_device(h->m, M, multicast_out, out_dtype, ldo, (cudaStream_t)stream, 1);
 }
 
 int b200fc_mlp_run_host(b200fc_mlp_t* h, const void* x, int64_t ldx, int M, void* out, int64_t ldo, void* stream) {

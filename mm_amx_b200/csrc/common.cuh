@@ -44,6 +44,7 @@ struct Epilogue {
     const float* deq_per_oc;
     float q_scale;
     const float* q_per_oc;
+    int mc_reduce = 0;  // 1: C is an NVLink multicast address; the store is a multimem.red.add (in-switch all-reduce)
 };
 
 // Fused Llama MLP object (b200fc_mlp_t)

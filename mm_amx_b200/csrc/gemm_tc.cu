@@ -170,6 +170,48 @@ __device__ __forceinline__ void epilogue_chunk(const unsigned (&r)[32], int m, i
 #pragma unroll
     for (int j = 0; j < 32; j++) v[j] = p.acc_is_int ? (float)(int)r[j] : __uint_as_float(r[j]);
 
+    if (ep.mc_reduce) {
+        // Fused all-reduce: C is a multicast mapping of the output on every GPU of the tensor-parallel group; the
+        // NVSwitch adds this rank's contribution into all replicas (multimem.red), so no separate collective runs.
+        const bool full = p.vec_ok && n + 32 <= p.n1;
+        if (ep.out_dtype == B200FC_F32) {
+            float* dst = (float*)(crow + (long long)n * 4);
+            if (full) {
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    asm volatile("multimem.red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * j),
+                                 "f"(v[4 * j]), "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
+                                 : "memory");
+            } else {
+                for (int j = 0; j < 32; j++)
+                    if (n + j < p.n1) asm volatile("multimem.red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(dst + j), "f"(v[j]) : "memory");
+            }
+        } else {
+            unsigned short* dst = (unsigned short*)(crow + (long long)n * 2);
+            if (full) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    unsigned o[4];
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * j + 2 * q], v[8 * j + 2 * q + 1]);
+                        o[q] = *(unsigned*)&h;
+                    }
+                    asm volatile("multimem.red.relaxed.sys.global.add.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(dst + 8 * j),
+                                 "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                                 : "memory");
+                }
+            } else {
+                for (int j = 0; j < 32; j += 2)   // the launcher guarantees an even column range for this mode
+                    if (n + j + 1 < p.n1) {
+                        __nv_bfloat162 h = __floats2bfloat162_rn(v[j], v[j + 1]);
+                        asm volatile("multimem.red.relaxed.sys.global.add.bf16x2 [%0], %1;" ::"l"(dst + j), "r"(*(unsigned*)&h) : "memory");
+                    }
+            }
+        }
+        return;
+    }
+
     if (ep.steps & B200FC_STEP_SILU_MUL) {
         // columns [0,16) gate, [16,32) up of the same 16 channels -> 16 bf16 outputs at column n/2
         __align__(16) unsigned short o[16];
@@ -754,7 +796,7 @@ int launch_cfg2(const CUtensorMap& ma, const CUtensorMap& mw, GemmParams p, cuda
     // Too few tiles to occupy the GPU (small M): split K so that every pair has work; the raw partial accumulators go
     // through a workspace of this stream and a second kernel sums them in order and runs the post-ops.
     int splits = 1;
-    if (tiles * 2 <= max_pairs && p.k_slabs >= 16) {
+    if (tiles * 2 <= max_pairs && p.k_slabs >= 16 && !p.ep.mc_reduce) {
         splits = max_pairs / tiles;
         if (splits > 8) splits = 8;
         if (splits > p.k_slabs / 8) splits = p.k_slabs / 8;
@@ -846,6 +888,10 @@ int launch_gemm_tc(const void* W_data, int w_dtype, int W_K_pad, int W_N_pad, co
     else
         p.vec_ok = (((uintptr_t)ep.C & 15) == 0 && (ep.ldc & 15) == 0 && ((n0 * es) & 15) == 0) ? 1 : 0;
     if (ep.out_dtype == B200FC_S32 && !i8) { set_error("raw int32 output needs an 8-bit GEMM"); return B200FC_ERR_INVALID; }
+    if (ep.mc_reduce && (ep.steps != 0 || i8 || ((n0 | n1) & 1) || ((uintptr_t)ep.C & 3) || (ep.ldc & 3))) {
+        set_error("multicast-reduce output needs a bf16 GEMM without post-ops and an even, 4-byte aligned column range");
+        return B200FC_ERR_INVALID;
+    }
 
     CUtensorMap ma, mw;
     int rc = make_map(&ma, A, i8, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BM);

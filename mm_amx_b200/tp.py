@@ -99,3 +99,44 @@ class TensorParallelMLP:
         cur.wait_stream(self._comm_stream)
         self._round(partial, out)
         return out
+
+
+class FusedTensorParallelMLP:
+    """Tensor-parallel MLP whose all-reduce happens inside the down-projection kernel.
+
+    The output lives in a torch symmetric-memory buffer that every rank maps through one NVLink multicast (NVLS)
+    address.  The GEMM epilogue adds each rank's contribution into all replicas with `multimem.red`
+    (b200fc_mlp_down_reduce), so the transfer overlaps the math tile by tile and no collective kernel runs.
+    Per step and rank:  zero own replica -> barrier -> gate/up -> down + in-switch reduce -> barrier.
+    Every replica receives every rank's contribution (ingress = world x output bytes), so this pays for small
+    tensor-parallel groups; larger groups use TensorParallelMLP (chunked all-reduce overlapping the GEMMs).
+    Needs M > 16 and a CUDA build of torch with symmetric memory + multicast support.
+    """
+
+    def __init__(self, mlp, K, max_M, group=None, out_dtype=torch.bfloat16):
+        """mlp: capi.Mlp holding this rank's shard (created with tp_rank / tp_size, or from pre-sharded weights)."""
+        import torch.distributed._symmetric_memory as symm_mem
+        self.mlp, self.K, self.max_M = mlp, K, max_M
+        self.group = group if group is not None else dist.group.WORLD
+        self.out_dtype = out_dtype
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.buf = symm_mem.empty((max_M, K), dtype=out_dtype, device=dev)
+        self.handle = symm_mem.rendezvous(self.buf, self.group.group_name)
+        if not self.handle.multicast_ptr:
+            raise RuntimeError("this system offers no NVLink multicast mapping for symmetric memory")
+
+    def forward(self, x):
+        """x [M, K] bf16 CUDA (replicated) -> view of the symmetric buffer [M, K] holding the reduced result.
+        The view is overwritten by the next forward."""
+        M = x.shape[0]
+        if not (16 < M <= self.max_M):
+            raise ValueError("M must be in (16, %d]" % self.max_M)
+        stream = torch.cuda.current_stream().cuda_stream
+        out = self.buf[:M]
+        out.zero_()
+        self.handle.barrier(channel=0)          # every replica is zero before anybody adds into it
+        self.mlp.gate_up(x.data_ptr(), x.stride(0) * 2, M, stream)
+        dt = capi.F32 if self.out_dtype == torch.float32 else capi.BF16
+        self.mlp.down_reduce(M, self.handle.multicast_ptr, dt, self.K * self.buf.element_size(), stream)
+        self.handle.barrier(channel=1)          # all contributions have landed in every replica
+        return out
