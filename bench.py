@@ -206,6 +206,14 @@ def run_ours(args, w, M, name):
                 dt = capi.F32 if oo.dtype == torch.float32 else capi.BF16
                 mlp.run_partial(xx.data_ptr(), H * 2, xx.shape[0], oo.data_ptr(), dt, oo.stride(0) * oo.element_size(),
                                 torch.cuda.current_stream().cuda_stream)
+
+            def gate_up(self, xx):
+                mlp.gate_up(xx.data_ptr(), H * 2, xx.shape[0], torch.cuda.current_stream().cuda_stream)
+
+            def down_rows(self, row0, rows, oo):
+                dt = capi.F32 if oo.dtype == torch.float32 else capi.BF16
+                mlp.down_rows(row0, rows, oo.data_ptr(), dt, oo.stride(0) * oo.element_size(),
+                              torch.cuda.current_stream().cuda_stream)
         if args.tp_mode == "fused":
             fused = tp.FusedTensorParallelMLP(mlp, H, M)
             def step():
@@ -455,7 +463,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=[None] + list(WORKLOADS))
     ap.add_argument("--M", type=int, default=None)
-    ap.add_argument("--chunk-rows", type=int, default=1024)
+    ap.add_argument("--chunk-rows", type=int, default=2048)
     ap.add_argument("--tp-mode", default="nccl", choices=["nccl", "fused"],
                     help="N > 1: 'nccl' = all-reduce in row chunks overlapping the GEMMs, 'fused' = in-switch reduction "
                          "from the down-projection epilogue (multimem.red)")

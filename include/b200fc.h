@@ -133,6 +133,10 @@ int b200fc_mlp_run_partial(b200fc_mlp_t* mlp, const void* x, int64_t ldx_bytes, 
  * Linear::run, :648-704): gate_up writes the internal [M, N/tp] bf16 activation, down consumes it. */
 int b200fc_mlp_gate_up(b200fc_mlp_t* mlp, const void* x, int64_t ldx_bytes, int M, void* stream);
 int b200fc_mlp_down(b200fc_mlp_t* mlp, int M, void* out, int out_dtype, int64_t ldo_bytes, void* stream);
+/* Linear::run on a row range: rows [row0, row0 + rows) of the activation left by the last b200fc_mlp_gate_up ->
+ * out[rows, K] (out points at the first of those rows).  Lets a tensor-parallel caller reduce finished row blocks
+ * while the following ones are still being multiplied. */
+int b200fc_mlp_down_rows(b200fc_mlp_t* mlp, int row0, int rows, void* out, int out_dtype, int64_t ldo_bytes, void* stream);
 /* Down projection fused with the tensor-parallel all-reduce (no reference counterpart; the reference's pairwise
  * split-K reduce, tests/amx-mlp.cpp:656-683, is its single-process ancestor).  `multicast_out` is an NVLink
  * multicast (NVLS) mapping of the [M, K] output that every rank of the group has bound, e.g. the multicast_ptr of a

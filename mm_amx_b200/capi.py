@@ -46,6 +46,7 @@ SIGNATURES = {
     "b200fc_mlp_run_partial": (c_int, [c_void_p, c_void_p, c_i64, c_int, c_void_p, c_int, c_i64, c_void_p]),
     "b200fc_mlp_gate_up": (c_int, [c_void_p, c_void_p, c_i64, c_int, c_void_p]),
     "b200fc_mlp_down": (c_int, [c_void_p, c_int, c_void_p, c_int, c_i64, c_void_p]),
+    "b200fc_mlp_down_rows": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_i64, c_void_p]),
     "b200fc_mlp_down_reduce": (c_int, [c_void_p, c_int, c_void_p, c_int, c_i64, c_void_p]),
     "b200fc_mlp_run_host": (c_int, [c_void_p, c_void_p, c_i64, c_int, c_void_p, c_i64, c_void_p]),
     "b200fc_mlp_run_decode_static": (c_int, [c_void_p, c_void_p, c_i64, c_int, c_void_p, c_int, c_i64, c_void_p]),
@@ -164,6 +165,9 @@ class Mlp:
 
     def down(self, M, out_ptr, out_dtype, ldo_bytes, stream=None):
         check(lib().b200fc_mlp_down(self.h, M, out_ptr, out_dtype, ldo_bytes, stream))
+
+    def down_rows(self, row0, rows, out_ptr, out_dtype, ldo_bytes, stream=None):
+        check(lib().b200fc_mlp_down_rows(self.h, row0, rows, out_ptr, out_dtype, ldo_bytes, stream))
 
     def down_reduce(self, M, multicast_ptr, out_dtype, ldo_bytes, stream=None):
         check(lib().b200fc_mlp_down_reduce(self.h, M, multicast_ptr, out_dtype, ldo_bytes, stream))

@@ -228,13 +228,15 @@ static int mlp_gate_up_device(Mlp& m, const void* x, int64_t ldx, int M, cudaStr
     return matmul_device(m.gate_up, nullptr, x, B200FC_BF16, M, m.K, ldx, 0, 2 * m.Ns, &e1, s);
 }
 
-static int mlp_down_device(Mlp& m, int M, void* out, int out_dtype, int64_t ldo, cudaStream_t s, int mc_reduce = 0) {
-    if (M < 0 || M > m.act_rows) { set_error("mlp_down: no activation of %d rows (gate_up ran %d)", M, m.act_rows); return B200FC_ERR_INVALID; }
+static int mlp_down_device(Mlp& m, int M, void* out, int out_dtype, int64_t ldo, cudaStream_t s, int mc_reduce = 0,
+                           int row0 = 0) {
+    if (M < 0 || row0 < 0 || row0 + M > m.act_rows) { set_error("mlp_down: rows [%d, %d) outside the activation of the last gate_up (%d rows)", row0, row0 + M, m.act_rows); return B200FC_ERR_INVALID; }
     if (M == 0) return B200FC_OK;
     b200fc_epilogue_t e2 = {};
     e2.steps = 0; e2.out_dtype = out_dtype; e2.C = out; e2.ldc_bytes = ldo;
     g_mc_reduce = mc_reduce;
-    int rc = matmul_device(m.down, nullptr, m.act, B200FC_BF16, M, m.Ns, (int64_t)m.Ns * 2, 0, m.K, &e2, s);
+    const char* act = (const char*)m.act + (size_t)row0 * m.Ns * 2;
+    int rc = matmul_device(m.down, nullptr, act, B200FC_BF16, M, m.Ns, (int64_t)m.Ns * 2, 0, m.K, &e2, s);
     g_mc_reduce = 0;
     return rc;
 }
@@ -495,6 +497,12 @@ int b200fc_mlp_down(b200fc_mlp_t* h, int M, void* out, int out_dtype, int64_t ld
     if (!h || !out) { set_error("mlp_down: null pointer"); return B200FC_ERR_INVALID; }
     if (out_dtype != B200FC_F32 && out_dtype != B200FC_BF16) { set_error("mlp_down: out_dtype must be f32 or bf16"); return B200FC_ERR_INVALID; }
     return mlp_down_device(h->m, M, out, out_dtype, ldo, (cudaStream_t)stream);
+}
+
+int b200fc_mlp_down_rows(b200fc_mlp_t* h, int row0, int rows, void* out, int out_dtype, int64_t ldo, void* stream) {
+    if (!h || !out) { set_error("mlp_down_rows: null pointer"); return B200FC_ERR_INVALID; }
+    if (out_dtype != B200FC_F32 && out_dtype != B200FC_BF16) { set_error("mlp_down_rows: out_dtype must be f32 or bf16"); return B200FC_ERR_INVALID; }
+    return mlp_down_device(h->m, rows, out, out_dtype, ldo, (cudaStream_t)stream, 0, row0);
 }
 
 int b200fc_mlp_down_reduce(b200fc_mlp_t* h, int M, void* multicast_out, int out_dtype, int64_t ldo, void* stream) {

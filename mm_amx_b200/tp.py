@@ -47,6 +47,15 @@ class CudaLocalMLP:
         self.mlp.run_partial(x.data_ptr(), x.stride(0) * 2, x.shape[0], out.data_ptr(), dt,
                              out.stride(0) * out.element_size(), torch.cuda.current_stream().cuda_stream)
 
+    def gate_up(self, x):
+        self.mlp.gate_up(x.data_ptr(), x.stride(0) * 2, x.shape[0], torch.cuda.current_stream().cuda_stream)
+
+    def down_rows(self, row0, rows, out):
+        """out [rows, K]: this rank's contribution for rows [row0, row0 + rows) of the last gate_up."""
+        dt = capi.F32 if out.dtype == torch.float32 else capi.BF16
+        self.mlp.down_rows(row0, rows, out.data_ptr(), dt, out.stride(0) * out.element_size(),
+                           torch.cuda.current_stream().cuda_stream)
+
 
 class TensorParallelMLP:
     def __init__(self, local, K, group=None, partial_dtype=torch.float32, chunk_rows=0):
@@ -83,14 +92,21 @@ class TensorParallelMLP:
                 dist.all_reduce(partial, group=self.group)
             self._round(partial, out)
             return out
-        # chunked: compute chunk i+1 on the current stream while NCCL reduces chunk i on a side stream
+        # chunked: the collective of finished rows runs on a side stream while the following rows are multiplied.
+        # When the local object can run the two stages separately, gate/up runs once over all rows (full GEMM waves)
+        # and only the down projection is cut into row blocks; otherwise whole forwards are chunked.
         if self._comm_stream is None:
             self._comm_stream = torch.cuda.Stream()
         cur = torch.cuda.current_stream()
-        works = []
+        staged = hasattr(self.local, "gate_up") and hasattr(self.local, "down_rows")
+        if staged:
+            self.local.gate_up(x)
         for m0 in range(0, M, chunk):
             m1 = min(M, m0 + chunk)
-            self.local.run_partial(x[m0:m1], partial[m0:m1])
+            if staged:
+                self.local.down_rows(m0, m1 - m0, partial[m0:m1])
+            else:
+                self.local.run_partial(x[m0:m1], partial[m0:m1])
             ev = torch.cuda.Event()
             ev.record(cur)
             with torch.cuda.stream(self._comm_stream):
