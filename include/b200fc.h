@@ -67,6 +67,10 @@ const char* b200fc_version(void);
 /* number of this library's kernels launched by the calling process so far (bench bookkeeping) */
 int64_t b200fc_launch_count(void);
 
+/* Limits the persistent GEMM kernels to `sms` SMs (0 = all).  A tensor-parallel caller that overlaps an NCCL
+ * all-reduce with the GEMMs leaves the collective a few SMs this way; otherwise its CTAs queue behind the GEMM's. */
+int b200fc_set_sm_limit(int sms);
+
 /* waits for `stream` and reports whether any kernel of this library gave up on a bounded wait since the last check
  * (B200FC_ERR_KERNEL); the _host entry points do this themselves */
 int b200fc_sync_check(void* stream);

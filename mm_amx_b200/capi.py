@@ -26,6 +26,7 @@ SIGNATURES = {
     "b200fc_version": (ctypes.c_char_p, []),
     "b200fc_launch_count": (c_i64, []),
     "b200fc_sync_check": (c_int, [c_void_p]),
+    "b200fc_set_sm_limit": (c_int, [c_int]),
     "b200fc_weight_pack": (c_int, [c_void_p, c_int, c_int, c_int, c_i64, c_int, c_int, c_void_p,
                                    ctypes.POINTER(c_void_p), c_void_p]),
     "b200fc_weight_free": (c_int, [c_void_p]),
@@ -93,6 +94,10 @@ def last_error():
 
 def launch_count():
     return lib().b200fc_launch_count()
+
+
+def set_sm_limit(sms):
+    check(lib().b200fc_set_sm_limit(sms))
 
 
 def sync_check(stream=None):

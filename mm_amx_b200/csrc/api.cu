@@ -27,6 +27,9 @@ int cuda_fail(cudaError_t e, const char* what) {
 }
 void count_launch(int n) { g_launches += n; }
 
+static std::atomic<int> g_sm_limit{0};
+int sm_limit() { return g_sm_limit.load(); }
+
 static std::mutex g_mu;
 static std::map<int, int*> g_status;  // per device
 
@@ -257,6 +260,12 @@ extern "C" {
 const char* b200fc_last_error(void) { return g_err; }
 const char* b200fc_version(void) { return "b200fc 0.1 (sm_100a)"; }
 int64_t b200fc_launch_count(void) { return (int64_t)g_launches.load(); }
+
+int b200fc_set_sm_limit(int sms) {
+    if (sms < 0) { set_error("set_sm_limit: negative"); return B200FC_ERR_INVALID; }
+    g_sm_limit = sms;
+    return B200FC_OK;
+}
 
 int b200fc_sync_check(void* stream) { return check_kernel_status((cudaStream_t)stream); }
 

@@ -62,6 +62,9 @@ struct Mlp {
     std::vector<cudaEvent_t> ev_in, ev_out;
 };
 
+// SM budget of the persistent GEMM grids (0 = all SMs); set through b200fc_set_sm_limit
+int sm_limit();
+
 // error plumbing (api.cu)
 void set_error(const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);

@@ -762,7 +762,9 @@ int num_sms() {
         cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
         if (n <= 0) n = 148;
     }
-    return n;
+    // the persistent GEMM grids take one CTA per SM; a caller that overlaps a collective with them leaves it a few SMs
+    const int lim = sm_limit();
+    return (lim >= 2 && lim < n) ? (lim & ~1) : n;
 }
 
 template <int BN, bool I8>
