@@ -218,6 +218,10 @@ def run_ours(args, w, M, name):
             fused = tp.FusedTensorParallelMLP(mlp, H, M)
             def step():
                 fused.forward(x)
+        elif args.tp_mode == "pull":
+            pull = tp.PullFusedTensorParallelMLP(mlp, H, M, comm_sms=args.comm_sms)
+            def step():
+                pull.forward(x)
         else:
             tpm = tp.TensorParallelMLP(Local(), H, partial_dtype=torch.bfloat16, chunk_rows=args.chunk_rows)
             def step():
@@ -464,9 +468,10 @@ def main():
     ap.add_argument("--workload", default=None, choices=[None] + list(WORKLOADS))
     ap.add_argument("--M", type=int, default=None)
     ap.add_argument("--chunk-rows", type=int, default=2048)
-    ap.add_argument("--tp-mode", default="nccl", choices=["nccl", "fused"],
+    ap.add_argument("--tp-mode", default="nccl", choices=["nccl", "fused", "pull"],
                     help="N > 1: 'nccl' = all-reduce in row chunks overlapping the GEMMs, 'fused' = in-switch reduction "
                          "from the down-projection epilogue (multimem.red)")
+    ap.add_argument("--comm-sms", type=int, default=16)
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--legs", default="kernel,e2e,decode,configs,cpu",
                     help="optional legs after the main timed loop (comma list of kernel,e2e,decode,configs,cpu; '' = none)")

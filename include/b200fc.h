@@ -148,6 +148,30 @@ int b200fc_mlp_down_rows(b200fc_mlp_t* mlp, int row0, int rows, void* out, int o
  * multimem.red, so no separate collective runs.  The caller zeroes the replicas and separates steps with a
  * cross-rank barrier (see mm_amx_b200/tp.py).  Needs M > 16; split-K shapes are not supported. */
 int b200fc_mlp_down_reduce(b200fc_mlp_t* mlp, int M, void* multicast_out, int out_dtype, int64_t ldo_bytes, void* stream);
+/* Down projection with the tensor-parallel all-reduce done by the same kernel, pull style (no reference
+ * counterpart).  Three symmetric buffers are shared by the ranks of the group (e.g. torch symmetric memory):
+ * `partial` and `out`, both [>= M, K] bf16 with row pitch ld_bytes, each also mapped through an NVLink multicast
+ * address, and one array of 32-bit arrival counters per rank.  Most CTA pairs multiply and store this rank's tile
+ * into its `partial` replica, then bump the tile's counter on the tile's owner (tile index % world); the last
+ * `comm_sms` SMs of the grid wait for the tiles this rank owns, pull them from all replicas with
+ * multimem.ld_reduce (summed in the switch, fp32 accumulation) and write the sum to every rank's `out` with
+ * multimem.st.  Each contribution crosses NVLink once and the transfer overlaps the multiplication of later tiles.
+ * Contract: the counters the call uses are zero when it starts on any rank; after the call every rank passes a
+ * cross-rank barrier before `out` is read, `partial` is rewritten or the counters are cleared (mm_amx_b200/tp.py
+ * alternates two counter arrays so that one barrier per step suffices).  Needs M > 16, K % 8 == 0, 2 <= world <= 8,
+ * and a GPU not shared with other kernels (the whole grid must be resident).  Waits are bounded (B200FC_ERR_KERNEL
+ * at the next b200fc_sync_check). */
+typedef struct {
+    int world, rank;
+    void* partial_local;     /* this rank's replica of `partial` */
+    const void* partial_mc;  /* multicast address of `partial` */
+    void* out_mc;            /* multicast address of `out` */
+    int64_t ld_bytes;
+    uint32_t* flags[8];      /* flags[r]: counter array of rank r as mapped on this GPU */
+    int max_tiles;           /* entries per counter array; a call uses ceil(M/256) * ceil(K/256) of them */
+    int comm_sms;            /* SMs that reduce instead of multiplying (even, e.g. 16) */
+} b200fc_allreduce_t;
+int b200fc_mlp_down_allreduce(b200fc_mlp_t* mlp, int M, const b200fc_allreduce_t* ar, void* stream);
 /* x and out in HOST memory; copies, runs, copies back, synchronises. */
 int b200fc_mlp_run_host(b200fc_mlp_t* mlp, const void* x, int64_t ldx_bytes, int M, void* out, int64_t ldo_bytes,
                         void* stream);

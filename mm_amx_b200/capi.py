@@ -20,6 +20,13 @@ class Epilogue(ctypes.Structure):
                 ("q_scale_per_oc", c_void_p)]
 
 
+class AllReduce(ctypes.Structure):
+    """b200fc_allreduce_t"""
+    _fields_ = [("world", c_int), ("rank", c_int), ("partial_local", c_void_p), ("partial_mc", c_void_p),
+                ("out_mc", c_void_p), ("ld_bytes", c_i64), ("flags", c_void_p * 8), ("max_tiles", c_int),
+                ("comm_sms", c_int)]
+
+
 # name -> (restype, argtypes); every symbol include/b200fc.h declares
 SIGNATURES = {
     "b200fc_last_error": (ctypes.c_char_p, []),
@@ -49,6 +56,7 @@ SIGNATURES = {
     "b200fc_mlp_down": (c_int, [c_void_p, c_int, c_void_p, c_int, c_i64, c_void_p]),
     "b200fc_mlp_down_rows": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_i64, c_void_p]),
     "b200fc_mlp_down_reduce": (c_int, [c_void_p, c_int, c_void_p, c_int, c_i64, c_void_p]),
+    "b200fc_mlp_down_allreduce": (c_int, [c_void_p, c_int, ctypes.POINTER(AllReduce), c_void_p]),
     "b200fc_mlp_run_host": (c_int, [c_void_p, c_void_p, c_i64, c_int, c_void_p, c_i64, c_void_p]),
     "b200fc_mlp_run_decode_static": (c_int, [c_void_p, c_void_p, c_i64, c_int, c_void_p, c_int, c_i64, c_void_p]),
     "b200fc_mlp_decode_static_capacity": (c_i64, []),
@@ -176,6 +184,10 @@ class Mlp:
 
     def down_reduce(self, M, multicast_ptr, out_dtype, ldo_bytes, stream=None):
         check(lib().b200fc_mlp_down_reduce(self.h, M, multicast_ptr, out_dtype, ldo_bytes, stream))
+
+    def down_allreduce(self, M, ar, stream=None):
+        """ar: capi.AllReduce; see b200fc_mlp_down_allreduce in include/b200fc.h."""
+        check(lib().b200fc_mlp_down_allreduce(self.h, M, ctypes.byref(ar), stream))
 
     def run_host(self, x_ptr, ldx_bytes, M, out_ptr, ldo_bytes, stream=None):
         check(lib().b200fc_mlp_run_host(self.h, x_ptr, ldx_bytes, M, out_ptr, ldo_bytes, stream))

@@ -521,6 +521,24 @@ int b200fc_mlp_down_reduce(b200fc_mlp_t* h, int M, void* multicast_out, int out_
     return mlp_down_device(h->m, M, multicast_out, out_dtype, ldo, (cudaStream_t)stream, 1);
 }
 
+int b200fc_mlp_down_allreduce(b200fc_mlp_t* h, int M, const b200fc_allreduce_t* ar, void* stream) {
+    if (!h || !ar || !ar->partial_local || !ar->partial_mc || !ar->out_mc) { set_error("mlp_down_allreduce: null pointer"); return B200FC_ERR_INVALID; }
+    Mlp& m = h->m;
+    if (M <= 16) { set_error("mlp_down_allreduce: needs M > 16 (decode-shaped batches use mlp_run_partial + an all-reduce)"); return B200FC_ERR_UNSUPPORTED; }
+    if (M > m.act_rows) { set_error("mlp_down_allreduce: no activation of %d rows (gate_up ran %d)", M, m.act_rows); return B200FC_ERR_INVALID; }
+    AllReduceDesc d;
+    d.world = ar->world; d.rank = ar->rank;
+    d.partial_local = ar->partial_local; d.partial_mc = ar->partial_mc; d.out_mc = ar->out_mc;
+    d.ld_bytes = ar->ld_bytes;
+    for (int i = 0; i < 8; i++) {
+        d.flags[i] = (i < ar->world) ? ar->flags[i] : nullptr;
+        if (i < ar->world && !ar->flags[i]) { set_error("mlp_down_allreduce: missing counter array of rank %d", i); return B200FC_ERR_INVALID; }
+    }
+    d.max_tiles = ar->max_tiles; d.comm_sms = ar->comm_sms;
+    return launch_gemm_tc_allreduce(m.down.data, m.down.K_pad, m.down.N_pad, m.act, M, m.Ns, (int64_t)m.Ns * 2, m.K, d,
+                                    (cudaStream_t)stream);
+}
+
 int b200fc_mlp_run_host(b200fc_mlp_t* h, const void* x, int64_t ldx, int M, void* out, int64_t ldo, void* stream) {
     cudaStream_t s = (cudaStream_t)stream;
     if (!h || !x || !out || M <= 0) { set_error("mlp_run_host: null pointer or M <= 0"); return B200FC_ERR_INVALID; }

@@ -109,6 +109,19 @@ int launch_gemv_tma(const Weight& w, const void* A, int M, int K, int64_t lda, i
 // gemm_tc.cu: tcgen05 GEMM, bf16 x bf16 -> fp32 or 8-bit x 8-bit -> int32
 int launch_gemm_tc(const void* W_data, int w_dtype, int W_K_pad, int W_N_pad, const void* A, int dtypeA, int M, int K,
                    int64_t lda, int n0, int n1, const Epilogue& ep, cudaStream_t s);
+// gemm_tc.cu: bf16 GEMM whose output is all-reduced over a tensor-parallel group inside the kernel
+struct AllReduceDesc {
+    int world, rank;
+    void* partial_local;      // this rank's replica of the symmetric partial buffer [M, N] bf16
+    const void* partial_mc;   // multicast address of all replicas of it
+    void* out_mc;             // multicast address of all replicas of the output buffer [M, N] bf16
+    int64_t ld_bytes;         // row pitch of both buffers
+    unsigned* flags[8];       // per rank: arrival counters, one per tile, zero before the call
+    int max_tiles;            // length of the counter arrays
+    int comm_sms;             // SMs given to the reducing role
+};
+int launch_gemm_tc_allreduce(const void* W_data, int W_K_pad, int W_N_pad, const void* A, int M, int K, int64_t lda,
+                             int N, const AllReduceDesc& ar, cudaStream_t s);
 // matvec.cu
 int launch_matvec(const void* A, int dtype, int M, int K, int64_t lda, const void* b, void* c, cudaStream_t s);
 

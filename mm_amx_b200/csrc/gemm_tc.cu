@@ -53,6 +53,15 @@ struct GemmParams {
     // slab `split` of a workspace ([splits][M][row pitch]) and a second kernel reduces and runs the post-ops
     int splits;
     long long split_stride;  // bytes between workspace slabs
+    // Fused tensor-parallel all-reduce (2-CTA kernel, ar_world > 0).  The epilogue stores this rank's bf16 tile into
+    // its replica of a symmetric "partial" buffer (ep.C) and bumps the tile's arrival counter on the tile's owner
+    // rank; the last CTA pairs of the grid do not multiply but reduce the tiles this rank owns.
+    int ar_world, ar_rank;
+    int ar_gemm_pairs;          // pairs that multiply; pairs beyond reduce
+    unsigned ar_target;         // arrivals that mean "every rank has stored this tile" (world x 8 epilogue warps)
+    unsigned* ar_flags[8];      // ar_flags[r]: arrival counters of rank r (peer-mapped), one per tile
+    const char* ar_partial_mc;  // multicast address of all replicas of the partial buffer
+    char* ar_out_mc;            // multicast address of all replicas of the output buffer
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------------------------
@@ -514,6 +523,8 @@ __device__ __forceinline__ void tc_mma_pair(unsigned d_tmem, unsigned long long 
     }
 }
 
+constexpr int AR_UNROLL = 8;
+
 template <int BN, bool I8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
@@ -532,7 +543,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const unsigned rank = cluster_ctarank();
     const bool leader = rank == 0;
-    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int pair = blockIdx.x >> 1, grid_pairs = gridDim.x >> 1;
+    const int num_pairs = p.ar_world ? p.ar_gemm_pairs : grid_pairs;  // pairs that take part in the multiplication
+    const bool comm_role = p.ar_world && pair >= num_pairs;
     const int num_tiles = p.tiles_m * p.tiles_n;  // tiles of 256 x BN
     const int num_items = num_tiles * p.splits;   // (tile, K split) work items
 
@@ -560,7 +573,62 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     tc_fence_after();
     const unsigned tmem_base = *tmem_holder;
 
-    if (warp == 0) {
+    if (comm_role) {
+        // ---------------- all-reduce role (whole CTA) ----------------
+        // Tile t belongs to rank t % world.  Once every rank has stored its bf16 contribution for an owned tile
+        // (arrival counter reached), the tile is pulled from all replicas with multimem.ld_reduce — the NVSwitch adds
+        // them, accumulating in fp32 — and the sum is written to every rank's output with multimem.st.  So each
+        // contribution crosses NVLink once, while the multiplying pairs are already busy with later tiles.
+        const int n_comm = 2 * (grid_pairs - num_pairs);
+        const int me = (pair - num_pairs) * 2 + (int)rank;
+        const unsigned* my_flags = p.ar_flags[p.ar_rank];
+        int owned = 0;
+        for (int tile = p.ar_rank; tile < num_tiles; tile += p.ar_world, owned++) {
+            if (owned % n_comm != me) continue;
+            if (threadIdx.x == 0) {
+                const unsigned long long t0 = globaltimer();
+                while (true) {
+                    unsigned v;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(my_flags + tile) : "memory");
+                    if (v >= p.ar_target) break;
+                    if (globaltimer() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; break; }
+                }
+            }
+            __syncthreads();
+            if (*abort_flag) break;
+            asm volatile("fence.acq_rel.sys;" ::: "memory");
+            const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+            const int r0 = tm * (2 * BM), c0 = p.n0 + tn * BN;
+            const int rows = min(2 * BM, p.M - r0), cols = min(BN, p.n1 - c0);
+            const int ppr = cols >> 3;  // 16-byte pieces (8 bf16) per row
+            const int total = rows * ppr;
+            // AR_UNROLL independent reductions in flight per thread: one round trip through the switch takes
+            // microseconds, so the pull is latency-bound unless many are outstanding.
+            for (int base = threadIdx.x; base < total; base += NUM_THREADS * AR_UNROLL) {
+                unsigned v[AR_UNROLL][4];
+                long long off[AR_UNROLL];
+#pragma unroll
+                for (int u = 0; u < AR_UNROLL; u++) {
+                    const int i = base + u * NUM_THREADS;
+                    const int row = i / ppr, pc = i - row * ppr;
+                    off[u] = (long long)(r0 + row) * p.ep.ldc + (long long)(c0 + pc * 8) * 2;
+                    if (i < total)
+                        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(v[u][0]), "=r"(v[u][1]), "=r"(v[u][2]), "=r"(v[u][3])
+                                     : "l"(p.ar_partial_mc + off[u])
+                                     : "memory");
+                }
+#pragma unroll
+                for (int u = 0; u < AR_UNROLL; u++) {
+                    const int i = base + u * NUM_THREADS;
+                    if (i < total)
+                        asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(p.ar_out_mc + off[u]),
+                                     "r"(v[u][0]), "r"(v[u][1]), "r"(v[u][2]), "r"(v[u][3])
+                                     : "memory");
+                }
+            }
+        }
+    } else if (warp == 0) {
         // ---------------- TMA producer (one per CTA) ----------------
         if (lane == 0) {
             int stage = 0;
@@ -646,8 +714,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 epilogue_chunk(r, m, n, p, row_ok, c_offset);
             }
             tc_fence_before();
+            if (p.ar_world) __threadfence_system();  // this warp's part of the tile is visible to every GPU ...
             __syncwarp();
-            if (lane == 0) mbar_arrive_remote(leader_acc_empty + 8 * ab);
+            if (lane == 0) {
+                mbar_arrive_remote(leader_acc_empty + 8 * ab);
+                if (p.ar_world)                      // ... before the tile's owner counts the arrival
+                    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.ar_flags[tile % p.ar_world] + tile), "r"(1u)
+                                 : "memory");
+            }
         }
     }
 
@@ -854,6 +928,57 @@ int forced_ctas() {
 
 }  // namespace
 
+int launch_gemm_tc_allreduce(const void* W_data, int W_K_pad, int W_N_pad, const void* A, int M, int K, int64_t lda,
+                             int N, const AllReduceDesc& ar, cudaStream_t s) {
+    if (((uintptr_t)A & 15) || (lda & 15)) { set_error("gemm allreduce: A must be 16-byte aligned"); return B200FC_ERR_INVALID; }
+    if (ar.world < 2 || ar.world > 8 || ar.rank < 0 || ar.rank >= ar.world) { set_error("gemm allreduce: bad rank / world"); return B200FC_ERR_INVALID; }
+    if ((N & 7) || (ar.ld_bytes & 15) || ((uintptr_t)ar.partial_local & 15) || ((uintptr_t)ar.partial_mc & 15) || ((uintptr_t)ar.out_mc & 15)) {
+        set_error("gemm allreduce: N must be a multiple of 8 and the buffers 16-byte aligned");
+        return B200FC_ERR_INVALID;
+    }
+    if (M <= 0) return B200FC_OK;
+    GemmParams p;
+    p.M = M; p.K = K; p.n0 = 0; p.n1 = N;
+    p.tiles_m = (M + 2 * BM - 1) / (2 * BM);
+    p.tiles_n = (N + 255) / 256;
+    if (p.tiles_m * p.tiles_n > ar.max_tiles) { set_error("gemm allreduce: %d tiles exceed the flag array (%d)", p.tiles_m * p.tiles_n, ar.max_tiles); return B200FC_ERR_INVALID; }
+    p.k_slabs = (K + 63) / 64;
+    p.idesc = make_idesc(false, false, false, 256, 2 * BM);
+    p.acc_is_int = 0;
+    p.ep.steps = 0; p.ep.out_dtype = B200FC_BF16; p.ep.C = ar.partial_local; p.ep.ldc = ar.ld_bytes;
+    p.ep.bias = nullptr; p.ep.deq_scale = 1.0f; p.ep.deq_per_oc = nullptr; p.ep.q_scale = 1.0f; p.ep.q_per_oc = nullptr;
+    p.ep.mc_reduce = 0;
+    p.vec_ok = 1;
+    p.status = kernel_status_word();
+    p.splits = 1; p.split_stride = 0;
+    p.ar_world = ar.world; p.ar_rank = ar.rank;
+    const int all_pairs = num_sms() / 2;
+    int comm_pairs = ar.comm_sms / 2;
+    if (comm_pairs < 1) comm_pairs = 1;
+    if (comm_pairs > all_pairs / 2) comm_pairs = all_pairs / 2;
+    p.ar_gemm_pairs = all_pairs - comm_pairs;
+    p.ar_target = (unsigned)ar.world * 8u;
+    for (int i = 0; i < 8; i++) p.ar_flags[i] = i < ar.world ? ar.flags[i] : nullptr;
+    p.ar_partial_mc = (const char*)ar.partial_mc;
+    p.ar_out_mc = (char*)ar.out_mc;
+    CUtensorMap ma, mw;
+    int rc = make_map(&ma, A, false, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BM);
+    if (rc) return rc;
+    rc = make_map(&mw, W_data, false, (uint64_t)W_K_pad, (uint64_t)W_N_pad, (uint64_t)W_K_pad * 2, 128);
+    if (rc) return rc;
+    using C = Cfg2<256>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        B200FC_CUDA(cudaFuncSetAttribute(gemm_tc2_kernel<256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+        attr_done = true;
+    }
+    // the whole grid must be resident (reducing pairs wait for multiplying pairs of every GPU): one CTA per SM
+    gemm_tc2_kernel<256, false><<<2 * all_pairs, NUM_THREADS, C::SMEM_BYTES, s>>>(ma, mw, p);
+    count_launch();
+    B200FC_CUDA(cudaGetLastError());
+    return B200FC_OK;
+}
+
 int launch_gemm_tc(const void* W_data, int w_dtype, int W_K_pad, int W_N_pad, const void* A, int dtypeA, int M, int K,
                    int64_t lda, int n0, int n1, const Epilogue& ep, cudaStream_t s) {
     const bool i8 = dtypeA != B200FC_BF16;
@@ -884,6 +1009,8 @@ int launch_gemm_tc(const void* W_data, int w_dtype, int W_K_pad, int W_N_pad, co
     p.ep = ep;
     p.status = kernel_status_word();
     p.splits = 1; p.split_stride = 0;
+    p.ar_world = 0; p.ar_rank = 0; p.ar_gemm_pairs = 0; p.ar_target = 0; p.ar_partial_mc = nullptr; p.ar_out_mc = nullptr;
+    for (int i = 0; i < 8; i++) p.ar_flags[i] = nullptr;
     int es = ep.out_dtype == B200FC_F32 || ep.out_dtype == B200FC_S32 ? 4 : (ep.out_dtype == B200FC_BF16 ? 2 : 1);
     if (ep.steps & B200FC_STEP_SILU_MUL)
         p.vec_ok = (((uintptr_t)ep.C & 15) == 0 && (ep.ldc & 15) == 0 && (n0 % 32) == 0) ? 1 : 0;

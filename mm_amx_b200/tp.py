@@ -156,3 +156,59 @@ class FusedTensorParallelMLP:
         self.mlp.down_reduce(M, self.handle.multicast_ptr, dt, self.K * self.buf.element_size(), stream)
         self.handle.barrier(channel=1)          # all contributions have landed in every replica
         return out
+
+
+class PullFusedTensorParallelMLP:
+    """Tensor-parallel MLP whose all-reduce is done by the down-projection kernel itself, pull style
+    (b200fc_mlp_down_allreduce): multiplying CTA pairs store bf16 tiles into a symmetric partial buffer and signal the
+    tile's owner; a few SMs of the same grid pull finished tiles from all ranks with multimem.ld_reduce (summed in the
+    NVSwitch) and multicast the sums into every rank's output with multimem.st.  One symmetric-memory barrier per step.
+    """
+
+    MAX_TILES = 8192
+
+    def __init__(self, mlp, K, max_M, group=None, comm_sms=16):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.mlp, self.K, self.max_M, self.comm_sms = mlp, K, max_M, comm_sms
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        name = self.group.group_name
+        self.partial = symm_mem.empty((max_M, K), dtype=torch.bfloat16, device=dev)
+        self.out = symm_mem.empty((max_M, K), dtype=torch.bfloat16, device=dev)
+        self.flags = symm_mem.empty((2, self.MAX_TILES), dtype=torch.int32, device=dev)  # two arrays, used alternately
+        self.h_partial = symm_mem.rendezvous(self.partial, name)
+        self.h_out = symm_mem.rendezvous(self.out, name)
+        self.h_flags = symm_mem.rendezvous(self.flags, name)
+        if not (self.h_partial.multicast_ptr and self.h_out.multicast_ptr):
+            raise RuntimeError("this system offers no NVLink multicast mapping for symmetric memory")
+        self.flags.zero_()
+        torch.cuda.synchronize()
+        self.h_flags.barrier(channel=0)
+        self.parity = 0
+
+    def forward(self, x):
+        """x [M, K] bf16 CUDA (replicated) -> view [M, K] of the symmetric output buffer (valid until the next call)."""
+        M = x.shape[0]
+        if not (16 < M <= self.max_M):
+            raise ValueError("M must be in (16, %d]" % self.max_M)
+        stream = torch.cuda.current_stream().cuda_stream
+        p = self.parity
+        # Clear the counters of the NEXT step now: nobody signals them before the barrier that ends this step, and this
+        # rank passes that barrier only after this memset.
+        self.flags[1 - p].zero_()
+        self.mlp.gate_up(x.data_ptr(), x.stride(0) * 2, M, stream)
+        ar = capi.AllReduce()
+        ar.world, ar.rank = self.world, self.rank
+        ar.partial_local = self.partial.data_ptr()
+        ar.partial_mc = self.h_partial.multicast_ptr
+        ar.out_mc = self.h_out.multicast_ptr
+        ar.ld_bytes = self.K * 2
+        for r in range(self.world):
+            ar.flags[r] = self.h_flags.buffer_ptrs[r] + p * self.MAX_TILES * 4
+        ar.max_tiles = self.MAX_TILES
+        ar.comm_sms = self.comm_sms
+        self.mlp.down_allreduce(M, ar, stream)
+        self.h_out.barrier(channel=1)   # every rank's tiles have been reduced and multicast
+        self.parity = 1 - p
+        return self.out[:M]

@@ -60,6 +60,23 @@ def worker(rank, world, port_no, results):
             torch.cuda.synchronize()
             got = (bits(out).astype(np.uint32) << 16).view(np.float32)
             errs.append(float(np.abs(got - ref_f).max() / np.abs(ref_f).max()))
+    # the all-reduce done by reducing CTAs of the down-projection grid (pull: multimem.ld_reduce + multimem.st)
+    try:
+        pull = tp.PullFusedTensorParallelMLP(local.mlp, K, 600, comm_sms=8)
+    except Exception as ex:
+        pull = None
+        if rank == 0:
+            print("pull-fused path unavailable:", ex)
+    if pull is not None:
+        for M in (300, 64, 600):
+            x = torch.randn(M, K).to(torch.bfloat16)
+            ref = port.mlp(bits(x), bits(gate), bits(up), bits(down))
+            ref_f = (ref.astype(np.uint32) << 16).view(np.float32)
+            for _ in range(3):      # three steps: both counter arrays get reused
+                out = pull.forward(x.cuda())
+            capi.sync_check()
+            got = (bits(out).astype(np.uint32) << 16).view(np.float32)
+            errs.append(float(np.abs(got - ref_f).max() / np.abs(ref_f).max()))
     results[rank] = errs
     dist.barrier()
     dist.destroy_process_group()
