@@ -168,7 +168,7 @@ typedef struct {
     void* out_mc;            /* multicast address of `out` */
     int64_t ld_bytes;
     uint32_t* flags[8];      /* flags[r]: counter array of rank r as mapped on this GPU */
-    int max_tiles;           /* entries per counter array; a call uses ceil(M/256) * ceil(K/256) of them */
+    int max_tiles;           /* entries per counter array; a call uses 2 * ceil(M/256) * ceil(K/256) of them */
     int comm_sms;            /* SMs that reduce instead of multiplying (even, e.g. 16) */
 } b200fc_allreduce_t;
 int b200fc_mlp_down_allreduce(b200fc_mlp_t* mlp, int M, const b200fc_allreduce_t* ar, void* stream);

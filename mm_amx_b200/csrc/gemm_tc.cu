@@ -57,9 +57,10 @@ struct GemmParams {
     // its replica of a symmetric "partial" buffer (ep.C) and bumps the tile's arrival counter on the tile's owner
     // rank; the last CTA pairs of the grid do not multiply but reduce the tiles this rank owns.
     int ar_world, ar_rank;
+    int ar_phases;              // bit 0: multiply, bit 1: reduce (both set in normal use; single bits for measurements)
     int ar_gemm_pairs;          // pairs that multiply; pairs beyond reduce
-    unsigned ar_target;         // arrivals that mean "every rank has stored this tile" (world x 8 epilogue warps)
-    unsigned* ar_flags[8];      // ar_flags[r]: arrival counters of rank r (peer-mapped), one per tile
+    unsigned ar_target;         // arrivals that mean "every rank has stored these 128 rows of the tile" (world x 4 epilogue warps)
+    unsigned* ar_flags[8];      // ar_flags[r]: arrival counters of rank r (peer-mapped), two per tile (one per CTA of the pair)
     const char* ar_partial_mc;  // multicast address of all replicas of the partial buffer
     char* ar_out_mc;            // multicast address of all replicas of the output buffer
 };
@@ -523,7 +524,7 @@ __device__ __forceinline__ void tc_mma_pair(unsigned d_tmem, unsigned long long 
     }
 }
 
-constexpr int AR_UNROLL = 8;
+constexpr int AR_UNROLL = 22;  // 192 threads x 22 pieces cover the 4096 pieces of a 128 x 256 bf16 unit
 
 template <int BN, bool I8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
@@ -573,7 +574,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     tc_fence_after();
     const unsigned tmem_base = *tmem_holder;
 
-    if (comm_role) {
+    if (comm_role && !(p.ar_phases & 2)) {
+    } else if (!comm_role && p.ar_world && !(p.ar_phases & 1)) {
+    } else if (comm_role) {
         // ---------------- all-reduce role (whole CTA) ----------------
         // Tile t belongs to rank t % world.  Once every rank has stored its bf16 contribution for an owned tile
         // (arrival counter reached), the tile is pulled from all replicas with multimem.ld_reduce — the NVSwitch adds
@@ -582,51 +585,58 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int n_comm = 2 * (grid_pairs - num_pairs);
         const int me = (pair - num_pairs) * 2 + (int)rank;
         const unsigned* my_flags = p.ar_flags[p.ar_rank];
-        int owned = 0;
-        for (int tile = p.ar_rank; tile < num_tiles; tile += p.ar_world, owned++) {
-            if (owned % n_comm != me) continue;
-            if (threadIdx.x == 0) {
-                const unsigned long long t0 = globaltimer();
-                while (true) {
-                    unsigned v;
-                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(my_flags + tile) : "memory");
-                    if (v >= p.ar_target) break;
-                    if (globaltimer() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; break; }
+        // Unit of work: the 128 rows of a tile that one CTA of a multiplying pair produced (own arrival counter).  A
+        // whole unit (<= 4096 16-byte pieces) is in flight at once — AR_UNROLL reductions per thread — because one
+        // round trip through the switch takes microseconds and tiles become ready in bursts, a wave at a time.
+        int q = 0;
+        for (int tile = p.ar_rank; tile < num_tiles; tile += p.ar_world) {
+            for (int half = 0; half < 2; half++, q++) {
+                if (q % n_comm != me) continue;
+                const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+                const int r0 = tm * (2 * BM) + half * BM, c0 = p.n0 + tn * BN;
+                const int rows = min(BM, p.M - r0), cols = min(BN, p.n1 - c0);
+                if (rows <= 0) continue;
+                if (threadIdx.x == 0) {
+                    const unsigned long long t0 = globaltimer();
+                    while (true) {
+                        unsigned v;
+                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(my_flags + 2 * tile + half) : "memory");
+                        if (v >= p.ar_target) break;
+                        if (globaltimer() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; break; }
+                    }
+                }
+                __syncthreads();
+                if (*abort_flag) break;
+                asm volatile("fence.acq_rel.sys;" ::: "memory");
+                const int ppr = cols >> 3;  // 16-byte pieces (8 bf16) per row
+                const int total = rows * ppr;
+                const long long base_off = (long long)r0 * p.ep.ldc + (long long)c0 * 2;
+                for (int base = threadIdx.x; base < total; base += NUM_THREADS * AR_UNROLL) {
+                    unsigned v[AR_UNROLL][4];
+#pragma unroll
+                    for (int u = 0; u < AR_UNROLL; u++) {
+                        const int i = base + u * NUM_THREADS;
+                        const int row = i / ppr, pc = i - row * ppr;
+                        const long long off = base_off + (long long)row * p.ep.ldc + pc * 16;
+                        if (i < total)
+                            asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                                         : "=r"(v[u][0]), "=r"(v[u][1]), "=r"(v[u][2]), "=r"(v[u][3])
+                                         : "l"(p.ar_partial_mc + off)
+                                         : "memory");
+                    }
+#pragma unroll
+                    for (int u = 0; u < AR_UNROLL; u++) {
+                        const int i = base + u * NUM_THREADS;
+                        const int row = i / ppr, pc = i - row * ppr;
+                        const long long off = base_off + (long long)row * p.ep.ldc + pc * 16;
+                        if (i < total)
+                            asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(p.ar_out_mc + off),
+                                         "r"(v[u][0]), "r"(v[u][1]), "r"(v[u][2]), "r"(v[u][3])
+                                         : "memory");
+                    }
                 }
             }
-            __syncthreads();
             if (*abort_flag) break;
-            asm volatile("fence.acq_rel.sys;" ::: "memory");
-            const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-            const int r0 = tm * (2 * BM), c0 = p.n0 + tn * BN;
-            const int rows = min(2 * BM, p.M - r0), cols = min(BN, p.n1 - c0);
-            const int ppr = cols >> 3;  // 16-byte pieces (8 bf16) per row
-            const int total = rows * ppr;
-            // AR_UNROLL independent reductions in flight per thread: one round trip through the switch takes
-            // microseconds, so the pull is latency-bound unless many are outstanding.
-            for (int base = threadIdx.x; base < total; base += NUM_THREADS * AR_UNROLL) {
-                unsigned v[AR_UNROLL][4];
-                long long off[AR_UNROLL];
-#pragma unroll
-                for (int u = 0; u < AR_UNROLL; u++) {
-                    const int i = base + u * NUM_THREADS;
-                    const int row = i / ppr, pc = i - row * ppr;
-                    off[u] = (long long)(r0 + row) * p.ep.ldc + (long long)(c0 + pc * 8) * 2;
-                    if (i < total)
-                        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
-                                     : "=r"(v[u][0]), "=r"(v[u][1]), "=r"(v[u][2]), "=r"(v[u][3])
-                                     : "l"(p.ar_partial_mc + off[u])
-                                     : "memory");
-                }
-#pragma unroll
-                for (int u = 0; u < AR_UNROLL; u++) {
-                    const int i = base + u * NUM_THREADS;
-                    if (i < total)
-                        asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(p.ar_out_mc + off[u]),
-                                     "r"(v[u][0]), "r"(v[u][1]), "r"(v[u][2]), "r"(v[u][3])
-                                     : "memory");
-                }
-            }
         }
     } else if (warp == 0) {
         // ---------------- TMA producer (one per CTA) ----------------
@@ -719,7 +729,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             if (lane == 0) {
                 mbar_arrive_remote(leader_acc_empty + 8 * ab);
                 if (p.ar_world)                      // ... before the tile's owner counts the arrival
-                    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.ar_flags[tile % p.ar_world] + tile), "r"(1u)
+                    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.ar_flags[tile % p.ar_world] + 2 * tile + (int)rank), "r"(1u)
                                  : "memory");
             }
         }
@@ -941,7 +951,7 @@ int launch_gemm_tc_allreduce(const void* W_data, int W_K_pad, int W_N_pad, const
     p.M = M; p.K = K; p.n0 = 0; p.n1 = N;
     p.tiles_m = (M + 2 * BM - 1) / (2 * BM);
     p.tiles_n = (N + 255) / 256;
-    if (p.tiles_m * p.tiles_n > ar.max_tiles) { set_error("gemm allreduce: %d tiles exceed the flag array (%d)", p.tiles_m * p.tiles_n, ar.max_tiles); return B200FC_ERR_INVALID; }
+    if (2 * p.tiles_m * p.tiles_n > ar.max_tiles) { set_error("gemm allreduce: %d arrival counters needed, %d given", 2 * p.tiles_m * p.tiles_n, ar.max_tiles); return B200FC_ERR_INVALID; }
     p.k_slabs = (K + 63) / 64;
     p.idesc = make_idesc(false, false, false, 256, 2 * BM);
     p.acc_is_int = 0;
@@ -952,12 +962,16 @@ int launch_gemm_tc_allreduce(const void* W_data, int W_K_pad, int W_N_pad, const
     p.status = kernel_status_word();
     p.splits = 1; p.split_stride = 0;
     p.ar_world = ar.world; p.ar_rank = ar.rank;
+    {
+        const char* e = getenv("B200FC_AR_PHASES");
+        p.ar_phases = e ? atoi(e) : 3;
+    }
     const int all_pairs = num_sms() / 2;
     int comm_pairs = ar.comm_sms / 2;
     if (comm_pairs < 1) comm_pairs = 1;
-    if (comm_pairs > all_pairs / 2) comm_pairs = all_pairs / 2;
+    if (comm_pairs > all_pairs - 1) comm_pairs = all_pairs - 1;
     p.ar_gemm_pairs = all_pairs - comm_pairs;
-    p.ar_target = (unsigned)ar.world * 8u;
+    p.ar_target = (unsigned)ar.world * 4u;
     for (int i = 0; i < 8; i++) p.ar_flags[i] = i < ar.world ? ar.flags[i] : nullptr;
     p.ar_partial_mc = (const char*)ar.partial_mc;
     p.ar_out_mc = (char*)ar.out_mc;
@@ -1009,7 +1023,7 @@ int launch_gemm_tc(const void* W_data, int w_dtype, int W_K_pad, int W_N_pad, co
     p.ep = ep;
     p.status = kernel_status_word();
     p.splits = 1; p.split_stride = 0;
-    p.ar_world = 0; p.ar_rank = 0; p.ar_gemm_pairs = 0; p.ar_target = 0; p.ar_partial_mc = nullptr; p.ar_out_mc = nullptr;
+    p.ar_world = 0; p.ar_rank = 0; p.ar_phases = 3; p.ar_gemm_pairs = 0; p.ar_target = 0; p.ar_partial_mc = nullptr; p.ar_out_mc = nullptr;
     for (int i = 0; i < 8; i++) p.ar_flags[i] = nullptr;
     int es = ep.out_dtype == B200FC_F32 || ep.out_dtype == B200FC_S32 ? 4 : (ep.out_dtype == B200FC_BF16 ? 2 : 1);
     if (ep.steps & B200FC_STEP_SILU_MUL)

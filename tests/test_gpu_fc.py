@@ -149,6 +149,23 @@ def test_split_k_shapes_exact(M, K, N):
     assert np.abs(got8.astype(np.int32) - ref8.astype(np.int32)).max() <= 1
 
 
+@pytest.mark.parametrize("M,K,N", [(512, 192, 10280), (300, 128, 20000), (1024, 64, 5000), (700, 96, 7177)])
+def test_many_tiles_exact(M, K, N):
+    """more 256 x 256 tiles than CTA pairs: every pair walks several tiles, both accumulator buffers get reused"""
+    rng = np.random.default_rng(M + K + N)
+    A = H.two_valued_bf16(rng, (M, K)); B = H.two_valued_bf16(rng, (K, N))
+    bias = (rng.integers(-8, 9, N) * 0.25).astype(np.float32)
+    w = H.pack(B)
+    ref = port.gemm_bf16(A, B)
+    got = H.run_matmul(w, A, capi.F32, steps=capi.STEP_BIAS, bias=bias)
+    assert np.array_equal(got, port.postops(ref, port.BIAS, port.F32, bias=bias))
+    got = H.run_matmul(w, A, capi.F32, n0=64, n1=N - 9)
+    assert np.array_equal(got[:, 64:N - 9], ref[:, 64:N - 9])
+    Ai = rng.integers(-128, 128, (M, K), dtype=np.int8); Bi = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    wi = H.pack(Bi)
+    assert np.array_equal(H.run_matmul(wi, Ai, capi.S32), port.gemm_i8(Ai, Bi))
+
+
 def test_column_range_and_sentinel():
     """n0/n1 compute a column sub-range only (Matmul::operator() n0, n1; kernels_amx.hpp:1169-1178)."""
     rng = np.random.default_rng(5)

@@ -90,6 +90,19 @@ def test_mlp_tensor_parallel_shards(M, tp):
     assert H.rel_to_max(bf16_to_f32(got), bf16_to_f32(ref)) < 1e-2
 
 
+def test_mlp_many_tiles():
+    """gate/up with more tiles than CTA pairs (several rounds of the persistent schedule, SiLU pairing in each)"""
+    rng = np.random.default_rng(77)
+    M, K, N = 520, 128, 5312
+    x, gate, up, down = make_mlp_inputs(rng, M, K, N)
+    ref, ref_act = port.mlp(x, gate, up, down, want_act=True)
+    got, act = run_mlp(x, gate, up, down)
+    assert H.rel_to_max(bf16_to_f32(act), bf16_to_f32(ref_act)) < 1e-2
+    assert H.rel_to_max(bf16_to_f32(got), bf16_to_f32(ref)) < 1e-2
+    # element-wise too: a misplaced tile would leave whole column ranges wrong but small
+    assert np.abs(bf16_to_f32(act) - bf16_to_f32(ref_act)).max() < 0.02 * np.abs(bf16_to_f32(ref_act)).max()
+
+
 def test_mlp_long_k_few_tiles():
     """M just above the decode limit with a long K: both GEMMs take the split-K route (SiLU pairing in the reduction)"""
     rng = np.random.default_rng(77)
