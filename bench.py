@@ -214,18 +214,32 @@ def run_ours(args, w, M, name):
                 dt = capi.F32 if oo.dtype == torch.float32 else capi.BF16
                 mlp.down_rows(row0, rows, oo.data_ptr(), dt, oo.stride(0) * oo.element_size(),
                               torch.cuda.current_stream().cuda_stream)
-        if args.tp_mode == "fused":
+        mode = args.tp_mode
+        if mode == "auto":
+            # the in-kernel pull all-reduce needs symmetric memory with an NVLink multicast mapping on every rank
+            try:
+                pull = tp.PullFusedTensorParallelMLP(mlp, H, M, comm_sms=args.comm_sms)
+                ok = 1
+            except Exception as ex:  # noqa: BLE001 - any failure means "not available here"
+                sys.stderr.write("rank %d: pull all-reduce unavailable (%s); using NCCL\n" % (rank, ex))
+                pull, ok = None, 0
+            t_ok = torch.tensor([ok], device=dev)
+            dist.all_reduce(t_ok, op=dist.ReduceOp.MIN)
+            mode = "pull" if int(t_ok.item()) == 1 else "nccl"
+        elif mode == "pull":
+            pull = tp.PullFusedTensorParallelMLP(mlp, H, M, comm_sms=args.comm_sms)
+        args.tp_mode = mode
+        if mode == "fused":
             fused = tp.FusedTensorParallelMLP(mlp, H, M)
             def step():
-                fused.forward(x)
-        elif args.tp_mode == "pull":
-            pull = tp.PullFusedTensorParallelMLP(mlp, H, M, comm_sms=args.comm_sms)
+                return fused.forward(x)
+        elif mode == "pull":
             def step():
-                pull.forward(x)
+                return pull.forward(x)
         else:
             tpm = tp.TensorParallelMLP(Local(), H, partial_dtype=torch.bfloat16, chunk_rows=args.chunk_rows)
             def step():
-                tpm.forward(x, out)
+                return tpm.forward(x, out)
 
     def barrier():
         if world > 1:
@@ -302,8 +316,7 @@ def run_ours(args, w, M, name):
         else:
             def e2e_step():
                 x.copy_(xh, non_blocking=True)
-                step()
-                oh.copy_(out, non_blocking=True)
+                oh.copy_(step(), non_blocking=True)
                 torch.cuda.current_stream().synchronize()
         for _ in range(3):
             e2e_step()
@@ -468,10 +481,12 @@ def main():
     ap.add_argument("--workload", default=None, choices=[None] + list(WORKLOADS))
     ap.add_argument("--M", type=int, default=None)
     ap.add_argument("--chunk-rows", type=int, default=2048)
-    ap.add_argument("--tp-mode", default="nccl", choices=["nccl", "fused", "pull"],
-                    help="N > 1: 'nccl' = all-reduce in row chunks overlapping the GEMMs, 'fused' = in-switch reduction "
-                         "from the down-projection epilogue (multimem.red)")
-    ap.add_argument("--comm-sms", type=int, default=16)
+    ap.add_argument("--tp-mode", default="auto", choices=["auto", "nccl", "fused", "pull"],
+                    help="N > 1: 'pull' = all-reduce inside the down-projection kernel (multimem.ld_reduce / multimem.st "
+                         "by reducing CTAs), 'nccl' = NCCL all-reduce in row chunks overlapping the GEMMs, 'fused' = "
+                         "in-switch reduction from the down-projection epilogue (multimem.red); 'auto' = pull when "
+                         "symmetric memory with multicast is available, else nccl")
+    ap.add_argument("--comm-sms", type=int, default=16, help="SMs reserved for the reduction in 'pull' mode")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--legs", default="kernel,e2e,decode,configs,cpu",
                     help="optional legs after the main timed loop (comma list of kernel,e2e,decode,configs,cpu; '' = none)")

@@ -153,9 +153,9 @@ int b200fc_mlp_down_reduce(b200fc_mlp_t* mlp, int M, void* multicast_out, int ou
  * `partial` and `out`, both [>= M, K] bf16 with row pitch ld_bytes, each also mapped through an NVLink multicast
  * address, and one array of 32-bit arrival counters per rank.  Most CTA pairs multiply and store this rank's tile
  * into its `partial` replica, then bump the tile's counter on the tile's owner (tile index % world); the last
- * `comm_sms` SMs of the grid wait for the tiles this rank owns, pull them from all replicas with
- * multimem.ld_reduce (summed in the switch, fp32 accumulation) and write the sum to every rank's `out` with
- * multimem.st.  Each contribution crosses NVLink once and the transfer overlaps the multiplication of later tiles.
+ * `comm_sms` SMs of the grid (and every other SM once its tiles are done) wait for the tiles this rank owns, pull
+ * them from all replicas with multimem.ld_reduce (summed in the switch, fp32 accumulation) and write the sum to
+ * every rank's `out` with multimem.st.  Each contribution crosses NVLink once and the transfer overlaps the multiplication of later tiles.
  * Contract: the counters the call uses are zero when it starts on any rank; after the call every rank passes a
  * cross-rank barrier before `out` is read, `partial` is rewritten or the counters are cleared (mm_amx_b200/tp.py
  * alternates two counter arrays so that one barrier per step suffices).  Needs M > 16, K % 8 == 0, 2 <= world <= 8,
@@ -168,7 +168,7 @@ typedef struct {
     void* out_mc;            /* multicast address of `out` */
     int64_t ld_bytes;
     uint32_t* flags[8];      /* flags[r]: counter array of rank r as mapped on this GPU */
-    int max_tiles;           /* entries per counter array; a call uses 2 * ceil(M/256) * ceil(K/256) of them */
+    int max_tiles;           /* entries per counter array; a call uses 2 * ceil(M/256) * ceil(K/256) of them and the last one (hands out reduction work) */
     int comm_sms;            /* SMs that reduce instead of multiplying (even, e.g. 16) */
 } b200fc_allreduce_t;
 int b200fc_mlp_down_allreduce(b200fc_mlp_t* mlp, int M, const b200fc_allreduce_t* ar, void* stream);

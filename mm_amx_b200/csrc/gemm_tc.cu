@@ -58,7 +58,8 @@ struct GemmParams {
     // rank; the last CTA pairs of the grid do not multiply but reduce the tiles this rank owns.
     int ar_world, ar_rank;
     int ar_phases;              // bit 0: multiply, bit 1: reduce (both set in normal use; single bits for measurements)
-    int ar_gemm_pairs;          // pairs that multiply; pairs beyond reduce
+    int ar_gemm_pairs;          // pairs that multiply; pairs beyond reduce from the start
+    int ar_work_counter;        // index, in this rank's counter array, of the counter that hands out reduction units
     unsigned ar_target;         // arrivals that mean "every rank has stored these 128 rows of the tile" (world x 4 epilogue warps)
     unsigned* ar_flags[8];      // ar_flags[r]: arrival counters of rank r (peer-mapped), two per tile (one per CTA of the pair)
     const char* ar_partial_mc;  // multicast address of all replicas of the partial buffer
@@ -526,6 +527,74 @@ __device__ __forceinline__ void tc_mma_pair(unsigned d_tmem, unsigned long long 
 
 constexpr int AR_UNROLL = 22;  // 192 threads x 22 pieces cover the 4096 pieces of a 128 x 256 bf16 unit
 
+// All-reduce work of the fused tensor-parallel down projection, run by whole CTAs: the pairs reserved for it from the
+// start of the kernel and every multiplying CTA once its own tiles are done.
+// Tile t belongs to rank t % world.  Unit of work: the 128 rows of an owned tile that one CTA of a multiplying pair
+// produced (own arrival counter); units are claimed in tile order from a counter in this rank's memory.  Once every
+// rank has stored its bf16 contribution (arrival counter reached), the unit is pulled from all replicas with
+// multimem.ld_reduce — the NVSwitch adds them, accumulating in fp32 — and the sum is written to every rank's output
+// with multimem.st.  So each contribution crosses NVLink once, while the multiplying pairs are busy with later
+// tiles.  A whole unit (<= 4096 16-byte pieces) is in flight at once, AR_UNROLL reductions per thread, because a trip
+// through the switch takes microseconds.
+template <int BN>
+__device__ void allreduce_units(const GemmParams& p, int num_tiles, volatile int* unit_slot, volatile int* abort_flag) {
+    unsigned* my_flags = p.ar_flags[p.ar_rank];
+    const int owned = (num_tiles - p.ar_rank + p.ar_world - 1) / p.ar_world;
+    const int n_units = 2 * owned;
+    while (true) {
+        if (threadIdx.x == 0) *unit_slot = (int)atomicAdd(my_flags + p.ar_work_counter, 1u);
+        __syncthreads();
+        const int u = *unit_slot;
+        if (u >= n_units) break;
+        const int tile = p.ar_rank + (u >> 1) * p.ar_world, half = u & 1;
+        const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+        const int r0 = tm * (2 * BM) + half * BM, c0 = p.n0 + tn * BN;
+        const int rows = min(BM, p.M - r0), cols = min(BN, p.n1 - c0);
+        if (threadIdx.x == 0 && rows > 0) {
+            const unsigned long long t0 = globaltimer();
+            while (true) {
+                unsigned v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(my_flags + 2 * tile + half) : "memory");
+                if (v >= p.ar_target) break;
+                if (globaltimer() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; break; }
+            }
+        }
+        // Thread 0's acquire load and the CTA barrier order every thread's loads below after the arrivals; a
+        // system-scope fence here would also wait for this thread's multicast stores of the previous unit to reach
+        // every GPU (measured: 8 us per unit).  The barrier also keeps unit_slot from being rewritten too early.
+        __syncthreads();
+        if (*abort_flag) break;
+        if (rows <= 0) continue;
+        const int ppr = cols >> 3;  // 16-byte pieces (8 bf16) per row
+        const int total = rows * ppr;
+        const long long base_off = (long long)r0 * p.ep.ldc + (long long)c0 * 2;
+        for (int base = threadIdx.x; base < total; base += NUM_THREADS * AR_UNROLL) {
+            unsigned v[AR_UNROLL][4];
+#pragma unroll
+            for (int k = 0; k < AR_UNROLL; k++) {
+                const int i = base + k * NUM_THREADS;
+                const int row = i / ppr, pc = i - row * ppr;
+                const long long off = base_off + (long long)row * p.ep.ldc + pc * 16;
+                if (i < total)
+                    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(v[k][0]), "=r"(v[k][1]), "=r"(v[k][2]), "=r"(v[k][3])
+                                 : "l"(p.ar_partial_mc + off)
+                                 : "memory");
+            }
+#pragma unroll
+            for (int k = 0; k < AR_UNROLL; k++) {
+                const int i = base + k * NUM_THREADS;
+                const int row = i / ppr, pc = i - row * ppr;
+                const long long off = base_off + (long long)row * p.ep.ldc + pc * 16;
+                if (i < total)
+                    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(p.ar_out_mc + off),
+                                 "r"(v[k][0]), "r"(v[k][1]), "r"(v[k][2]), "r"(v[k][3])
+                                 : "memory");
+            }
+        }
+    }
+}
+
 template <int BN, bool I8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
@@ -540,6 +609,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const unsigned bar_acc_empty = smem_u32(bars + 2 * C::STAGES + 2);
     unsigned* tmem_holder = (unsigned*)(bars + 2 * C::STAGES + 4);
     volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
+    volatile int* unit_slot = (volatile int*)(tmem_holder + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const unsigned rank = cluster_ctarank();
@@ -574,70 +644,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     tc_fence_after();
     const unsigned tmem_base = *tmem_holder;
 
-    if (comm_role && !(p.ar_phases & 2)) {
-    } else if (!comm_role && p.ar_world && !(p.ar_phases & 1)) {
-    } else if (comm_role) {
+    if (comm_role) {
         // ---------------- all-reduce role (whole CTA) ----------------
-        // Tile t belongs to rank t % world.  Once every rank has stored its bf16 contribution for an owned tile
-        // (arrival counter reached), the tile is pulled from all replicas with multimem.ld_reduce — the NVSwitch adds
-        // them, accumulating in fp32 — and the sum is written to every rank's output with multimem.st.  So each
-        // contribution crosses NVLink once, while the multiplying pairs are already busy with later tiles.
-        const int n_comm = 2 * (grid_pairs - num_pairs);
-        const int me = (pair - num_pairs) * 2 + (int)rank;
-        const unsigned* my_flags = p.ar_flags[p.ar_rank];
-        // Unit of work: the 128 rows of a tile that one CTA of a multiplying pair produced (own arrival counter).  A
-        // whole unit (<= 4096 16-byte pieces) is in flight at once — AR_UNROLL reductions per thread — because one
-        // round trip through the switch takes microseconds and tiles become ready in bursts, a wave at a time.
-        int q = 0;
-        for (int tile = p.ar_rank; tile < num_tiles; tile += p.ar_world) {
-            for (int half = 0; half < 2; half++, q++) {
-                if (q % n_comm != me) continue;
-                const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-                const int r0 = tm * (2 * BM) + half * BM, c0 = p.n0 + tn * BN;
-                const int rows = min(BM, p.M - r0), cols = min(BN, p.n1 - c0);
-                if (rows <= 0) continue;
-                if (threadIdx.x == 0) {
-                    const unsigned long long t0 = globaltimer();
-                    while (true) {
-                        unsigned v;
-                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(my_flags + 2 * tile + half) : "memory");
-                        if (v >= p.ar_target) break;
-                        if (globaltimer() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; break; }
-                    }
-                }
-                __syncthreads();
-                if (*abort_flag) break;
-                asm volatile("fence.acq_rel.sys;" ::: "memory");
-                const int ppr = cols >> 3;  // 16-byte pieces (8 bf16) per row
-                const int total = rows * ppr;
-                const long long base_off = (long long)r0 * p.ep.ldc + (long long)c0 * 2;
-                for (int base = threadIdx.x; base < total; base += NUM_THREADS * AR_UNROLL) {
-                    unsigned v[AR_UNROLL][4];
-#pragma unroll
-                    for (int u = 0; u < AR_UNROLL; u++) {
-                        const int i = base + u * NUM_THREADS;
-                        const int row = i / ppr, pc = i - row * ppr;
-                        const long long off = base_off + (long long)row * p.ep.ldc + pc * 16;
-                        if (i < total)
-                            asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
-                                         : "=r"(v[u][0]), "=r"(v[u][1]), "=r"(v[u][2]), "=r"(v[u][3])
-                                         : "l"(p.ar_partial_mc + off)
-                                         : "memory");
-                    }
-#pragma unroll
-                    for (int u = 0; u < AR_UNROLL; u++) {
-                        const int i = base + u * NUM_THREADS;
-                        const int row = i / ppr, pc = i - row * ppr;
-                        const long long off = base_off + (long long)row * p.ep.ldc + pc * 16;
-                        if (i < total)
-                            asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(p.ar_out_mc + off),
-                                         "r"(v[u][0]), "r"(v[u][1]), "r"(v[u][2]), "r"(v[u][3])
-                                         : "memory");
-                    }
-                }
-            }
-            if (*abort_flag) break;
-        }
+        if (p.ar_phases & 2) allreduce_units<BN>(p, num_tiles, unit_slot, abort_flag);
+    } else if (p.ar_world && !(p.ar_phases & 1)) {
     } else if (warp == 0) {
         // ---------------- TMA producer (one per CTA) ----------------
         if (lane == 0) {
@@ -733,6 +743,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                  : "memory");
             }
         }
+    }
+
+    if (p.ar_world && !comm_role && p.ar_phases == 3) {
+        // this CTA's tiles are done: help with the reduction of the tiles this rank owns (the last round's arrive late)
+        __syncthreads();
+        if (!*abort_flag) allreduce_units<BN>(p, num_tiles, unit_slot, abort_flag);
     }
 
     // ---------------- common exit ----------------
@@ -951,7 +967,7 @@ int launch_gemm_tc_allreduce(const void* W_data, int W_K_pad, int W_N_pad, const
     p.M = M; p.K = K; p.n0 = 0; p.n1 = N;
     p.tiles_m = (M + 2 * BM - 1) / (2 * BM);
     p.tiles_n = (N + 255) / 256;
-    if (2 * p.tiles_m * p.tiles_n > ar.max_tiles) { set_error("gemm allreduce: %d arrival counters needed, %d given", 2 * p.tiles_m * p.tiles_n, ar.max_tiles); return B200FC_ERR_INVALID; }
+    if (2 * p.tiles_m * p.tiles_n > ar.max_tiles - 1) { set_error("gemm allreduce: %d arrival counters needed, %d given", 2 * p.tiles_m * p.tiles_n, ar.max_tiles); return B200FC_ERR_INVALID; }
     p.k_slabs = (K + 63) / 64;
     p.idesc = make_idesc(false, false, false, 256, 2 * BM);
     p.acc_is_int = 0;
@@ -972,6 +988,7 @@ int launch_gemm_tc_allreduce(const void* W_data, int W_K_pad, int W_N_pad, const
     if (comm_pairs > all_pairs - 1) comm_pairs = all_pairs - 1;
     p.ar_gemm_pairs = all_pairs - comm_pairs;
     p.ar_target = (unsigned)ar.world * 4u;
+    p.ar_work_counter = ar.max_tiles - 1;
     for (int i = 0; i < 8; i++) p.ar_flags[i] = i < ar.world ? ar.flags[i] : nullptr;
     p.ar_partial_mc = (const char*)ar.partial_mc;
     p.ar_out_mc = (char*)ar.out_mc;
@@ -1023,7 +1040,7 @@ int launch_gemm_tc(const void* W_data, int w_dtype, int W_K_pad, int W_N_pad, co
     p.ep = ep;
     p.status = kernel_status_word();
     p.splits = 1; p.split_stride = 0;
-    p.ar_world = 0; p.ar_rank = 0; p.ar_phases = 3; p.ar_gemm_pairs = 0; p.ar_target = 0; p.ar_partial_mc = nullptr; p.ar_out_mc = nullptr;
+    p.ar_world = 0; p.ar_rank = 0; p.ar_phases = 3; p.ar_gemm_pairs = 0; p.ar_work_counter = 0; p.ar_target = 0; p.ar_partial_mc = nullptr; p.ar_out_mc = nullptr;
     for (int i = 0; i < 8; i++) p.ar_flags[i] = nullptr;
     int es = ep.out_dtype == B200FC_F32 || ep.out_dtype == B200FC_S32 ? 4 : (ep.out_dtype == B200FC_BF16 ? 2 : 1);
     if (ep.steps & B200FC_STEP_SILU_MUL)
