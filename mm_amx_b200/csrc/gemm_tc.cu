@@ -31,6 +31,10 @@ constexpr int MMA_K_BYTES = 32;          // K extent of one tcgen05.mma (16 bf16
 constexpr int NUM_THREADS = 192;
 constexpr int EPI_WARP0 = 2;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+#ifndef B200FC_EPI_SLEEP_NS
+#define B200FC_EPI_SLEEP_NS 256
+#endif
+constexpr int EPI_SLEEP_NS = B200FC_EPI_SLEEP_NS;
 
 template <int BN> struct Cfg {
     static constexpr int STAGES = BN == 256 ? 4 : 6;
@@ -94,10 +98,14 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
     return ok != 0;
 }
 // Bounded wait.  Returns false when the CTA is aborting (this wait or another role's ran out of time).
+// SLEEP_NS > 0: back off between polls (for waits that are long and not latency critical: the epilogue warps wait most
+// of a tile's main loop, and five spinning warps cost issue slots and power that the tensor pipe could use).
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = globaltimer();
     while (true) {
+        if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
         if (globaltimer() - t0 > WAIT_LIMIT_NS) {
@@ -417,7 +425,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int ab = it & 1;
             const unsigned acc_phase = (unsigned)(it >> 1) & 1;
             const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-            if (!mbar_wait(bar_acc_full + 8 * ab, acc_phase, abort_flag)) { ok = false; break; }
+            if (!mbar_wait<EPI_SLEEP_NS>(bar_acc_full + 8 * ab, acc_phase, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const int m = tm * BM + quarter * 32 + lane;
             const bool row_ok = m < p.M;
@@ -673,8 +681,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer (leader CTA only) ----------------
-        if (leader) {
+        // ---------------- MMA issuer (leader CTA only; one thread waits and issues, its warp mates park) ----------------
+        if (leader && lane == 0) {
             int stage = 0;
             unsigned phase = 0;
             int it = 0;
@@ -690,23 +698,21 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 for (int ks = ks0; ks < ks1; ks++) {
                     if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    if (lane == 0) {
-                        const unsigned sa = smem_u32(smem + stage * C::STAGE_BYTES);
-                        const unsigned long long adesc = make_smem_desc(sa);
-                        const unsigned long long bdesc = make_smem_desc(sa + C::A_BYTES);
+                    const unsigned sa = smem_u32(smem + stage * C::STAGE_BYTES);
+                    const unsigned long long adesc = make_smem_desc(sa);
+                    const unsigned long long bdesc = make_smem_desc(sa + C::A_BYTES);
 #pragma unroll
-                        for (int k = 0; k < SLAB_BYTES / MMA_K_BYTES; k++)
-                            tc_mma_pair<I8>(d_tmem, adesc + (unsigned long long)(k * (MMA_K_BYTES >> 4)),
-                                            bdesc + (unsigned long long)(k * (MMA_K_BYTES >> 4)), p.idesc,
-                                            (unsigned)(((ks - ks0) | k) != 0));
-                        tc_commit_pair(bar_empty + 8 * stage);
-                        if (ks == ks1 - 1) tc_commit_pair(bar_acc_full + 8 * ab);
-                    }
-                    __syncwarp();
+                    for (int k = 0; k < SLAB_BYTES / MMA_K_BYTES; k++)
+                        tc_mma_pair<I8>(d_tmem, adesc + (unsigned long long)(k * (MMA_K_BYTES >> 4)),
+                                        bdesc + (unsigned long long)(k * (MMA_K_BYTES >> 4)), p.idesc,
+                                        (unsigned)(((ks - ks0) | k) != 0));
+                    tc_commit_pair(bar_empty + 8 * stage);
+                    if (ks == ks1 - 1) tc_commit_pair(bar_acc_full + 8 * ab);
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
             }
         }
+        __syncwarp();
     } else {
         // ---------------- epilogue warps (both CTAs, own 128 rows) ----------------
         const int quarter = warp & 3;
@@ -719,7 +725,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int ab = it & 1;
             const unsigned acc_phase = (unsigned)(it >> 1) & 1;
             const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-            if (!mbar_wait(bar_acc_full + 8 * ab, acc_phase, abort_flag)) { ok = false; break; }
+            if (!mbar_wait<EPI_SLEEP_NS>(bar_acc_full + 8 * ab, acc_phase, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const int m = tm * (2 * BM) + (int)rank * BM + quarter * 32 + lane;
             const bool row_ok = m < p.M;
