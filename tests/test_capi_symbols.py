@@ -42,6 +42,31 @@ def test_epilogue_struct_layout_matches_header():
     assert capi.Epilogue.q_scale.offset == 48 and capi.Epilogue.q_scale_per_oc.offset == 56
 
 
+def test_allreduce_struct_layout_matches_header(tmp_path):
+    """compile the header with the host C compiler and compare sizeof / offsetof with the ctypes mirror"""
+    import subprocess
+    src = tmp_path / "layout.c"
+    src.write_text(
+        '#include <stdio.h>\n#include <stddef.h>\n#include "b200fc.h"\n'
+        'int main(void) { printf("%zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(b200fc_allreduce_t),\n'
+        '  offsetof(b200fc_allreduce_t, partial_local), offsetof(b200fc_allreduce_t, partial_mc),\n'
+        '  offsetof(b200fc_allreduce_t, out_mc), offsetof(b200fc_allreduce_t, ld_bytes),\n'
+        '  offsetof(b200fc_allreduce_t, flags), offsetof(b200fc_allreduce_t, max_tiles),\n'
+        '  offsetof(b200fc_allreduce_t, comm_sms)); return 0; }\n')
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    got = [int(v) for v in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()]
+    A = capi.AllReduce
+    assert got == [ctypes.sizeof(A), A.partial_local.offset, A.partial_mc.offset, A.out_mc.offset, A.ld_bytes.offset,
+                   A.flags.offset, A.max_tiles.offset, A.comm_sms.offset]
+
+
+def test_allreduce_argument_checks_need_no_gpu():
+    L = capi.lib()
+    rc = L.b200fc_mlp_down_allreduce(None, 64, None, None)
+    assert rc == capi.ERR_INVALID and b"null" in L.b200fc_last_error()
+
+
 def test_argument_checks_need_no_gpu():
     L = capi.lib()
     h = ctypes.c_void_p()
