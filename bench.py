@@ -486,7 +486,7 @@ def main():
                          "by reducing CTAs), 'nccl' = NCCL all-reduce in row chunks overlapping the GEMMs, 'fused' = "
                          "in-switch reduction from the down-projection epilogue (multimem.red); 'auto' = pull when "
                          "symmetric memory with multicast is available, else nccl")
-    ap.add_argument("--comm-sms", type=int, default=16, help="SMs reserved for the reduction in 'pull' mode")
+    ap.add_argument("--comm-sms", type=int, default=8, help="SMs reserved for the reduction in 'pull' mode")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--legs", default="kernel,e2e,decode,configs,cpu",
                     help="optional legs after the main timed loop (comma list of kernel,e2e,decode,configs,cpu; '' = none)")

@@ -492,6 +492,14 @@ int launch_gemv_tma(const Weight& w, const void* A, int M, int K, int64_t lda, i
     // SM and every split keeps at least two stages
     int S = 1;
     while (S < 8 && row_ctas * S * 2 <= 148 * 2 && p.n_stages_total >= 4 * S) S *= 2;
+    {
+        static int forced = -1;  // B200FC_GEMV_SPLITS=1|2|4|8 (for experiments)
+        if (forced < 0) {
+            const char* e = getenv("B200FC_GEMV_SPLITS");
+            forced = e ? atoi(e) : 0;
+        }
+        if ((forced == 1 || forced == 2 || forced == 4 || forced == 8) && p.n_stages_total >= 2 * forced) S = forced;
+    }
     p.splits = S;
     const bool w8 = w.dtype == B200FC_S8;
     if (M <= 8) return w8 ? launch_variant<true, 1>(map, p, row_ctas, s) : launch_variant<false, 1>(map, p, row_ctas, s);

@@ -167,7 +167,7 @@ class PullFusedTensorParallelMLP:
 
     MAX_TILES = 8192
 
-    def __init__(self, mlp, K, max_M, group=None, comm_sms=16):
+    def __init__(self, mlp, K, max_M, group=None, comm_sms=8):
         import torch.distributed._symmetric_memory as symm_mem
         self.mlp, self.K, self.max_M, self.comm_sms = mlp, K, max_M, comm_sms
         self.group = group if group is not None else dist.group.WORLD
