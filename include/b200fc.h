@@ -15,6 +15,7 @@
 #ifndef B200FC_H
 #define B200FC_H
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -97,6 +98,16 @@ int b200fc_weight_free(b200fc_weight_t* w);
 int b200fc_weight_info(const b200fc_weight_t* w, int* K, int* N, int* dtype, int* compressed, float* deq_scale);
 /* copies the packed weights back as a plain row-major [N, K] matrix of their stored dtype (host or device dst) */
 int b200fc_weight_unpack(const b200fc_weight_t* w, void* dst, int64_t ld_bytes, void* stream);
+
+/* Serialised packed weights: a self-describing blob in HOST memory (64-byte header, the packed matrix as it lies in
+ * HBM, then the per-channel scales if the object has them) that b200fc_weight_import turns back into an identical
+ * object without re-packing or re-quantising.  The reference has no on-disk form — it re-packs at every start-up — but
+ * its torch extension clones the packed copy in __deepcopy__ (torch-ext/amx_mlp.cpp:499-510); this pair serves both
+ * uses (checkpoint files of packed weights, clones).  The blob is tied to this library's packing (version in the
+ * header); import rejects anything else with B200FC_ERR_INVALID.  Both calls synchronise the stream. */
+int b200fc_weight_export_size(const b200fc_weight_t* w, size_t* bytes);
+int b200fc_weight_export(const b200fc_weight_t* w, void* host_dst, size_t capacity, void* stream);
+int b200fc_weight_import(const void* host_src, size_t bytes, b200fc_weight_t** out, void* stream);
 
 /* ---- Matmul::operator()(A, B, n0, n1, ppkernel), include/kernels_amx.hpp:1169-1314 and :1343-1516 ------------- */
 /* C[:, n0:n1) = postops(A[M,K] * W[:, n0:n1)).  dtypeA: B200FC_BF16 with bf16 or compressed weights, B200FC_S8 /

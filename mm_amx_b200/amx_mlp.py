@@ -27,7 +27,7 @@ class LinearNxN:
     def __init__(self):
         self.name = ""
         self._w = None
-        self._weight = None
+        self._cuda = False
         self.N = self.K = 0
 
     def set_weight(self, weight):
@@ -39,7 +39,7 @@ class LinearNxN:
         _require(weight.stride(1) == 1, "weight rows must be contiguous")
         self._w = capi.Weight(weight.data_ptr(), capi.BF16, K, N, weight.stride(0) * 2, True, capi.PACK_PLAIN, None,
                               _stream(weight))
-        self._weight = weight  # kept for __deepcopy__ (the reference clones its packed copy)
+        self._cuda = weight.is_cuda
         self.N, self.K = N, K
 
     def forward(self, x, y):
@@ -57,11 +57,26 @@ class LinearNxN:
             self._w.matmul_host(x.data_ptr(), capi.BF16, x.shape[0], self.K, x.stride(0) * 2, ep)
 
     def __deepcopy__(self, memo):
+        """Clones the PACKED weights, like the reference (torch-ext/amx_mlp.cpp:499-510); nothing is re-packed and the
+        original tensor is not kept alive for it."""
         other = LinearNxN()
         other.name = self.name
-        if self._weight is not None:
-            other.set_weight(self._weight)
+        if self._w is not None:
+            other._w = capi.Weight.from_blob(self._w.export())
+            other._cuda, other.N, other.K = self._cuda, self.N, self.K
         return other
+
+    def packed_state(self):
+        """The packed weights as a uint8 tensor (for torch.save); load_packed_state() restores them without packing."""
+        _require(self._w is not None, "set_weight first")
+        return torch.frombuffer(self._w.export(), dtype=torch.uint8).clone()
+
+    def load_packed_state(self, state):
+        _require(state.dtype == torch.uint8 and state.dim() == 1, "state must be the 1-D uint8 tensor of packed_state()")
+        w = capi.Weight.from_blob(state.cpu().contiguous().numpy().tobytes())
+        info = w.info()
+        _require(info["dtype"] == capi.BF16 and not info["compressed"], "state does not hold bf16 weights")
+        self._w, self.N, self.K = w, info["N"], info["K"]
 
 
 def clflush(x):

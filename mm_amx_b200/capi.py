@@ -40,6 +40,9 @@ SIGNATURES = {
     "b200fc_weight_info": (c_int, [c_void_p, ctypes.POINTER(c_int), ctypes.POINTER(c_int), ctypes.POINTER(c_int),
                                    ctypes.POINTER(c_int), ctypes.POINTER(c_float)]),
     "b200fc_weight_unpack": (c_int, [c_void_p, c_void_p, c_i64, c_void_p]),
+    "b200fc_weight_export_size": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_size_t)]),
+    "b200fc_weight_export": (c_int, [c_void_p, c_void_p, ctypes.c_size_t, c_void_p]),
+    "b200fc_weight_import": (c_int, [c_void_p, ctypes.c_size_t, ctypes.POINTER(c_void_p), c_void_p]),
     "b200fc_matmul": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_i64, c_int, c_int,
                               ctypes.POINTER(Epilogue), c_void_p]),
     "b200fc_matmul_host": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_i64, c_int, c_int,
@@ -135,6 +138,29 @@ class Weight:
 
     def unpack(self, dst_ptr, ld_bytes, stream=None):
         check(lib().b200fc_weight_unpack(self.h, dst_ptr, ld_bytes, stream))
+
+    def export(self, stream=None):
+        """Serialised form of the packed weights (bytearray); Weight.from_blob() rebuilds the object from it."""
+        n = ctypes.c_size_t()
+        check(lib().b200fc_weight_export_size(self.h, ctypes.byref(n)))
+        buf = bytearray(n.value)
+        view = (ctypes.c_char * n.value).from_buffer(buf)
+        check(lib().b200fc_weight_export(self.h, ctypes.addressof(view), n.value, stream))
+        del view
+        return buf
+
+    @classmethod
+    def from_blob(cls, blob, stream=None):
+        """blob: bytes-like object written by export() (e.g. read back from a file)."""
+        raw = bytes(blob) if not isinstance(blob, (bytes, bytearray)) else blob
+        src = (ctypes.c_char * len(raw)).from_buffer_copy(raw)
+        h = c_void_p()
+        check(lib().b200fc_weight_import(ctypes.addressof(src), len(raw), ctypes.byref(h), stream))
+        self = cls.__new__(cls)
+        self.h = h
+        info = self.info()
+        self.K, self.N = info["K"], info["N"]
+        return self
 
     def matmul(self, A_ptr, dtypeA, M, K, lda_bytes, ep, n0=0, n1=None, stream=None):
         check(lib().b200fc_matmul(self.h, A_ptr, dtypeA, M, K, lda_bytes, n0, self.N if n1 is None else n1,

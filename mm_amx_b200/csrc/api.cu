@@ -366,6 +366,104 @@ int b200fc_weight_unpack(const b200fc_weight_t* h, void* dst, int64_t ld_bytes, 
     return B200FC_OK;
 }
 
+// ---- serialised packed weights ----------------------------------------------------------------------------------
+namespace {
+struct BlobHeader {           // 64 bytes, little endian
+    char magic[8];            // "B2FCWGT1": the 1 is the packing version
+    uint32_t header_bytes;    // 64
+    int32_t dtype, K, N, K_pad, N_pad, compressed, has_scales;
+    float deq_scale;
+    uint32_t reserved;
+    uint64_t data_bytes;      // N_pad * K_pad * element size
+    uint64_t total_bytes;     // header + data + scales
+};
+static_assert(sizeof(BlobHeader) == 64, "blob header layout");
+const char kBlobMagic[8] = {'B', '2', 'F', 'C', 'W', 'G', 'T', '1'};
+
+void fill_blob_header(const Weight& w, BlobHeader* hd) {
+    memset(hd, 0, sizeof(*hd));
+    memcpy(hd->magic, kBlobMagic, 8);
+    hd->header_bytes = 64;
+    hd->dtype = w.dtype; hd->K = w.K; hd->N = w.N; hd->K_pad = w.K_pad; hd->N_pad = w.N_pad;
+    hd->compressed = w.compressed ? 1 : 0;
+    hd->has_scales = w.scale_per_oc ? 1 : 0;
+    hd->deq_scale = w.deq_scale;
+    hd->data_bytes = (uint64_t)w.N_pad * (uint64_t)w.K_pad * (uint64_t)elem_size(w.dtype);
+    hd->total_bytes = 64 + hd->data_bytes + (hd->has_scales ? (uint64_t)w.N_pad * sizeof(float) : 0);
+}
+}  // namespace
+
+int b200fc_weight_export_size(const b200fc_weight_t* h, size_t* bytes) {
+    if (!h || !bytes) { set_error("weight_export_size: null pointer"); return B200FC_ERR_INVALID; }
+    BlobHeader hd;
+    fill_blob_header(h->w, &hd);
+    *bytes = (size_t)hd.total_bytes;
+    return B200FC_OK;
+}
+
+int b200fc_weight_export(const b200fc_weight_t* h, void* host_dst, size_t capacity, void* stream) {
+    if (!h || !host_dst) { set_error("weight_export: null pointer"); return B200FC_ERR_INVALID; }
+    const Weight& w = h->w;
+    BlobHeader hd;
+    fill_blob_header(w, &hd);
+    if (capacity < hd.total_bytes) {
+        set_error("weight_export: buffer of %zu bytes, %llu needed", capacity, (unsigned long long)hd.total_bytes);
+        return B200FC_ERR_INVALID;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    char* dst = (char*)host_dst;
+    memcpy(dst, &hd, sizeof(hd));
+    B200FC_CUDA(cudaMemcpyAsync(dst + 64, w.data, (size_t)hd.data_bytes, cudaMemcpyDeviceToHost, s));
+    if (hd.has_scales)
+        B200FC_CUDA(cudaMemcpyAsync(dst + 64 + hd.data_bytes, w.scale_per_oc, (size_t)w.N_pad * sizeof(float),
+                                    cudaMemcpyDeviceToHost, s));
+    B200FC_CUDA(cudaStreamSynchronize(s));
+    return B200FC_OK;
+}
+
+int b200fc_weight_import(const void* host_src, size_t bytes, b200fc_weight_t** out, void* stream) {
+    if (!host_src || !out) { set_error("weight_import: null pointer"); return B200FC_ERR_INVALID; }
+    if (bytes < sizeof(BlobHeader)) { set_error("weight_import: %zu bytes is shorter than a header", bytes); return B200FC_ERR_INVALID; }
+    BlobHeader hd;
+    memcpy(&hd, host_src, sizeof(hd));
+    if (memcmp(hd.magic, kBlobMagic, 8) != 0 || hd.header_bytes != 64) {
+        set_error("weight_import: not a packed-weight blob of this library version");
+        return B200FC_ERR_INVALID;
+    }
+    const int es = (hd.dtype == B200FC_BF16 || hd.dtype == B200FC_S8 || hd.dtype == B200FC_U8) ? elem_size(hd.dtype) : 0;
+    if (!es || hd.K <= 0 || hd.N <= 0) { set_error("weight_import: bad dtype or shape in the header"); return B200FC_ERR_INVALID; }
+    const int K_pad = round_up(hd.K * es, kKPadBytes) / es, N_pad = round_up(hd.N, kRowPad);
+    const uint64_t data_bytes = (uint64_t)N_pad * (uint64_t)K_pad * (uint64_t)es;
+    const uint64_t total = 64 + data_bytes + (hd.has_scales ? (uint64_t)N_pad * sizeof(float) : 0);
+    if (hd.K_pad != K_pad || hd.N_pad != N_pad || hd.data_bytes != data_bytes || hd.total_bytes != total || bytes < total ||
+        (hd.compressed && hd.dtype != B200FC_S8) || (hd.has_scales && !hd.compressed)) {
+        set_error("weight_import: header does not describe a blob this library wrote (or the buffer is truncated)");
+        return B200FC_ERR_INVALID;
+    }
+    b200fc_weight_t* h = new (std::nothrow) b200fc_weight_t;
+    if (!h) { set_error("out of host memory"); return B200FC_ERR_NOMEM; }
+    Weight& w = h->w;
+    cudaStream_t s = (cudaStream_t)stream;
+    const char* src = (const char*)host_src;
+    int rc = alloc_weight(w, hd.K, hd.N, hd.dtype);
+    if (!rc && cudaMemcpyAsync(w.data, src + 64, (size_t)data_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess) rc = B200FC_ERR_CUDA;
+    if (!rc && hd.has_scales) {
+        if (cudaMalloc(&w.scale_per_oc, (size_t)N_pad * sizeof(float)) != cudaSuccess) rc = B200FC_ERR_NOMEM;
+        if (!rc && cudaMemcpyAsync(w.scale_per_oc, src + 64 + data_bytes, (size_t)N_pad * sizeof(float), cudaMemcpyHostToDevice, s) != cudaSuccess)
+            rc = B200FC_ERR_CUDA;
+    }
+    if (!rc && cudaStreamSynchronize(s) != cudaSuccess) rc = B200FC_ERR_CUDA;
+    if (rc) {
+        if (rc == B200FC_ERR_NOMEM) set_error("weight_import: out of device memory");
+        else if (rc == B200FC_ERR_CUDA && !g_err[0]) set_error("weight_import: CUDA failure: %s", cudaGetErrorString(cudaGetLastError()));
+        free_weight(&w); delete h; return rc;
+    }
+    w.compressed = hd.compressed != 0;
+    w.deq_scale = hd.deq_scale;
+    *out = h;
+    return B200FC_OK;
+}
+
 int b200fc_matmul(const b200fc_weight_t* W, const void* A, int dtypeA, int M, int K, int64_t lda_bytes, int n0, int n1,
                   const b200fc_epilogue_t* ep, void* stream) {
     if (!W || !A) { set_error("matmul: null pointer"); return B200FC_ERR_INVALID; }

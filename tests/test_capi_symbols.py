@@ -67,6 +67,18 @@ def test_allreduce_argument_checks_need_no_gpu():
     assert rc == capi.ERR_INVALID and b"null" in L.b200fc_last_error()
 
 
+def test_weight_import_rejects_foreign_blobs_without_gpu():
+    L = capi.lib()
+    h = ctypes.c_void_p()
+    for raw in (b"", b"short", b"x" * 64, b"B2FCWGT1" + b"\0" * 56, b"B2FCWGT1" + (64).to_bytes(4, "little") + b"\xff" * 52):
+        buf = ctypes.create_string_buffer(raw, max(len(raw), 1))
+        rc = L.b200fc_weight_import(buf, len(raw), ctypes.byref(h), None)
+        assert rc == capi.ERR_INVALID, raw[:12]
+    assert L.b200fc_weight_import(None, 64, ctypes.byref(h), None) == capi.ERR_INVALID
+    n = ctypes.c_size_t()
+    assert L.b200fc_weight_export_size(None, ctypes.byref(n)) == capi.ERR_INVALID
+
+
 def test_argument_checks_need_no_gpu():
     L = capi.lib()
     h = ctypes.c_void_p()

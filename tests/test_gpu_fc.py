@@ -166,6 +166,38 @@ def test_many_tiles_exact(M, K, N):
     assert np.array_equal(H.run_matmul(wi, Ai, capi.S32), port.gemm_i8(Ai, Bi))
 
 
+def test_packed_weight_export_import_round_trip(tmp_path):
+    """a blob written by export rebuilds an object that computes bit-identical results, without re-packing:
+    bf16, int8, per-tensor quantised and per-channel int8 weights; through a file, like a checkpoint"""
+    rng = np.random.default_rng(5)
+    M, K, N = 40, 200, 333
+    A = H.uniform_bf16(rng, (M, K)); B = H.uniform_bf16(rng, (K, N))
+    Ai = rng.integers(-128, 128, (M, K), dtype=np.int8); Bi = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    scale = rng.uniform(0.001, 0.02, N).astype(np.float32)
+    cases = [
+        (H.pack(B), A, dict(out=capi.F32)),
+        (H.pack(Bi), Ai, dict(out=capi.S32)),
+        (H.pack(B, False, capi.PACK_QUANT_TENSOR), A, dict(out=capi.F32, steps=capi.STEP_DEQUANT)),
+        (H.pack(Bi, False, capi.PACK_INT8_CHANNEL, scales=scale), A, dict(out=capi.BF16, steps=capi.STEP_DEQUANT)),
+    ]
+    for i, (w, act, kw) in enumerate(cases):
+        blob = w.export()
+        path = tmp_path / ("w%d.bin" % i)
+        path.write_bytes(blob)
+        w2 = capi.Weight.from_blob(path.read_bytes())
+        assert w2.info() == w.info()
+        for rows in (3, M):     # decode-shaped and GEMM-shaped paths
+            want = H.run_matmul(w, act[:rows], kw["out"], steps=kw.get("steps", 0))
+            got = H.run_matmul(w2, act[:rows], kw["out"], steps=kw.get("steps", 0))
+            assert np.array_equal(got, want)
+        assert w2.export() == blob
+    # a truncated or foreign blob is refused
+    blob = cases[0][0].export()
+    for bad in (blob[:100], b"x" * 200, bytes(blob[:8]) + b"\0" * 56):
+        with pytest.raises(capi.B200FCError):
+            capi.Weight.from_blob(bad)
+
+
 def test_column_range_and_sentinel():
     """n0/n1 compute a column sub-range only (Matmul::operator() n0, n1; kernels_amx.hpp:1169-1178)."""
     rng = np.random.default_rng(5)

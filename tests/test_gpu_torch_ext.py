@@ -28,6 +28,12 @@ def test_linear_check_acc(M, N, K, device):
     y2 = torch.zeros_like(y1)
     n2.forward(x.to(torch.bfloat16).to(device), y2)
     assert torch.equal(y1, y2)
+    # packed weights as a tensor (torch.save-able) and back, no re-packing
+    n3 = amx_mlp.LinearNxN()
+    n3.load_packed_state(n.packed_state())
+    y3 = torch.zeros_like(y1)
+    n3.forward(x.to(torch.bfloat16).to(device), y3)
+    assert torch.equal(y1, y3)
 
 
 def test_linear_precondition_errors():
