@@ -1,5 +1,6 @@
 // Shared declarations of the b200fc library: packed-weight object, kernel launch entry points, post-op math.
 #pragma once
+#include <atomic>
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
@@ -61,6 +62,20 @@ struct Mlp {
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     std::vector<cudaEvent_t> ev_in, ev_out;
 };
+
+// cudaFuncSetAttribute applies to the current device only.  Runs `set_attr` (returns a status code) the first time
+// the calling launcher is used on a device and remembers the device in `mask` (one bit per device ordinal); two
+// threads racing on the first use both set the attribute, which is harmless.
+template <typename F>
+inline int once_per_device(std::atomic<unsigned long long>& mask, F&& set_attr) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) dev = 0;
+    const unsigned long long bit = 1ull << (dev & 63);
+    if (mask.load(std::memory_order_acquire) & bit) return 0;
+    const int rc = set_attr();
+    if (!rc) mask.fetch_or(bit, std::memory_order_release);
+    return rc;
+}
 
 // SM budget of the persistent GEMM grids (0 = all SMs); set through b200fc_set_sm_limit
 int sm_limit();

@@ -876,11 +876,14 @@ int num_sms() {
 template <int BN, bool I8>
 int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& p, cudaStream_t s) {
     using C = Cfg<BN>;
-    static bool attr_done = false;
-    if (!attr_done) {
-        B200FC_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, I8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         C::SMEM_BYTES));
-        attr_done = true;
+    static std::atomic<unsigned long long> attr_devices{0};
+    {
+        const int arc = once_per_device(attr_devices, [] {
+            B200FC_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, I8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             C::SMEM_BYTES));
+            return (int)B200FC_OK;
+        });
+        if (arc) return arc;
     }
     int tiles = p.tiles_m * p.tiles_n;
     int grid = tiles < num_sms() ? tiles : num_sms();
@@ -893,11 +896,14 @@ int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& p
 template <int BN, bool I8>
 int launch_cfg2(const CUtensorMap& ma, const CUtensorMap& mw, GemmParams p, cudaStream_t s) {
     using C = Cfg2<BN>;
-    static bool attr_done = false;
-    if (!attr_done) {
-        B200FC_CUDA(cudaFuncSetAttribute(gemm_tc2_kernel<BN, I8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         C::SMEM_BYTES));
-        attr_done = true;
+    static std::atomic<unsigned long long> attr_devices{0};
+    {
+        const int arc = once_per_device(attr_devices, [] {
+            B200FC_CUDA(cudaFuncSetAttribute(gemm_tc2_kernel<BN, I8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             C::SMEM_BYTES));
+            return (int)B200FC_OK;
+        });
+        if (arc) return arc;
     }
     const int tiles = p.tiles_m * p.tiles_n;
     const int max_pairs = num_sms() / 2;
@@ -1004,10 +1010,13 @@ int launch_gemm_tc_allreduce(const void* W_data, int W_K_pad, int W_N_pad, const
     rc = make_map(&mw, W_data, false, (uint64_t)W_K_pad, (uint64_t)W_N_pad, (uint64_t)W_K_pad * 2, 128);
     if (rc) return rc;
     using C = Cfg2<256>;
-    static bool attr_done = false;
-    if (!attr_done) {
-        B200FC_CUDA(cudaFuncSetAttribute(gemm_tc2_kernel<256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-        attr_done = true;
+    static std::atomic<unsigned long long> attr_devices{0};
+    {
+        const int arc = once_per_device(attr_devices, [] {
+            B200FC_CUDA(cudaFuncSetAttribute(gemm_tc2_kernel<256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+            return (int)B200FC_OK;
+        });
+        if (arc) return arc;
     }
     // the whole grid must be resident (reducing pairs wait for multiplying pairs of every GPU): one CTA per SM
     gemm_tc2_kernel<256, false><<<2 * all_pairs, NUM_THREADS, C::SMEM_BYTES, s>>>(ma, mw, p);

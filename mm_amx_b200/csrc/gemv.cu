@@ -368,10 +368,13 @@ int launch_variant(const GemvParams& p, int row_ctas, cudaStream_t s) {
     constexpr int XROW = CHUNK_K * 2 + (W8 ? 16 : 64);
     constexpr int SMEM = 8 * NT * XROW + (W8 ? 8 * NT * (WARPS + 1) * 4 : 0);
     static_assert(SMEM >= ROWS_PER_CTA * 8 * NT * 4, "partial tile must fit the staging buffer");
-    static bool attr_done = false;
-    if (!attr_done) {
-        B200FC_CUDA(cudaFuncSetAttribute(gemv_kernel<W8, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-        attr_done = true;
+    static std::atomic<unsigned long long> attr_devices{0};
+    {
+        const int arc = once_per_device(attr_devices, [] {
+            B200FC_CUDA(cudaFuncSetAttribute(gemv_kernel<W8, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+            return (int)B200FC_OK;
+        });
+        if (arc) return arc;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(row_ctas, p.splits, 1);

@@ -435,10 +435,13 @@ template <bool W8, int NT>
 int launch_variant(const CUtensorMap& map, const Params& p, int row_ctas, cudaStream_t s) {
     using L = Layout<W8, NT>;
     static_assert(L::MP * L::XROW >= 2 * ROWS_PER_CTA * L::MP * 4, "partial tiles must fit the activation buffer");
-    static bool attr_done = false;
-    if (!attr_done) {
-        B200FC_CUDA(cudaFuncSetAttribute(gemv_tma_kernel<W8, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM));
-        attr_done = true;
+    static std::atomic<unsigned long long> attr_devices{0};
+    {
+        const int arc = once_per_device(attr_devices, [] {
+            B200FC_CUDA(cudaFuncSetAttribute(gemv_tma_kernel<W8, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM));
+            return (int)B200FC_OK;
+        });
+        if (arc) return arc;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(row_ctas, p.splits, 1);
