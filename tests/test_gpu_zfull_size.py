@@ -1,0 +1,170 @@
+"""GPU: the BASELINE configurations at their FULL sizes, where the CPU oracle would take minutes.
+
+The small-shape tests pin the kernels against the oracle bit for bit; here the same entry points run the shapes the
+benchmark is quoted on and are checked against an independent full-size computation on the same GPU (torch fp32 /
+fp64 matmuls, not this library) and through properties that do not depend on the size:
+  * int8 x int8 accumulators equal the fp64 product exactly (|acc| < 2^53);
+  * bf16 paths stay within max|err| <= 1e-2 * max|ref|, the bar of the bf16 paths;
+  * the decode kernels (M <= 16) and the GEMM (M > 16) agree on the rows they share;
+  * the MLP is positively homogeneous in the down projection: scaling `down` by 2 (exact in bf16) doubles the output
+    bit for bit.
+The reference builders are plain functions of torch tensors so that a CPU test can run them on tiny shapes.
+"""
+import pytest
+import torch
+
+from mm_amx_b200 import capi
+
+BAR = 1e-2   # max|err| / max|ref| for bf16 paths
+
+
+def rel_to_max(got, ref):
+    return float((got.float() - ref.float()).abs().max() / ref.float().abs().max())
+
+
+def mlp_reference(x, gate, up, down):
+    """fp32 products, bf16 rounding of the activation and of the output, like the reference's mlp_ref
+    (tests/amx-mlp.cpp:811-819)."""
+    act = (torch.nn.functional.silu(x.float() @ gate.float().T) * (x.float() @ up.float().T)).to(torch.bfloat16)
+    return (act.float() @ down.float().T).to(torch.bfloat16)
+
+
+def int8_weight_reference(x, wq, scale):
+    """bf16 activations x int8 weights, per-output-channel fp32 scale, bf16 output (BASELINE config 3)."""
+    return ((x.float() @ wq.float().T) * scale[None, :]).to(torch.bfloat16)
+
+
+def randn_bf16(shape, std, gen, device):
+    return (torch.randn(shape, generator=gen, device=device) * std).to(torch.bfloat16)
+
+
+def run_mlp(x, gate, up, down):
+    M, K = x.shape
+    mlp = capi.Mlp(gate.data_ptr(), up.data_ptr(), down.data_ptr(), K, gate.shape[0])
+    out = torch.empty((M, K), dtype=torch.bfloat16, device=x.device)
+    mlp.run(x.data_ptr(), K * 2, M, out.data_ptr(), K * 2)
+    capi.sync_check()
+    return out, mlp
+
+
+@pytest.mark.gpu
+def test_config1_bf16_linear_256x4096x4096_bias():
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev); g.manual_seed(1001)
+    M, K, N = 256, 4096, 4096
+    A = (torch.rand((M, K), generator=g, device=dev) * 2 - 1).to(torch.bfloat16)
+    B = (torch.rand((N, K), generator=g, device=dev) * 2 - 1).to(torch.bfloat16)      # [N, K]: transposeB
+    bias = torch.randn(N, generator=g, device=dev)
+    w = capi.Weight(B.data_ptr(), capi.BF16, K, N, K * 2, True)
+    C = torch.empty((M, N), dtype=torch.float32, device=dev)
+    ep = capi.make_epilogue(C.data_ptr(), N * 4, capi.F32, capi.STEP_BIAS, bias.data_ptr())
+    w.matmul(A.data_ptr(), capi.BF16, M, K, K * 2, ep)
+    capi.sync_check()
+    ref = A.float() @ B.float().T + bias[None, :]
+    assert rel_to_max(C, ref) < 1e-4          # fp32 output: far inside the bf16 bar
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,K,N", [(2048, 4096, 22016), (2048, 11008, 4096), (4096, 8192, 7168)])
+def test_llama_shaped_gemms_against_fp32(M, K, N):
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev); g.manual_seed(M + N)
+    A = randn_bf16((M, K), 1.0, g, dev)
+    B = randn_bf16((N, K), 0.02, g, dev)
+    w = capi.Weight(B.data_ptr(), capi.BF16, K, N, K * 2, True)
+    C = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    ep = capi.make_epilogue(C.data_ptr(), N * 2, capi.BF16)
+    w.matmul(A.data_ptr(), capi.BF16, M, K, K * 2, ep)
+    capi.sync_check()
+    ref = A.float() @ B.float().T
+    assert rel_to_max(C, ref) < BAR
+    # decode kernel and GEMM agree on shared rows (both round the same fp32 sums to bf16, up to summation order)
+    C4 = torch.empty((4, N), dtype=torch.bfloat16, device=dev)
+    ep4 = capi.make_epilogue(C4.data_ptr(), N * 2, capi.BF16)
+    w.matmul(A.data_ptr(), capi.BF16, 4, K, K * 2, ep4)
+    capi.sync_check()
+    assert rel_to_max(C4, ref[:4]) < BAR
+    assert rel_to_max(C4, C[:4]) < BAR
+
+
+@pytest.mark.gpu
+def test_config4_int8_2048x4096x4096_exact():
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev); g.manual_seed(1004)
+    M, K, N = 2048, 4096, 4096
+    A = torch.randint(-128, 128, (M, K), generator=g, device=dev, dtype=torch.int8)
+    B = torch.randint(-128, 128, (N, K), generator=g, device=dev, dtype=torch.int8)
+    w = capi.Weight(B.data_ptr(), capi.S8, K, N, K, True)
+    C = torch.empty((M, N), dtype=torch.int32, device=dev)
+    ep = capi.make_epilogue(C.data_ptr(), N * 4, capi.S32)
+    w.matmul(A.data_ptr(), capi.S8, M, K, K, ep)
+    capi.sync_check()
+    ref = (A.double() @ B.double().T).to(torch.int64)      # exact: |acc| <= 2^26
+    assert torch.equal(C.to(torch.int64), ref)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("N", [4096, 11008])
+@pytest.mark.parametrize("M", [1, 4, 16])
+def test_config3_int8_weight_gemv(M, N):
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev); g.manual_seed(1003 + M + N)
+    K = 4096
+    x = randn_bf16((M, K), 1.0, g, dev)
+    wq = torch.randint(-127, 128, (N, K), generator=g, device=dev, dtype=torch.int8)
+    scale = torch.rand(N, generator=g, device=dev) * 0.019 + 0.001
+    w = capi.Weight(wq.data_ptr(), capi.S8, K, N, K, True, capi.PACK_INT8_CHANNEL, scale.data_ptr())
+    C = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    ep = capi.make_epilogue(C.data_ptr(), N * 2, capi.BF16, capi.STEP_DEQUANT)
+    w.matmul(x.data_ptr(), capi.BF16, M, K, K * 2, ep)
+    capi.sync_check()
+    assert rel_to_max(C, int8_weight_reference(x, wq, scale)) < BAR
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M", [1, 16, 256, 2048])
+def test_config2_llama7b_mlp(M):
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev); g.manual_seed(1002)
+    H, I = 4096, 11008
+    gate, up, down = randn_bf16((I, H), 0.02, g, dev), randn_bf16((I, H), 0.02, g, dev), randn_bf16((H, I), 0.02, g, dev)
+    x = randn_bf16((M, H), 1.0, g, dev)
+    out, _ = run_mlp(x, gate, up, down)
+    assert rel_to_max(out, mlp_reference(x, gate, up, down)) < BAR
+    # scaling the down projection by 2 is exact in bf16 and in every fp32 sum: the output doubles bit for bit
+    out2, _ = run_mlp(x, gate, up, (down.float() * 2).to(torch.bfloat16))
+    assert torch.equal(out2.float(), out.float() * 2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M", [16, 1024])
+def test_config5_llama70b_mlp_shard_of_8(M):
+    """one rank's share at tensor-parallel size 8 (rows of gate/up and columns of down), fp32 contribution"""
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev); g.manual_seed(1005)
+    H, Is = 8192, 28672 // 8
+    gate, up, down = randn_bf16((Is, H), 0.02, g, dev), randn_bf16((Is, H), 0.02, g, dev), randn_bf16((H, Is), 0.02, g, dev)
+    x = randn_bf16((M, H), 1.0, g, dev)
+    mlp = capi.Mlp(gate.data_ptr(), up.data_ptr(), down.data_ptr(), H, Is)
+    part = torch.empty((M, H), dtype=torch.float32, device=dev)
+    mlp.run_partial(x.data_ptr(), H * 2, M, part.data_ptr(), capi.F32, H * 4)
+    capi.sync_check()
+    act = (torch.nn.functional.silu(x.float() @ gate.float().T) * (x.float() @ up.float().T)).to(torch.bfloat16)
+    ref = act.float() @ down.float().T
+    assert rel_to_max(part, ref) < BAR
+
+
+def test_reference_builders_on_cpu():
+    """the reference functions above, on tiny CPU tensors (no GPU, no library call): shapes, dtypes, homogeneity"""
+    g = torch.Generator(); g.manual_seed(0)
+    x = randn_bf16((3, 64), 1.0, g, "cpu")
+    gate, up, down = randn_bf16((96, 64), 0.1, g, "cpu"), randn_bf16((96, 64), 0.1, g, "cpu"), randn_bf16((64, 96), 0.1, g, "cpu")
+    ref = mlp_reference(x, gate, up, down)
+    assert ref.shape == (3, 64) and ref.dtype == torch.bfloat16
+    ref2 = mlp_reference(x, gate, up, (down.float() * 2).to(torch.bfloat16))
+    assert torch.equal(ref2.float(), ref.float() * 2)
+    wq = torch.randint(-127, 128, (32, 64), generator=g, dtype=torch.int8)
+    scale = torch.rand(32, generator=g) * 0.019 + 0.001
+    r = int8_weight_reference(x, wq, scale)
+    assert r.shape == (3, 32) and r.dtype == torch.bfloat16
+    assert rel_to_max(r, r) == 0.0
