@@ -7,7 +7,8 @@ Workloads (synthetic, seeded; shapes from the reference's own benchmark configur
   llama7b_mlp   x[M,4096] ~N(0,1), W_gate/W_up [11008,4096], W_down [4096,11008] ~N(0,0.02), bf16, fp32 accumulate,
                 bf16 output.  Default at 1 GPU with M = 2048 (prefill-shaped, tensor-core bound).
   llama70b_mlp  hidden 8192, intermediate 28672, M = 4096, tensor-parallel over N GPUs (gate/up column split, down
-                row split, one all-reduce on the output).  Default when N > 1; strong scaling.
+                row split, one all-reduce on the output: inside the down-projection kernel when torch symmetric
+                memory offers an NVLink multicast mapping, else NCCL; --tp-mode).  Default when N > 1; strong scaling.
 A step is one MLP forward over one batch.  value = 6*M*H*I flops / time, whole job.  Weights (>= 270 MB) exceed the
 126 MB L2, so every step streams them from HBM again.
 

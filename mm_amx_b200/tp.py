@@ -1,5 +1,9 @@
 """Megatron-style tensor-parallel Llama MLP: one process per GPU, one all-reduce on the down-projection output.
 
+Three ways to do that all-reduce: PullFusedTensorParallelMLP (inside the down-projection kernel; the fastest, needs
+torch symmetric memory with an NVLink multicast mapping), TensorParallelMLP (torch.distributed: NCCL on GPUs, gloo in
+the CPU tests), FusedTensorParallelMLP (multimem.red from the epilogue).
+
 The reference shards the same way across CPU cores: gate/up by output channels (Linear::setup, tests/amx-mlp.cpp:554-593)
 and the down projection by K with an fp32 add of the partial results before the bf16 rounding (:559-589, :656-683).
 Here rank r keeps rows [r*N/t, (r+1)*N/t) of gate and up and the same columns of down; every rank computes its
@@ -124,8 +128,9 @@ class FusedTensorParallelMLP:
     address.  The GEMM epilogue adds each rank's contribution into all replicas with `multimem.red`
     (b200fc_mlp_down_reduce), so the transfer overlaps the math tile by tile and no collective kernel runs.
     Per step and rank:  zero own replica -> barrier -> gate/up -> down + in-switch reduce -> barrier.
-    Every replica receives every rank's contribution (ingress = world x output bytes), so this pays for small
-    tensor-parallel groups; larger groups use TensorParallelMLP (chunked all-reduce overlapping the GEMMs).
+    Every replica receives every rank's contribution (ingress = world x output bytes) and the in-switch atomics slow
+    the epilogue; PullFusedTensorParallelMLP below moves the optimal number of bytes and measured faster at every
+    group size.
     Needs M > 16 and a CUDA build of torch with symmetric memory + multicast support.
     """
 
