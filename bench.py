@@ -41,6 +41,28 @@ WORKLOADS = {
 NCU_TRAFFIC_BYTES = {"llama7b_mlp": 233.73e6, "llama70b_mlp": None}  # profiles/gemm_tc2_kernel_llama7b_mlp_M2048.md
 
 
+_REAL_STDOUT = None
+
+
+def claim_stdout():
+    """The contract is ONE JSON line on stdout, but native libraries write to file descriptor 1 too (NCCL prints its
+    version there).  Keep a private duplicate of the real stdout for the JSON line and point descriptor 1 at stderr
+    for everything else."""
+    global _REAL_STDOUT
+    if _REAL_STDOUT is None:
+        sys.stdout.flush()
+        _REAL_STDOUT = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line):
+    data = (json.dumps(line) + "\n").encode()
+    if _REAL_STDOUT is None:
+        sys.stdout.write(data.decode()); sys.stdout.flush()
+    else:
+        os.write(_REAL_STDOUT, data)
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -164,7 +186,7 @@ def run_reference(args, w, M, name):
                        "cold": "weights larger than last-level cache"},
             "cpu_baseline": info,
             "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ------------------------------------------------------------------------------------------------ GPU arm
@@ -384,7 +406,7 @@ def run_ours(args, w, M, name):
             line["cpu_baseline"] = {"value": None, "unit": "TFLOP/s", "cores": 0, "kind": "port",
                                     "sample": "failed: %s" % ex}
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -492,6 +514,7 @@ def main():
     ap.add_argument("--legs", default="kernel,e2e,decode,configs,cpu",
                     help="optional legs after the main timed loop (comma list of kernel,e2e,decode,configs,cpu; '' = none)")
     args = ap.parse_args()
+    claim_stdout()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1:
         args.gpus = world
