@@ -21,6 +21,7 @@ plain C++ oracle port), clocks sampled during the timed region, and the number o
 """
 import argparse
 import ctypes
+import datetime
 import json
 import os
 import subprocess
@@ -74,12 +75,16 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+    """Samples SM clocks and throttle reasons with nvidia-smi.  The process is started before the warm-up (it needs
+    tens of milliseconds to produce its first line) and every line carries nvidia-smi's own timestamp; the summary
+    uses the samples that fall inside the timed region, marked with begin() / end()."""
+    Q = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, index):
         self.index, self.proc, self.lines = index, None, []
+        self.t0 = self.t1 = None
 
     def start(self):
         try:
@@ -95,30 +100,57 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    def begin(self):
+        self.t0 = datetime.datetime.now()
+
+    def end(self):
+        self.t1 = datetime.datetime.now()
+
     def stop(self):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.03)   # let the sample that covers the end of the region arrive
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except Exception:
             pass
-        mhz, mx, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
-            f = [x.strip() for x in ln.split(",")]
-            if len(f) < 6:
-                continue
-            try:
-                mhz.append(float(f[0])); mx = float(f[1])
-            except ValueError:
-                continue
-            for n, v in zip(names, f[2:6]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        mhz.sort()
-        med = mhz[len(mhz) // 2] if mhz else None
-        return {"sm_mhz": med, "sm_max_mhz": mx, "samples": len(mhz), "reasons": sorted(reasons)}
+        return summarise_clock_lines(self.lines, self.t0, self.t1)
+
+
+def summarise_clock_lines(lines, t0, t1):
+    """lines: 'YYYY/MM/DD HH:MM:SS.mmm, sm MHz, max MHz, 4 x Active|Not Active'.  Samples stamped inside [t0, t1] (one
+    sampling period of slack) are used; if none is, the last lines read (sampling stops right after the region); if the
+    timestamps cannot be read, all samples."""
+    rows = []
+    for ln in lines:
+        f = [x.strip() for x in ln.split(",")]
+        if len(f) < 7:
+            continue
+        try:
+            mhz, mx = float(f[1]), float(f[2])
+        except ValueError:
+            continue
+        try:
+            ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f")
+        except ValueError:
+            ts = None
+        rows.append((ts, mhz, mx, [n for n, v in zip(ClockSampler.NAMES, f[3:7]) if v.lower().startswith("active")]))
+    window = "all samples"
+    if rows and t0 is not None and t1 is not None and all(r[0] is not None for r in rows):
+        slack = datetime.timedelta(milliseconds=20)
+        inside = [r for r in rows if t0 - slack <= r[0] <= t1 + slack]
+        if inside:
+            rows, window = inside, "timed region"
+        else:
+            # no stamp inside the region (clock or time-zone mismatch between nvidia-smi and this process): sampling
+            # stops right after the region, so the last lines read are the ones that cover it
+            n = max(2, int((t1 - t0).total_seconds() / 0.02) + 1)
+            rows, window = rows[-n:], "last samples before the end of the timed region"
+    mhz = sorted(r[1] for r in rows)
+    reasons = sorted({n for r in rows for n in r[3]})
+    return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": rows[-1][2] if rows else None,
+            "samples": len(mhz), "window": window, "reasons": reasons}
 
 
 def flops_of(w, M):
@@ -203,6 +235,9 @@ def run_ours(args, w, M, name):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     capi.lib()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()     # long before the timed region: the synthetic weights are created and packed meanwhile
     H, I = w["H"], w["I"]
     Is = I // world
     stream = torch.cuda.current_stream().cuda_stream
@@ -272,17 +307,16 @@ def run_ours(args, w, M, name):
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     l0 = capi.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    sampler.begin()
     e0.record()
     for _ in range(args.steps):
         step()
     e1.record()
     barrier()
+    sampler.end()
     launches = capi.launch_count() - l0
     ms = e0.elapsed_time(e1) / args.steps
     capi.sync_check(stream)
