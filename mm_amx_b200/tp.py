@@ -89,19 +89,22 @@ class TensorParallelMLP:
         if partial is None:
             partial = out if self.partial_dtype == torch.bfloat16 else torch.empty((M, self.K), dtype=torch.float32,
                                                                                    device=x.device)
-        chunk = self.chunk_rows if (self.chunk_rows and x.is_cuda and self.world > 1) else M
+        chunk = self.chunk_rows if (self.chunk_rows and self.world > 1) else M
         if chunk >= M:
             self.local.run_partial(x, partial)
             if self.world > 1:
                 dist.all_reduce(partial, group=self.group)
             self._round(partial, out)
             return out
-        # chunked: the collective of finished rows runs on a side stream while the following rows are multiplied.
+        # chunked: the collective of finished rows runs on a side stream while the following rows are multiplied
+        # (CUDA; on CPU tensors the same row blocks are reduced one after the other).
         # When the local object can run the two stages separately, gate/up runs once over all rows (full GEMM waves)
         # and only the down projection is cut into row blocks; otherwise whole forwards are chunked.
-        if self._comm_stream is None:
-            self._comm_stream = torch.cuda.Stream()
-        cur = torch.cuda.current_stream()
+        overlap = x.is_cuda
+        if overlap:
+            if self._comm_stream is None:
+                self._comm_stream = torch.cuda.Stream()
+            cur = torch.cuda.current_stream()
         staged = hasattr(self.local, "gate_up") and hasattr(self.local, "down_rows")
         if staged:
             self.local.gate_up(x)
@@ -111,12 +114,16 @@ class TensorParallelMLP:
                 self.local.down_rows(m0, m1 - m0, partial[m0:m1])
             else:
                 self.local.run_partial(x[m0:m1], partial[m0:m1])
-            ev = torch.cuda.Event()
-            ev.record(cur)
-            with torch.cuda.stream(self._comm_stream):
-                self._comm_stream.wait_event(ev)
+            if overlap:
+                ev = torch.cuda.Event()
+                ev.record(cur)
+                with torch.cuda.stream(self._comm_stream):
+                    self._comm_stream.wait_event(ev)
+                    dist.all_reduce(partial[m0:m1], group=self.group)
+            else:
                 dist.all_reduce(partial[m0:m1], group=self.group)
-        cur.wait_stream(self._comm_stream)
+        if overlap:
+            cur.wait_stream(self._comm_stream)
         self._round(partial, out)
         return out
 

@@ -30,10 +30,30 @@ class OracleLocal:
         from oracle import port
         xb = x.contiguous().view(torch.int16).numpy().view(np.uint16)
         _, part = port.mlp(xb, self.g, self.u, self.d, want_partial=True)
+        self._store(part, out)
+
+    @staticmethod
+    def _store(part, out):
+        from oracle import port
         if out.dtype == torch.float32:
             out.copy_(torch.from_numpy(part))
         else:
             out.copy_(torch.from_numpy(port.f32_to_bf16(part).view(np.int16)).view(torch.bfloat16))
+
+
+class StagedOracleLocal(OracleLocal):
+    """also offers the two stages on their own, like tp.CudaLocalMLP: gate_up() keeps the activation, down_rows()
+    multiplies a block of its rows"""
+
+    def gate_up(self, x):
+        from oracle import port
+        xb = x.contiguous().view(torch.int16).numpy().view(np.uint16)
+        _, self.act = port.mlp(xb, self.g, self.u, self.d, want_act=True)
+
+    def down_rows(self, row0, rows, out):
+        from oracle import port
+        part = port.gemm_bf16(np.ascontiguousarray(self.act[row0:row0 + rows]), np.ascontiguousarray(self.d.T))
+        self._store(part, out)
 
 
 def worker(rank, world, port_no, results):
@@ -62,6 +82,12 @@ def worker(rank, world, port_no, results):
         gathered = [torch.empty_like(out) for _ in range(world)]
         dist.all_gather(gathered, out)
         assert all(torch.equal(g, gathered[0]) for g in gathered)
+    # row blocks: whole forwards per block, and gate/up once + the down projection per block (ragged last block)
+    for local_cls in (OracleLocal, StagedOracleLocal):
+        m = tp.TensorParallelMLP(local_cls(gate, up, down, rank, world), K, partial_dtype=torch.float32, chunk_rows=4)
+        out = m.forward(x)
+        got = (bits(out).astype(np.uint32) << 16).view(np.float32)
+        errs.append(float(np.abs(got - full_f).max() / np.abs(full_f).max()))
     results[rank] = errs
     dist.destroy_process_group()
 
@@ -74,9 +100,10 @@ def test_tensor_parallel_mlp_world2_gloo():
     mp.spawn(worker, args=(world, port_no, results), nprocs=world, join=True)
     assert len(results) == world
     for r in range(world):
-        e32, e16 = results[r]
+        e32, e16, e_blocks, e_staged = results[r]
         assert e32 < 4e-3      # fp32 partial sum, one bf16 rounding (a bf16 ulp is 2^-8 = 3.9e-3 of the value)
         assert e16 < 1e-2      # bf16 partials: the bound of the bf16 paths
+        assert e_blocks == e32 and e_staged < 4e-3   # row blocks change nothing; the staged path sums the same shards
 
 
 def test_shard_rows():
