@@ -75,6 +75,11 @@ int b200fc_set_sm_limit(int sms);
 /* waits for `stream` and reports whether any kernel of this library gave up on a bounded wait since the last check
  * (B200FC_ERR_KERNEL); the _host entry points do this themselves */
 int b200fc_sync_check(void* stream);
+/* Every wait inside a kernel (on a shared-memory barrier, on another GPU's arrival counter) is bounded; a wait that
+ * runs out makes the kernel stop cleanly and b200fc_sync_check report B200FC_ERR_KERNEL.  Sets that bound for
+ * kernels launched from now on (default 2 s; at least 1 us).  The reference has no counterpart (its only rendez-vous
+ * is an atomic between two threads, tests/amx-mlp.cpp:656-660). */
+int b200fc_set_wait_limit_ns(uint64_t ns);
 
 /* ---- packed weights: the `internalB` cache of amx_kernel::Matmul (include/kernels_amx.hpp:1045-1072) ---------- */
 typedef struct b200fc_weight b200fc_weight_t;
@@ -190,16 +195,21 @@ int b200fc_mlp_run_host(b200fc_mlp_t* mlp, const void* x, int64_t ldx_bytes, int
  * reference.  For callers that may not enter the CUDA allocator while they run (a serving loop with a frozen memory
  * plan, code that must not trigger the device synchronisation cudaMalloc / cudaFree imply).  The gate/up activation
  * lives in a fixed 1 MiB device array inside the library image, so M * (N / tp) * 2 bytes must not exceed
- * b200fc_mlp_decode_static_capacity(); larger requests fail with B200FC_ERR_INVALID.  out is [M, K] in out_dtype
- * B200FC_BF16 (the full result when tp_size == 1) or B200FC_F32 / B200FC_BF16 (this rank's contribution otherwise).
- *   - The first call on each device looks up the array's device address; make that first call during start-up,
- *     before any stream capture begins.
- *   - All calls on a device share the one array: calls whose kernels can overlap on the GPU (different streams
- *     without ordering) race on it.  Calls on one stream are ordered and safe.
- *   - The array keeps the previous call's activation; every element a call reads it has written first. */
+ * b200fc_mlp_decode_static_capacity(); larger requests fail with B200FC_ERR_INVALID.  A second fixed array (about
+ * 5 MiB) holds the decode kernel's partial sums and arrival counters; b200fc_mlp_decode_static_footprint() is the total
+ * every GPU that loads the library holds until the process exits.  out is [M, K] in out_dtype B200FC_BF16 (the full
+ * result when tp_size == 1) or B200FC_F32 / B200FC_BF16 (this rank's contribution otherwise).
+ *   - The first call on each device looks up the device addresses of these arrays and of the library's status word
+ *     (all three are part of the image: nothing is allocated) and sets the kernels' shared-memory attribute; make
+ *     that first call during start-up, before any stream capture begins.
+ *   - All calls on a device share the arrays: calls whose kernels can overlap on the GPU (different streams
+ *     without ordering) race on them.  Calls on one stream are ordered and safe.
+ *   - The arrays keep the previous call's contents; every element a call reads it has written first, and the
+ *     counters are back at zero when a call's kernels finish. */
 int b200fc_mlp_run_decode_static(b200fc_mlp_t* mlp, const void* x, int64_t ldx_bytes, int M, void* out, int out_dtype,
                                  int64_t ldo_bytes, void* stream);
 int64_t b200fc_mlp_decode_static_capacity(void);
+int64_t b200fc_mlp_decode_static_footprint(void);
 /* device pointer to the [M, N/tp] bf16 activation of the last run (debug / layer-wise parity) */
 const void* b200fc_mlp_act(const b200fc_mlp_t* mlp);
 

@@ -33,6 +33,7 @@ SIGNATURES = {
     "b200fc_version": (ctypes.c_char_p, []),
     "b200fc_launch_count": (c_i64, []),
     "b200fc_sync_check": (c_int, [c_void_p]),
+    "b200fc_set_wait_limit_ns": (c_int, [ctypes.c_uint64]),
     "b200fc_set_sm_limit": (c_int, [c_int]),
     "b200fc_weight_pack": (c_int, [c_void_p, c_int, c_int, c_int, c_i64, c_int, c_int, c_void_p,
                                    ctypes.POINTER(c_void_p), c_void_p]),
@@ -63,6 +64,7 @@ SIGNATURES = {
     "b200fc_mlp_run_host": (c_int, [c_void_p, c_void_p, c_i64, c_int, c_void_p, c_i64, c_void_p]),
     "b200fc_mlp_run_decode_static": (c_int, [c_void_p, c_void_p, c_i64, c_int, c_void_p, c_int, c_i64, c_void_p]),
     "b200fc_mlp_decode_static_capacity": (c_i64, []),
+    "b200fc_mlp_decode_static_footprint": (c_i64, []),
     "b200fc_mlp_act": (c_void_p, [c_void_p]),
     "b200fc_device_malloc": (c_int, [ctypes.POINTER(c_void_p), c_i64]),
     "b200fc_device_free": (c_int, [c_void_p]),
@@ -113,6 +115,11 @@ def set_sm_limit(sms):
 
 def sync_check(stream=None):
     check(lib().b200fc_sync_check(stream))
+
+
+def set_wait_limit_ns(ns):
+    """Bound of every wait inside the kernels (default 2 s); see b200fc_set_wait_limit_ns in include/b200fc.h."""
+    check(lib().b200fc_set_wait_limit_ns(int(ns)))
 
 
 def make_epilogue(C, ldc_bytes, out_dtype, steps=0, bias=None, deq_scale=1.0, deq_scale_per_oc=None, q_scale=1.0,

@@ -30,18 +30,24 @@ void count_launch(int n) { g_launches += n; }
 static std::atomic<int> g_sm_limit{0};
 int sm_limit() { return g_sm_limit.load(); }
 
+static std::atomic<unsigned long long> g_wait_limit_ns{2000000000ull};
+unsigned long long wait_limit_ns() { return g_wait_limit_ns.load(); }
+
 static std::mutex g_mu;
 static std::map<int, int*> g_status;  // per device
 
+// The status word is part of the library image (zero when a device loads it), so no call ever has to allocate it;
+// host code needs its device address, looked up once per device.
+static __device__ int g_status_word;
+
 int* kernel_status_word() {
     int dev = 0;
-    cudaGetDevice(&dev);
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
     std::lock_guard<std::mutex> lk(g_mu);
     auto it = g_status.find(dev);
     if (it != g_status.end()) return it->second;
     int* p = nullptr;
-    if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) return nullptr;
-    cudaMemset(p, 0, sizeof(int));
+    if (cudaGetSymbolAddress((void**)&p, g_status_word) != cudaSuccess || !p) { cudaGetLastError(); return nullptr; }
     g_status[dev] = p;
     return p;
 }
@@ -80,6 +86,7 @@ int get_stream_scratch(size_t bytes, cudaStream_t s, int slot, void** out) {
         if (sc.p) { cudaStreamSynchronize(s); cudaFree(sc.p); sc.p = nullptr; sc.bytes = 0; }
         B200FC_CUDA(cudaMalloc(&sc.p, bytes));
         sc.bytes = bytes;
+        B200FC_CUDA(cudaMemsetAsync(sc.p, 0, bytes, s));
     }
     *out = sc.p;
     return B200FC_OK;
@@ -163,7 +170,7 @@ static int validate_epilogue(const b200fc_epilogue_t* ep, bool int_acc) {
 }
 
 int matmul_device(const Weight& w, Weight* w_mut, const void* A, int dtypeA, int M, int K, int64_t lda, int n0,
-                         int n1, const b200fc_epilogue_t* ep_in, cudaStream_t s) {
+                  int n1, const b200fc_epilogue_t* ep_in, cudaStream_t s, void* gemv_scratch) {
     if (M < 0 || K != w.K) { set_error("matmul: K=%d does not match the packed weights (K=%d) or M<0", K, w.K); return B200FC_ERR_INVALID; }
     if (n0 < 0 || n1 > w.N || n0 > n1) { set_error("matmul: column range [%d,%d) outside [0,%d)", n0, n1, w.N); return B200FC_ERR_INVALID; }
     const bool a8 = dtypeA == B200FC_S8 || dtypeA == B200FC_U8;
@@ -191,7 +198,7 @@ int matmul_device(const Weight& w, Weight* w_mut, const void* A, int dtypeA, int
         return B200FC_ERR_INVALID;
     }
 
-    if (!a8 && M <= 16) return launch_gemv(w, A, M, K, lda, n0, n1, ep, s);
+    if (!a8 && M <= 16) return launch_gemv_tma(w, A, M, K, lda, n0, n1, ep, s, gemv_scratch);
 
     // tensor-core path: TMA needs a 16-byte aligned base and leading dimension
     const void* A_use = A;
@@ -268,6 +275,12 @@ int b200fc_set_sm_limit(int sms) {
 }
 
 int b200fc_sync_check(void* stream) { return check_kernel_status((cudaStream_t)stream); }
+
+int b200fc_set_wait_limit_ns(uint64_t ns) {
+    if (ns < 1000) { set_error("set_wait_limit_ns: limit below one microsecond"); return B200FC_ERR_INVALID; }
+    g_wait_limit_ns = ns;
+    return B200FC_OK;
+}
 
 int b200fc_weight_pack(const void* B, int dtypeB, int K, int N, int64_t ldb, int transposeB, int pack_mode,
                        const float* scales, b200fc_weight_t** out, void* stream) {
@@ -726,9 +739,21 @@ int b200fc_add_round_bf16(const float* a, const float* b, void* out, int64_t n, 
 }
 
 int b200fc_flush_l2(void* stream) {
-    static void* buf = nullptr;
+    static std::map<int, void*> bufs;               // one buffer per device, under g_mu
     static const size_t bytes = (size_t)256 << 20;  // twice the 126 MB L2
-    if (!buf) B200FC_CUDA(cudaMalloc(&buf, bytes));
+    int dev = 0;
+    B200FC_CUDA(cudaGetDevice(&dev));
+    void* buf = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        auto it = bufs.find(dev);
+        if (it == bufs.end()) {
+            B200FC_CUDA(cudaMalloc(&buf, bytes));
+            bufs[dev] = buf;
+        } else {
+            buf = it->second;
+        }
+    }
     return launch_fill(buf, bytes, (cudaStream_t)stream);
 }
 

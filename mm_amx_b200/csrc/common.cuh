@@ -87,8 +87,11 @@ void count_launch(int n = 1);
 int* kernel_status_word();  // device int, 0 = OK; kernels store a non-zero code when a bounded wait runs out
 int check_kernel_status(cudaStream_t s);  // synchronises and reads it
 // growing device scratch owned by (device, stream, slot): work on one stream is ordered, so kernels launched on it
-// may share it; slot 0 = re-strided activations, slot 1 = stream-K partial tiles
+// may share it; slot 0 = re-strided activations, slot 1 = split-K partial tiles of the GEMM, slot 2 = counters and
+// partial sums of the decode kernel (fixed size), slot 3 = fused-MLP activation.  A fresh allocation is zero-filled.
 int get_stream_scratch(size_t bytes, cudaStream_t s, int slot, void** out);
+// time limit of every bounded device-side wait (b200fc_set_wait_limit_ns; 2 s unless changed)
+unsigned long long wait_limit_ns();
 
 #define B200FC_CUDA(call)                                                   \
     do {                                                                    \
@@ -98,8 +101,10 @@ int get_stream_scratch(size_t bytes, cudaStream_t s, int slot, void** out);
 
 // api.cu: validated dispatch of one Matmul call on device pointers (w_mut: the same object when the call may create
 // its lazily built bf16 copy of compressed weights, else null)
+// gemv_scratch: counters + partial-sum slots for the decode kernel (gemv_scratch_bytes(), counters zero), or null to
+// use the stream's own
 int matmul_device(const Weight& w, Weight* w_mut, const void* A, int dtypeA, int M, int K, int64_t lda, int n0, int n1,
-                  const b200fc_epilogue_t* ep, cudaStream_t s);
+                  const b200fc_epilogue_t* ep, cudaStream_t s, void* gemv_scratch = nullptr);
 
 // ---- launchers -------------------------------------------------------------------------------------------------
 // pack.cu
@@ -115,12 +120,13 @@ int launch_copy2d(const void* src, int64_t lds, void* dst, int64_t ldd, int rows
                   cudaStream_t s);
 int launch_add_round_bf16(const float* a, const float* b, void* out, int64_t n, cudaStream_t s);
 int launch_fill(void* p, size_t bytes, cudaStream_t s);
-// gemv.cu: M <= 16, bf16 activations, bf16 or int8 weights
-int launch_gemv(const Weight& w, const void* A, int M, int K, int64_t lda, int n0, int n1, const Epilogue& ep,
-                cudaStream_t s);
-// gemv_tma.cu: the same operation with the weights streamed by TMA through a shared-memory ring
+// gemv_tma.cu: M <= 16, bf16 activations, bf16 or int8 weights streamed by TMA through a shared-memory ring.
+// `scratch`: gemv_scratch_bytes() of device memory whose first kGemvMaxCtas words are zero (the kernel leaves them
+// zero), shared by the launches of one stream; null = the stream's own (allocated on first use).
+constexpr int kGemvMaxCtas = 320;
+size_t gemv_scratch_bytes();
 int launch_gemv_tma(const Weight& w, const void* A, int M, int K, int64_t lda, int n0, int n1, const Epilogue& ep,
-                    cudaStream_t s);
+                    cudaStream_t s, void* scratch);
 // gemm_tc.cu: tcgen05 GEMM, bf16 x bf16 -> fp32 or 8-bit x 8-bit -> int32
 int launch_gemm_tc(const void* W_data, int w_dtype, int W_K_pad, int W_N_pad, const void* A, int dtypeA, int M, int K,
                    int64_t lda, int n0, int n1, const Epilogue& ep, cudaStream_t s);

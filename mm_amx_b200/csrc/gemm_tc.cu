@@ -30,7 +30,6 @@ constexpr int SLAB_BYTES = 128;          // K extent of one pipeline stage, in b
 constexpr int MMA_K_BYTES = 32;          // K extent of one tcgen05.mma (16 bf16 / 32 int8)
 constexpr int NUM_THREADS = 192;
 constexpr int EPI_WARP0 = 2;
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 #ifndef B200FC_EPI_SLEEP_NS
 #define B200FC_EPI_SLEEP_NS 256
 #endif
@@ -68,6 +67,7 @@ struct GemmParams {
     unsigned* ar_flags[8];      // ar_flags[r]: arrival counters of rank r (peer-mapped), two per tile (one per CTA of the pair)
     const char* ar_partial_mc;  // multicast address of all replicas of the partial buffer
     char* ar_out_mc;            // multicast address of all replicas of the output buffer
+    unsigned long long wait_limit_ns;  // every bounded wait gives up after this long
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------------------------
@@ -101,14 +101,14 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
 // SLEEP_NS > 0: back off between polls (for waits that are long and not latency critical: the epilogue warps wait most
 // of a tile's main loop, and five spinning warps cost issue slots and power that the tensor pipe could use).
 template <int SLEEP_NS = 0>
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, unsigned long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = globaltimer();
     while (true) {
         if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (globaltimer() - t0 > WAIT_LIMIT_NS) {
+        if (globaltimer() - t0 > limit) {
             *abort_flag = 1;
             return false;
         }
@@ -372,7 +372,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
                 const int row_a = tm * BM, row_w = p.n0 + tn * BN;
                 for (int ks = 0; ks < p.k_slabs; ks++) {
-                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.wait_limit_ns)) { ok = false; break; }
                     const unsigned full = bar_full + 8 * stage;
                     mbar_expect_tx(full, C::STAGE_BYTES);
                     const unsigned sa = smem_u32(smem + stage * C::STAGE_BYTES);
@@ -392,11 +392,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, it++) {
             const int ab = it & 1;
             const unsigned acc_phase = (unsigned)(it >> 1) & 1;
-            if (!mbar_wait(bar_acc_empty + 8 * ab, acc_phase ^ 1, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(bar_acc_empty + 8 * ab, acc_phase ^ 1, abort_flag, p.wait_limit_ns)) { ok = false; break; }
             tc_fence_after();
             const unsigned d_tmem = tmem_base + (unsigned)(ab * BN);
             for (int ks = 0; ks < p.k_slabs; ks++) {
-                if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.wait_limit_ns)) { ok = false; break; }
                 tc_fence_after();
                 if (lane == 0) {
                     const unsigned sa = smem_u32(smem + stage * C::STAGE_BYTES);
@@ -425,7 +425,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int ab = it & 1;
             const unsigned acc_phase = (unsigned)(it >> 1) & 1;
             const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-            if (!mbar_wait<EPI_SLEEP_NS>(bar_acc_full + 8 * ab, acc_phase, abort_flag)) { ok = false; break; }
+            if (!mbar_wait<EPI_SLEEP_NS>(bar_acc_full + 8 * ab, acc_phase, abort_flag, p.wait_limit_ns)) { ok = false; break; }
             tc_fence_after();
             const int m = tm * BM + quarter * 32 + lane;
             const bool row_ok = m < p.M;
@@ -564,7 +564,7 @@ __device__ void allreduce_units(const GemmParams& p, int num_tiles, volatile int
                 unsigned v;
                 asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(my_flags + 2 * tile + half) : "memory");
                 if (v >= p.ar_target) break;
-                if (globaltimer() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; break; }
+                if (globaltimer() - t0 > p.wait_limit_ns) { *abort_flag = 1; break; }
             }
         }
         // Thread 0's acquire load and the CTA barrier order every thread's loads below after the arrivals; a
@@ -670,7 +670,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int row_a = tm * (2 * BM) + (int)rank * BM;
                 const int row_w = p.n0 + tn * BN + (int)rank * (BN / 2);
                 for (int ks = ks0; ks < ks1; ks++) {
-                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.wait_limit_ns)) { ok = false; break; }
                     if (leader) mbar_expect_tx(bar_full + 8 * stage, 2 * C::STAGE_BYTES);
                     const unsigned sa = smem_u32(smem + stage * C::STAGE_BYTES);
                     const int kx = ks * (I8 ? SLAB_BYTES : SLAB_BYTES / 2);
@@ -692,11 +692,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int ks0 = p.k_slabs * split / p.splits, ks1 = p.k_slabs * (split + 1) / p.splits;
                 const int ab = it & 1;
                 const unsigned acc_phase = (unsigned)(it >> 1) & 1;
-                if (!mbar_wait(bar_acc_empty + 8 * ab, acc_phase ^ 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(bar_acc_empty + 8 * ab, acc_phase ^ 1, abort_flag, p.wait_limit_ns)) { ok = false; break; }
                 tc_fence_after();
                 const unsigned d_tmem = tmem_base + (unsigned)(ab * BN);
                 for (int ks = ks0; ks < ks1; ks++) {
-                    if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.wait_limit_ns)) { ok = false; break; }
                     tc_fence_after();
                     const unsigned sa = smem_u32(smem + stage * C::STAGE_BYTES);
                     const unsigned long long adesc = make_smem_desc(sa);
@@ -725,7 +725,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int ab = it & 1;
             const unsigned acc_phase = (unsigned)(it >> 1) & 1;
             const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-            if (!mbar_wait<EPI_SLEEP_NS>(bar_acc_full + 8 * ab, acc_phase, abort_flag)) { ok = false; break; }
+            if (!mbar_wait<EPI_SLEEP_NS>(bar_acc_full + 8 * ab, acc_phase, abort_flag, p.wait_limit_ns)) { ok = false; break; }
             tc_fence_after();
             const int m = tm * (2 * BM) + (int)rank * BM + quarter * 32 + lane;
             const bool row_ok = m < p.M;
@@ -861,12 +861,14 @@ unsigned make_idesc(bool i8, bool a_signed, bool b_signed, int bn, int mma_m = B
 }
 
 int num_sms() {
-    static int n = 0;
+    static std::atomic<int> cache[64];   // SM count per device ordinal (0 = not asked yet)
+    int dev = 0;
+    cudaGetDevice(&dev);
+    int n = cache[dev & 63].load(std::memory_order_relaxed);
     if (!n) {
-        int dev = 0;
-        cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
         if (n <= 0) n = 148;
+        cache[dev & 63].store(n, std::memory_order_relaxed);
     }
     // the persistent GEMM grids take one CTA per SM; a caller that overlaps a collective with them leaves it a few SMs
     const int lim = sm_limit();
@@ -988,6 +990,8 @@ int launch_gemm_tc_allreduce(const void* W_data, int W_K_pad, int W_N_pad, const
     p.ep.mc_reduce = 0;
     p.vec_ok = 1;
     p.status = kernel_status_word();
+    if (!p.status) { set_error("gemm: no kernel status word on this device"); return B200FC_ERR_CUDA; }
+    p.wait_limit_ns = wait_limit_ns();
     p.splits = 1; p.split_stride = 0;
     p.ar_world = ar.world; p.ar_rank = ar.rank;
     {
@@ -1054,6 +1058,8 @@ int launch_gemm_tc(const void* W_data, int w_dtype, int W_K_pad, int W_N_pad, co
     p.acc_is_int = i8 ? 1 : 0;
     p.ep = ep;
     p.status = kernel_status_word();
+    if (!p.status) { set_error("gemm: no kernel status word on this device"); return B200FC_ERR_CUDA; }
+    p.wait_limit_ns = wait_limit_ns();
     p.splits = 1; p.split_stride = 0;
     p.ar_world = 0; p.ar_rank = 0; p.ar_phases = 3; p.ar_gemm_pairs = 0; p.ar_work_counter = 0; p.ar_target = 0; p.ar_partial_mc = nullptr; p.ar_out_mc = nullptr;
     for (int i = 0; i < 8; i++) p.ar_flags[i] = nullptr;

@@ -1,48 +1,79 @@
-// Decode-shaped fully-connected layer (M <= 16), weight stream fed by TMA into a shared-memory ring.
+// Decode-shaped fully-connected layer (M <= 16 rows of bf16 activations): an HBM-bound weight stream.
 //
-// Same contract and arithmetic as gemv.cu (the reference routines it replaces are listed there:
-// amx_kernel::Matmul M <= 16 branches, include/kernels_amx.hpp:1216-1253 and 1381-1441,
-// weight_compression/fc16m.cpp:451-502, fused-MLP decode tests/amx-mlp.cpp:648-737); what changes is how the bytes
-// reach the multipliers.  Registers can hold only ~8 KB of weights in flight per warp, which leaves an SM short of
-// the bytes in flight that 6.5 TB/s of HBM need.  Here one producer warp per CTA streams 16 KB stages (128 weight
-// rows x 128 bytes of K, one 2-D TMA box with 128-byte swizzle) into a ring of 4-5 stages; with two CTAs per SM
-// about 160 KB are in flight per SM and the stream never stops while the eight consumer warps stage activations,
-// widen int8 weights or reduce.  Consumers copy their share of a stage (32 rows x 64 bytes of K: activation
-// fragments are reused over two 16-row MMA blocks, which halves the shared-memory reads per weight) into registers
-// (conflict-free through the swizzle), release the stage, and run the same mma.sync path as gemv.cu.
+// Replaces the M <= 16 branches of amx_kernel::Matmul (include/kernels_amx.hpp:1216-1253), of the compressed-weight
+// specialisation Matmul<bf16,int8_t,float> (kernels_amx.hpp:1381-1441) and its stand-alone development version
+// matmul16m_Wint8B (weight_compression/fc16m.cpp:451-502), plus the M <= 16 case of the fused MLP
+// (tests/amx-mlp.cpp:707-737, 648-704).
+//
+// How the bytes move
+//   The packed weights are [N_pad, K_pad] with K contiguous.  The unit of the stream is a 16 KB stage: 128 weight rows
+//   x 128 bytes of K, one 2-D TMA box with 128-byte swizzle.  All stages of the call — row blocks outermost, K inside —
+//   form one sequence that is cut into equal contiguous pieces, one per CTA ("stream-K"), so every SM streams the
+//   same number of bytes whatever N and K are.  One producer warp per CTA keeps a ring of 4-5 stages in flight; eight
+//   consumer warps copy their share of a stage (32 rows x 64 bytes of K) into registers (conflict-free through the
+//   swizzle), release the stage and feed mma.sync.m16n8k16 with the weights as the 16-row operand and the <= 16
+//   activation rows as the 8-column operand (K permuted identically on both sides, which a dot product does not see).
+//   Compressed (int8) weights are stored offset-binary (v + 128): one byte permute builds the fp16 number
+//   1024 + v + 128, one subtraction leaves v — one instruction per weight, next to the consumer (the role of the
+//   reference's ping-pong dequantisation buffer).  fp16 because only its 11-bit significand holds all 8 bits; the
+//   activations are converted to fp16 per staged chunk after an exact power-of-two scaling per row.
+//   A piece that ends inside a row block leaves a partial sum: it goes to a slot of a small global scratch, the CTAs
+//   that share the row block count themselves on a counter, and the last one to arrive adds the slots in CTA order
+//   (deterministic) and runs the post-ops.  Nobody waits for anybody.
+//   The grid is at most one CTA per SM although two fit: with programmatic dependent launch the next kernel of the
+//   stream becomes resident beside this one and fills its own ring while this one still computes, so a chain of
+//   decode layers keeps HBM busy across kernel boundaries (weights never depend on the previous kernel; activations,
+//   the scratch and the output are touched only after griddepcontrol.wait).
 //   full[s]  : TMA complete_tx + one arrive.expect_tx by the producer        empty[s] : one arrive per consumer warp
-// All mbarrier waits are bounded; on a time-out the CTA raises an abort flag, every role leaves its loop, the kernel
-// stores an error code and still takes part in the cluster barriers.
-#include <cooperative_groups.h>
+// All mbarrier waits are bounded; on a time-out the CTA raises an abort flag, every role stops waiting, the kernel
+// stores an error code and still publishes (meaningless) partial sums so that the counters return to zero.
 #include <cuda.h>
 #include <cuda_fp16.h>
+#include <cstdlib>
 #include "common.cuh"
-
-namespace cg = cooperative_groups;
 
 namespace b200fc {
 
 namespace {
 
 constexpr int CWARPS = 8;                       // consumer warps
+constexpr int CTHREADS = CWARPS * 32;
 constexpr int ROWS_PER_WARP = 32;               // a warp owns 32 rows x one 64-byte half of every stage
 constexpr int ROWS_PER_CTA = (CWARPS / 2) * ROWS_PER_WARP;  // 128
 constexpr int STAGE_K_BYTES = 128;              // bytes of K per row and stage (one swizzle atom)
 constexpr int STAGE_BYTES = ROWS_PER_CTA * STAGE_K_BYTES;  // 16 KB
 constexpr int CHUNK_K = 1024;                   // activation elements staged per chunk
 constexpr int THREADS = (CWARPS + 1) * 32;
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+constexpr int SLOT_FLOATS = 16 * ROWS_PER_CTA;  // one partial-sum slot: [16 activation rows][128 weight rows] fp32
 
 struct Params {
-    int n_stages_total;   // stages in a packed row (K_pad bytes / 128)
+    int spr;              // stages per packed row (K_pad bytes / 128)
+    long long total;      // stages of the whole call: row blocks x spr
+    int S;                // > 0: every row block is cut into S pieces, CTA c takes piece c % S of row block c / S;
+                          // 0: the whole stage sequence is cut into gridDim.x equal pieces ("stream-K")
     const unsigned char* X;
     long long ldx;
     int M, K;
     int n0, n1;
-    int splits;
     Epilogue ep;
     int* status;
+    float* slots;         // [gridDim.x][2][SLOT_FLOATS]: partial sums of the first / last piece of each CTA
+    unsigned* counters;   // [gridDim.x], zero between launches
+    unsigned long long wait_limit_ns;
+    int cluster;          // 1: launched as clusters of S CTAs (S <= 8); the pieces of a row block meet in distributed
+                          // shared memory instead of the global scratch
+    int pf_cap;           // stages beyond the ring that the producer prefetches into L2 when the CTA starts
+#ifdef B200FC_TRACE
+    unsigned long long* trace;   // [launch % 64][gridDim.x <= 320][8] globaltimer stamps (timeline studies only)
+    int trace_launch;
+#endif
 };
+
+#ifdef B200FC_TRACE
+#define TRACE_STAMP(i) do { if (p.trace && (threadIdx.x & 31) == 0) p.trace[((size_t)(p.trace_launch & 63) * 320 + blockIdx.x) * 8 + (i)] = globaltimer(); } while (0)
+#else
+#define TRACE_STAMP(i) do { } while (0)
+#endif
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ unsigned long long globaltimer() {
@@ -70,13 +101,13 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
         : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, unsigned long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = globaltimer();
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (globaltimer() - t0 > WAIT_LIMIT_NS) {
+        if (globaltimer() - t0 > limit) {
             *abort_flag = 1;
             return false;
         }
@@ -88,7 +119,22 @@ __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
         : "memory");
 }
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CWARPS * 32) : "memory"); }
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// fp32 at shared-memory address `addr` (of this CTA's window) in CTA `rank` of the cluster
+__device__ __forceinline__ float ld_peer_f32(unsigned addr, unsigned rank) {
+    unsigned ra;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
+    return v;
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CTHREADS) : "memory"); }
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
                                          unsigned b1) {
@@ -106,7 +152,8 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], unsigned a0, unsigned a1,
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-// two offset-binary weights (bytes `sel` of w) -> f16x2 holding their values exactly (see gemv.cu)
+// two offset-binary weights (bytes `sel` of w) -> f16x2 holding their values exactly:
+// 0x64xx is the fp16 number 1024 + xx, and 1024 + (v + 128) - 1152 = v
 __device__ __forceinline__ unsigned u8x2_to_f16x2(unsigned w, unsigned sel) {
     unsigned p = __byte_perm(w, 0x64646464u, sel);
     const __half2 off = __floats2half2_rn(1152.0f, 1152.0f);
@@ -123,9 +170,34 @@ template <bool W8, int NT> struct Layout {
     static constexpr int RING = STAGES * STAGE_BYTES;
     static constexpr int X_OFF = RING;
     static constexpr int AUX_OFF = X_OFF + MP * XROW;          // smax [MP][CWARPS], sexp [MP]
-    static constexpr int BAR_OFF = AUX_OFF + MP * (CWARPS + 1) * 4;
-    static constexpr int SMEM = BAR_OFF + 2 * STAGES * 8 + 16 + 1024;  // + barriers, abort flag, alignment slack
+    static constexpr int EP_OFF = AUX_OFF + MP * (CWARPS + 1) * 4;   // dequant scale, bias, quant scale of 128 rows
+    static constexpr int BAR_OFF = EP_OFF + 3 * ROWS_PER_CTA * 4;
+    static constexpr int SMEM = BAR_OFF + 2 * STAGES * 8 + 16 + 1024;  // + barriers, abort flag, last flag, alignment slack
 };
+
+// first stage of CTA c's piece, and the CTA whose piece holds stage s
+__device__ __forceinline__ long long piece_begin(const Params& p, int G, int c) {
+    if (p.S > 0) return (long long)(c / p.S) * p.spr + (long long)p.spr * (c % p.S) / p.S;
+    return p.total * c / G;      // pieces are [c * total / G, (c + 1) * total / G)
+}
+__device__ __forceinline__ int piece_of(const Params& p, int G, long long s) {
+    if (p.S > 0) {
+        const int rb = (int)(s / p.spr), ks = (int)(s - (long long)rb * p.spr);
+        return rb * p.S + (int)((((long long)ks + 1) * p.S - 1) / p.spr);
+    }
+    return (int)(((s + 1) * G - 1) / p.total);
+}
+
+// DEQUANT -> BIAS -> GELU -> QUANT on one value of weight row `row` of the current row block; s_ep holds the three
+// per-row vectors (dequant scale, bias, quant scale), loaded next to the activations so that the epilogue does not
+// wait for global memory again
+__device__ __forceinline__ float postop_staged(float v, int row, int steps, const float* s_ep) {
+    if (steps & B200FC_STEP_DEQUANT) v *= s_ep[row];
+    if (steps & B200FC_STEP_BIAS) v += s_ep[ROWS_PER_CTA + row];
+    if (steps & B200FC_STEP_GELU) v = gelu_erf_poly(v);
+    if (steps & B200FC_STEP_QUANT) v *= s_ep[2 * ROWS_PER_CTA + row];
+    return v;
+}
 
 template <bool W8, int NT>
 __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
@@ -143,17 +215,17 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
     const unsigned bar_full = smem_u32(smem + L::BAR_OFF);
     const unsigned bar_empty = bar_full + STAGES * 8;
     volatile int* abort_flag = (volatile int*)(smem + L::BAR_OFF + 2 * STAGES * 8);
+    volatile int* last_flag = abort_flag + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    cg::cluster_group cluster = cg::this_cluster();
-    const int S = p.splits;
-    const int rank = S > 1 ? (int)cluster.block_rank() : 0;
-    const int it_begin = (int)((long long)p.n_stages_total * rank / S);
-    const int it_end = (int)((long long)p.n_stages_total * (rank + 1) / S);
-    const int cta_row0 = p.n0 + blockIdx.x * ROWS_PER_CTA;
+    const int G = (int)gridDim.x, cta = (int)blockIdx.x;
+    const long long it_begin = piece_begin(p, G, cta), it_end = piece_begin(p, G, cta + 1);
+    const unsigned long long limit = p.wait_limit_ns;
 
     if (threadIdx.x == 0) {
+        TRACE_STAMP(0);   // CTA started
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
         for (int i = 0; i < STAGES; i++) {
             mbar_init(bar_full + 8 * i, 1);
             mbar_init(bar_empty + 8 * i, CWARPS);
@@ -162,38 +234,52 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    // the next kernel in the stream may start its own weight stream now
+    // the next kernel in the stream may become resident and start its own weight stream now
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-
-    constexpr int RB = ROWS_PER_WARP / 16;  // 16-row MMA blocks per warp
-    float acc[RB][NT][4];
-#pragma unroll
-    for (int rb = 0; rb < RB; rb++)
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) acc[rb][nt][i] = 0.0f;
 
     if (warp == CWARPS) {
         // ---------------- producer: weights never depend on the previous kernel, stream at once ----------------
         if (lane == 0) {
             int stage = 0;
             unsigned phase = 0;
-            for (int it = it_begin; it < it_end; it++) {
-                if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag)) break;
+            int rb = (int)(it_begin / p.spr), ks = (int)(it_begin - (long long)rb * p.spr);
+            for (long long it = it_begin; it < it_end; it++) {
+                if (it == it_begin + STAGES && p.pf_cap > 0) {
+                    // The ring is full and this CTA may have to wait for the previous kernel of the stream: ask L2
+                    // for the next stages meanwhile, so that their DRAM round trip is not paid later, one ring slot
+                    // at a time, on the path between two dependent kernels.
+                    long long pf_to = it + p.pf_cap < it_end ? it + p.pf_cap : it_end;
+                    int pf_rb = rb, pf_ks = ks;
+                    for (long long pf = it; pf < pf_to; pf++) {
+                        tma_prefetch_l2_2d(&map_w, pf_ks * STAGE_K_BYTES, p.n0 + pf_rb * ROWS_PER_CTA);
+                        if (++pf_ks == p.spr) { pf_ks = 0; pf_rb++; }
+                    }
+                }
+                if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, limit)) break;
                 mbar_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
-                tma_load_2d(smem_u32(smem + stage * STAGE_BYTES), &map_w, bar_full + 8 * stage, it * STAGE_K_BYTES, cta_row0);
+                tma_load_2d(smem_u32(smem + stage * STAGE_BYTES), &map_w, bar_full + 8 * stage, ks * STAGE_K_BYTES,
+                            p.n0 + rb * ROWS_PER_CTA);
+                if (++ks == p.spr) { ks = 0; rb++; }
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
         }
     } else {
         // ---------------- consumers ----------------
-        asm volatile("griddepcontrol.wait;" ::: "memory");  // activations may come from the previous kernel
-        const int ctid = threadIdx.x;                        // 0 .. 127
+        // activations, the scratch and the output may belong to the previous kernel of the stream until here
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (threadIdx.x == 0) TRACE_STAMP(1);   // previous kernel complete
+        const int ctid = threadIdx.x;                        // 0 .. 255
         const bool x_vec = (((uintptr_t)p.X & 15) == 0) && ((p.ldx & 15) == 0);
-        const int k_begin = it_begin * KE, k_end = it_end * KE;
+        const bool x_fast = x_vec && (p.K & 7) == 0;
         auto load_x_unit = [&](int row, int k) -> uint4 {
             uint4 v = make_uint4(0, 0, 0, 0);
+            if (x_fast) {
+                // no branch around the load, so that the loads of all passes are in flight together: out-of-range
+                // units read element (0, 0) and are zeroed afterwards
+                const bool in = row < p.M && k < p.K;
+                const uint4 r = *(const uint4*)(p.X + (long long)(in ? row : 0) * p.ldx + (long long)(in ? k : 0) * 2);
+                return in ? r : v;
+            }
             if (row < p.M && k < p.K) {
                 const unsigned char* src = p.X + (long long)row * p.ldx + (long long)k * 2;
                 if (x_vec && k + 8 <= p.K) {
@@ -208,23 +294,29 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
             }
             return v;
         };
-        // Stages CHUNK_K activation elements of all MP rows: 128 sixteen-byte units per row, the 256 consumer
-        // threads take two rows per pass.  All loads of a thread are issued before the first is converted / stored.
+        constexpr int RB = ROWS_PER_WARP / 16;  // 16-row MMA blocks per warp
+        // AS > 1 would give every MMA of a 16-byte weight load its own accumulator set (shorter dependent chains);
+        // measured slower (the extra registers spill), so one set is used.
+        constexpr int AS = 1;
+        float acc[AS][RB][NT][4];
+        // Compressed weights multiply fp16 x fp16, so every staged chunk is scaled per activation row by the power of two
+        // that puts the row's largest magnitude (within the chunk) at 2^13 and converted to fp16: exact, since fp16 keeps
+        // the 8-bit significand of bf16.  The accumulators carry the row's current scale (cur_e) and are rescaled when a
+        // new chunk brings a different one; the scale is undone after the last stage of a piece.
+        int cur_e[NT][2];
+
+        // Stages CHUNK_K activation elements of all MP rows, starting at stage ks of a row: 128 sixteen-byte units per
+        // row, the 256 consumer threads take two rows per pass.  All loads of a thread are issued before the first is
+        // converted / stored.
         constexpr int UNITS = CHUNK_K / 8;                    // 128
-        constexpr int ROWS_PER_PASS = CWARPS * 32 / UNITS;    // 2
+        constexpr int ROWS_PER_PASS = CTHREADS / UNITS;       // 2
         constexpr int PASSES = MP / ROWS_PER_PASS;
         const int unit = ctid % UNITS, row0 = ctid / UNITS;
-        // Compressed weights multiply fp16 x fp16, so every staged chunk is scaled per activation row by the power
-        // of two that puts the row's largest magnitude (within the chunk) at 2^13 and converted to fp16: exact, since
-        // fp16 keeps the 8-bit significand of bf16.  The accumulators carry the row's current scale (cur_e) and are
-        // rescaled when a new chunk brings a different one; the scale is undone after the last stage.
-        int cur_e[NT][2];
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++) cur_e[nt][0] = cur_e[nt][1] = 0;
-        auto stage_x = [&](int it) {
-            const int k = it * KE + unit * 8;
-            const bool need = k < k_end;
+        auto stage_x = [&](int ks, int ks_end) {
+            const int k = ks * KE + unit * 8;
+            const bool need = k < ks_end * KE;
             consumer_sync();  // everyone is done with the previous chunk
+            if (threadIdx.x == 0 && ks * KE < CHUNK_K) TRACE_STAMP(6);   // staging of a first chunk begins
             uint4 v[PASSES];
 #pragma unroll
             for (int i = 0; i < PASSES; i++) v[i] = need ? load_x_unit(row0 + i * ROWS_PER_PASS, k) : make_uint4(0, 0, 0, 0);
@@ -276,12 +368,14 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
                     const int e0 = sexp[nt * 8 + 2 * t], e1 = sexp[nt * 8 + 2 * t + 1];
                     if (cur_e[nt][0] != e0 || cur_e[nt][1] != e1) {
 #pragma unroll
-                        for (int rb = 0; rb < RB; rb++) {
-                            acc[rb][nt][0] = scalbnf(acc[rb][nt][0], cur_e[nt][0] - e0);
-                            acc[rb][nt][2] = scalbnf(acc[rb][nt][2], cur_e[nt][0] - e0);
-                            acc[rb][nt][1] = scalbnf(acc[rb][nt][1], cur_e[nt][1] - e1);
-                            acc[rb][nt][3] = scalbnf(acc[rb][nt][3], cur_e[nt][1] - e1);
-                        }
+                        for (int as = 0; as < AS; as++)
+#pragma unroll
+                            for (int rb = 0; rb < RB; rb++) {
+                                acc[as][rb][nt][0] = scalbnf(acc[as][rb][nt][0], cur_e[nt][0] - e0);
+                                acc[as][rb][nt][2] = scalbnf(acc[as][rb][nt][2], cur_e[nt][0] - e0);
+                                acc[as][rb][nt][1] = scalbnf(acc[as][rb][nt][1], cur_e[nt][1] - e1);
+                                acc[as][rb][nt][3] = scalbnf(acc[as][rb][nt][3], cur_e[nt][1] - e1);
+                            }
                         cur_e[nt][0] = e0; cur_e[nt][1] = e1;
                     }
                 }
@@ -294,23 +388,65 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
         // logical chunk 2t + j, physical chunk = logical ^ (row & 7) = logical ^ g
         const int rg = warp >> 1, kh = warp & 1;       // row group (32 rows) and K half (64 bytes) of this warp
         const int row_base = rg * ROWS_PER_WARP + g;
+        float* part = (float*)xbuf;                    // partial tiles of a finished piece: part[K half][token][row]
+        constexpr int PART_HALF = MP * ROWS_PER_CTA;   // floats per K half
+        const Epilogue& ep = p.ep;
+        const bool silu = (ep.steps & B200FC_STEP_SILU_MUL) != 0;
+        float* s_ep = (float*)(smem + L::EP_OFF);
         bool ok = true;
-        for (int it = it_begin; it < it_end && ok; it++) {
-            const int it_in_chunk = (it - it_begin) % STAGES_PER_CHUNK;
-            if (it_in_chunk == 0) stage_x(it);
-            if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) { ok = false; break; }
-            uint4 w[RB][2];
-            const unsigned char* sbase = smem + stage * STAGE_BYTES;
-#pragma unroll
-            for (int rb = 0; rb < RB; rb++)
-#pragma unroll
-                for (int h = 0; h < 2; h++)
-                    w[rb][h] = *(const uint4*)(sbase + (row_base + rb * 16 + h * 8) * STAGE_K_BYTES + (((2 * t + kh) ^ g) << 4));
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_empty + 8 * stage);
-            if (++stage == STAGES) { stage = 0; phase ^= 1; }
 
-            {
+        long long it = it_begin;
+        while (it < it_end) {
+            // ---- one piece: stages [ks0, ks1) of row block rbk ----
+            const int rbk = (int)(it / p.spr);
+            const int ks0 = (int)(it - (long long)rbk * p.spr);
+            const int ks1 = (long long)(p.spr - ks0) < it_end - it ? p.spr : ks0 + (int)(it_end - it);
+            const bool first_piece = it == it_begin;
+#pragma unroll
+            for (int as = 0; as < AS; as++)
+#pragma unroll
+                for (int rb = 0; rb < RB; rb++)
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                        for (int i = 0; i < 4; i++) acc[as][rb][nt][i] = 0.0f;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) cur_e[nt][0] = cur_e[nt][1] = 0;
+
+            // post-op vectors of this row block (one row per thread of the first four warps); the loads travel together
+            // with those of the first activation chunk
+            float ep_deq = 1.0f, ep_bias = 0.0f, ep_q = 1.0f;
+            if (ctid < ROWS_PER_CTA) {
+                const int n = p.n0 + rbk * ROWS_PER_CTA + ctid;
+                if (n < p.n1) {
+                    if (ep.steps & B200FC_STEP_DEQUANT) ep_deq = ep.deq_per_oc ? ep.deq_scale * ep.deq_per_oc[n] : ep.deq_scale;
+                    if (ep.steps & B200FC_STEP_BIAS) ep_bias = ep.bias[n];
+                    if (ep.steps & B200FC_STEP_QUANT) ep_q = ep.q_per_oc ? ep.q_per_oc[n] : ep.q_scale;
+                }
+            }
+            for (int ks = ks0; ks < ks1; ks++) {
+                const int it_in_chunk = (ks - ks0) % STAGES_PER_CHUNK;
+                if (it_in_chunk == 0) stage_x(ks, ks1);
+                if (ks == ks0 && ctid < ROWS_PER_CTA) {
+                    // (the first barrier of stage_x has been passed: nobody still reads the previous piece's vectors)
+                    s_ep[ctid] = ep_deq; s_ep[ROWS_PER_CTA + ctid] = ep_bias; s_ep[2 * ROWS_PER_CTA + ctid] = ep_q;
+                }
+                if (threadIdx.x == 0 && ks == ks0 && first_piece) TRACE_STAMP(2);   // first activation chunk staged
+                // warp-uniform outcome: either every lane goes on to the MMAs or none does
+                ok = __all_sync(0xffffffffu, ok && mbar_wait(bar_full + 8 * stage, phase, abort_flag, limit));
+                if (threadIdx.x == 0 && ks == ks0 && first_piece) TRACE_STAMP(7);   // first stage of weights is there
+                if (!ok) continue;
+                uint4 w[RB][2];
+                const unsigned char* sbase = smem + stage * STAGE_BYTES;
+#pragma unroll
+                for (int rb = 0; rb < RB; rb++)
+#pragma unroll
+                    for (int h = 0; h < 2; h++)
+                        w[rb][h] = *(const uint4*)(sbase + (row_base + rb * 16 + h * 8) * STAGE_K_BYTES + (((2 * t + kh) ^ g) << 4));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_empty + 8 * stage);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+
                 const int j = kh;
                 // activations matching this thread's weight bytes: K elements [(2t + j) * (W8 ? 16 : 8), ...) of the stage
                 const int xoff = W8 ? it_in_chunk * KE * 2 + (8 * j + t) * 16 : (it_in_chunk * KE + (2 * t + j) * 8) * 2;
@@ -341,78 +477,171 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
                         }
 #pragma unroll
                         for (int nt = 0; nt < NT; nt++) {
-                            if constexpr (W8) mma_f16(acc[rb][nt], a0, a1, a2, a3, xb[nt][2 * q], xb[nt][2 * q + 1]);
-                            else mma_bf16(acc[rb][nt], a0, a1, a2, a3, xb[nt][2 * q], xb[nt][2 * q + 1]);
+                            if constexpr (W8) mma_f16(acc[q % AS][rb][nt], a0, a1, a2, a3, xb[nt][2 * q], xb[nt][2 * q + 1]);
+                            else mma_bf16(acc[q % AS][rb][nt], a0, a1, a2, a3, xb[nt][2 * q], xb[nt][2 * q + 1]);
                         }
                     }
                 }
             }
-        }
-        if constexpr (W8) {
+            it += ks1 - ks0;
+            if (threadIdx.x == 0 && it == it_end) TRACE_STAMP(3);   // last stage multiplied
+            // the accumulator sets are added in a fixed order
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++)
+            for (int as = 1; as < AS; as++)
 #pragma unroll
-                for (int rb = 0; rb < RB; rb++) {
-                    acc[rb][nt][0] = scalbnf(acc[rb][nt][0], cur_e[nt][0]);
-                    acc[rb][nt][2] = scalbnf(acc[rb][nt][2], cur_e[nt][0]);
-                    acc[rb][nt][1] = scalbnf(acc[rb][nt][1], cur_e[nt][1]);
-                    acc[rb][nt][3] = scalbnf(acc[rb][nt][3], cur_e[nt][1]);
+                for (int rb = 0; rb < RB; rb++)
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                        for (int i = 0; i < 4; i++) acc[0][rb][nt][i] += acc[as][rb][nt][i];
+            if constexpr (W8) {
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                    for (int rb = 0; rb < RB; rb++) {
+                        acc[0][rb][nt][0] = scalbnf(acc[0][rb][nt][0], cur_e[nt][0]);
+                        acc[0][rb][nt][2] = scalbnf(acc[0][rb][nt][2], cur_e[nt][0]);
+                        acc[0][rb][nt][1] = scalbnf(acc[0][rb][nt][1], cur_e[nt][1]);
+                        acc[0][rb][nt][3] = scalbnf(acc[0][rb][nt][3], cur_e[nt][1]);
+                    }
+            }
+
+            // ---- the piece's partial tile -> shared memory (over the activation buffer) ----
+            consumer_sync();
+#pragma unroll
+            for (int rb = 0; rb < RB; rb++)
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const int row = rg * ROWS_PER_WARP + rb * 16 + g, tok = nt * 8 + 2 * t;
+                    float* pp = part + kh * PART_HALF;
+                    pp[tok * ROWS_PER_CTA + row] = acc[0][rb][nt][0];
+                    pp[(tok + 1) * ROWS_PER_CTA + row] = acc[0][rb][nt][1];
+                    pp[tok * ROWS_PER_CTA + row + 8] = acc[0][rb][nt][2];
+                    pp[(tok + 1) * ROWS_PER_CTA + row + 8] = acc[0][rb][nt][3];
                 }
+            consumer_sync();
+
+            // ---- who finishes the row block?  a piece that covers it alone does; otherwise the last CTA to arrive ----
+            const bool whole = ks0 == 0 && ks1 == p.spr;
+            int c_first = cta, c_last = cta;
+            bool finish = true;
+            if (p.cluster) {
+                // the two K halves are added here; the cluster's CTAs then share the rest of the work (end of kernel)
+                for (int e = ctid; e < p.M * ROWS_PER_CTA; e += CTHREADS) part[e] += part[PART_HALF + e];
+                finish = false;
+            } else if (!whole) {
+                const int nvec = p.M * ROWS_PER_CTA / 4;
+                float4* slot = (float4*)(p.slots + (size_t)(2 * cta + (first_piece ? 0 : 1)) * SLOT_FLOATS);
+                for (int v = ctid; v < nvec; v += CTHREADS) {
+                    const float4 a = ((const float4*)part)[v], b = ((const float4*)(part + PART_HALF))[v];
+                    slot[v] = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+                }
+                consumer_sync();
+                const long long s_first = (long long)rbk * p.spr;
+                c_first = piece_of(p, G, s_first);
+                c_last = piece_of(p, G, s_first + p.spr - 1);
+                if (ctid == 0) {
+                    // release: the slot stores of all consumer threads (ordered before this by the barrier) are visible to
+                    // whoever reads the counter; acquire: so are the slots of the CTAs that counted themselves earlier
+                    unsigned old;
+                    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(p.counters + c_first) : "memory");
+                    const bool last = old == (unsigned)(c_last - c_first);
+                    if (last) p.counters[c_first] = 0;   // the counter is ready for the next launch
+                    *last_flag = last ? 1 : 0;
+                }
+                consumer_sync();
+                if (threadIdx.x == 0 && it == it_end) TRACE_STAMP(4);   // counted
+                finish = *last_flag != 0;
+                if (finish) {
+                    // Sum the slots of the CTAs that share the row block, in CTA order, into part[token][row].  Only the
+                    // first of them can hold the row block as the piece that CLOSES its range (slot 1); for all others it
+                    // opens their range (slot 0).  Eight slots are read at a time so that the L2 round trips overlap.
+                    const int which_first = piece_begin(p, G, c_first) < s_first ? 1 : 0;
+                    const float4* base = (const float4*)p.slots;
+                    for (int v = ctid; v < nvec; v += CTHREADS) {
+                        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        for (int c = c_first; c <= c_last; c += 8) {
+                            float4 t4[8];
+#pragma unroll
+                            for (int u = 0; u < 8; u++) {
+                                const int cc = c + u;
+                                const int which = cc == c_first ? which_first : 0;
+                                t4[u] = cc <= c_last ? __ldcg(base + (size_t)(2 * cc + which) * (SLOT_FLOATS / 4) + v)
+                                                     : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                            }
+#pragma unroll
+                            for (int u = 0; u < 8; u++) {
+                                sum.x += t4[u].x; sum.y += t4[u].y; sum.z += t4[u].z; sum.w += t4[u].w;
+                            }
+                        }
+                        ((float4*)part)[v] = sum;
+                    }
+                    consumer_sync();
+                }
+            }
+            if (finish) {
+                // value of element [token][row] of the row block
+                auto reduced = [&](int idx) -> float { return whole ? part[idx] + part[PART_HALF + idx] : part[idx]; };
+                const int blk_row0 = p.n0 + rbk * ROWS_PER_CTA;
+                const int out_rows = silu ? ROWS_PER_CTA / 2 : ROWS_PER_CTA;
+                const int n_out = out_rows * p.M;
+                for (int e = ctid; e < n_out; e += CTHREADS) {
+                    const int tok = e / out_rows, orow = e % out_rows;
+                    if (silu) {
+                        const int grow = 32 * (orow >> 4) + (orow & 15);
+                        if (blk_row0 + grow + 16 < p.n1) {
+                            const float gsum = reduced(tok * ROWS_PER_CTA + grow), usum = reduced(tok * ROWS_PER_CTA + grow + 16);
+                            unsigned short* crow = (unsigned short*)((char*)ep.C + (long long)tok * ep.ldc);
+                            crow[(blk_row0 >> 1) + orow] = f32_to_bf16_bits(silu_f(gsum) * usum);
+                        }
+                    } else {
+                        const int n = blk_row0 + orow;
+                        if (n < p.n1) store_scalar(postop_staged(reduced(tok * ROWS_PER_CTA + orow), orow, ep.steps, s_ep), tok, n, ep);
+                    }
+                }
+            }
         }
+        if (ctid == 0) TRACE_STAMP(5);   // done
     }
 
-    // ---- partial tiles -> shared memory (over the activation buffer): part[K half][token][row] ----
-    __syncthreads();
-    float* part = (float*)xbuf;
-    constexpr int PART_HALF = MP * ROWS_PER_CTA;  // floats per K half
-    if (warp < CWARPS) {
-        const int rg = warp >> 1, kh = warp & 1;
-#pragma unroll
-        for (int rb = 0; rb < RB; rb++)
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++) {
-                const int row = rg * ROWS_PER_WARP + rb * 16 + g, tok = nt * 8 + 2 * t;
-                float* pp = part + kh * PART_HALF;
-                pp[tok * ROWS_PER_CTA + row] = acc[rb][nt][0];
-                pp[(tok + 1) * ROWS_PER_CTA + row] = acc[rb][nt][1];
-                pp[tok * ROWS_PER_CTA + row + 8] = acc[rb][nt][2];
-                pp[(tok + 1) * ROWS_PER_CTA + row + 8] = acc[rb][nt][3];
+    if (p.cluster) {
+        // ---- the S pieces of this row block meet: every CTA of the cluster finishes 1/S of the outputs, adding the
+        // partial tiles of all S CTAs in rank order (deterministic) ----
+        __syncwarp();
+        cluster_sync_all();
+        if (threadIdx.x == 0) TRACE_STAMP(4);   // all pieces of the row block are there
+        const int S = p.S, rank = cta % S, blk_row0 = p.n0 + (cta / S) * ROWS_PER_CTA;
+        const unsigned part_addr = smem_u32(xbuf);
+        const Epilogue& ep = p.ep;
+        const bool silu = (ep.steps & B200FC_STEP_SILU_MUL) != 0;
+        const int out_rows = silu ? ROWS_PER_CTA / 2 : ROWS_PER_CTA;
+        const int n_out = out_rows * p.M;
+        const int e_begin = (int)((long long)n_out * rank / S), e_end = (int)((long long)n_out * (rank + 1) / S);
+        const float* s_ep = (const float*)(smem + L::EP_OFF);
+        for (int e = e_begin + (int)threadIdx.x; e < e_end; e += THREADS) {
+            const int tok = e / out_rows, orow = e % out_rows;
+            if (silu) {
+                const int grow = 32 * (orow >> 4) + (orow & 15);
+                float gsum = 0.0f, usum = 0.0f;
+                for (int q = 0; q < S; q++) {
+                    gsum += ld_peer_f32(part_addr + 4u * (unsigned)(tok * ROWS_PER_CTA + grow), (unsigned)q);
+                    usum += ld_peer_f32(part_addr + 4u * (unsigned)(tok * ROWS_PER_CTA + grow + 16), (unsigned)q);
+                }
+                if (blk_row0 + grow + 16 < p.n1) {
+                    unsigned short* crow = (unsigned short*)((char*)ep.C + (long long)tok * ep.ldc);
+                    crow[(blk_row0 >> 1) + orow] = f32_to_bf16_bits(silu_f(gsum) * usum);
+                }
+            } else {
+                float sum = 0.0f;
+                for (int q = 0; q < S; q++) sum += ld_peer_f32(part_addr + 4u * (unsigned)(tok * ROWS_PER_CTA + orow), (unsigned)q);
+                const int n = blk_row0 + orow;
+                if (n < p.n1) store_scalar(postop_staged(sum, orow, ep.steps, s_ep), tok, n, ep);
             }
+        }
+        if (threadIdx.x == 0) TRACE_STAMP(5);
+        cluster_sync_all();  // nobody leaves while a peer may still read its partial tile
     }
     if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, 3);
-    if (S > 1) cluster.sync(); else __syncthreads();
-
-    // ---- reduce over splits in rank order, post-ops, store; the cluster's CTAs share the output elements ----
-    const Epilogue& ep = p.ep;
-    const bool silu = (ep.steps & B200FC_STEP_SILU_MUL) != 0;
-    const int out_rows = silu ? ROWS_PER_CTA / 2 : ROWS_PER_CTA;
-    const int total = out_rows * p.M;
-    const int e_begin = (int)((long long)total * rank / S), e_end = (int)((long long)total * (rank + 1) / S);
-    for (int e = e_begin + threadIdx.x; e < e_end; e += blockDim.x) {
-        const int tok = e / out_rows, orow = e % out_rows;
-        if (silu) {
-            const int grow = 32 * (orow >> 4) + (orow & 15);
-            float gsum = 0.0f, usum = 0.0f;
-            for (int q = 0; q < S; q++) {
-                const float* rp = S > 1 ? cluster.map_shared_rank(part, q) : part;
-                gsum += rp[tok * ROWS_PER_CTA + grow] + rp[PART_HALF + tok * ROWS_PER_CTA + grow];
-                usum += rp[tok * ROWS_PER_CTA + grow + 16] + rp[PART_HALF + tok * ROWS_PER_CTA + grow + 16];
-            }
-            if (cta_row0 + grow + 16 < p.n1) {
-                unsigned short* crow = (unsigned short*)((char*)ep.C + (long long)tok * ep.ldc);
-                crow[(cta_row0 >> 1) + orow] = f32_to_bf16_bits(silu_f(gsum) * usum);
-            }
-        } else {
-            float sum = 0.0f;
-            for (int q = 0; q < S; q++) {
-                const float* rp = S > 1 ? cluster.map_shared_rank(part, q) : part;
-                sum += rp[tok * ROWS_PER_CTA + orow] + rp[PART_HALF + tok * ROWS_PER_CTA + orow];
-            }
-            const int n = cta_row0 + orow;
-            if (n < p.n1) store_scalar(postop_scalar(sum, n, ep), tok, n, ep);
-        }
-    }
-    if (S > 1) cluster.sync();  // nobody leaves while a peer may still read its partial tile
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -431,8 +660,16 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
+int device_sms() {
+    int dev = 0, n = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n > 0 ? n : 148;
+}
+
 template <bool W8, int NT>
-int launch_variant(const CUtensorMap& map, const Params& p, int row_ctas, cudaStream_t s) {
+int launch_variant(const CUtensorMap& map, const Params& p, int grid, cudaStream_t s) {
+    const int cluster = p.cluster ? p.S : 1;
     using L = Layout<W8, NT>;
     static_assert(L::MP * L::XROW >= 2 * ROWS_PER_CTA * L::MP * 4, "partial tiles must fit the activation buffer");
     static std::atomic<unsigned long long> attr_devices{0};
@@ -444,17 +681,17 @@ int launch_variant(const CUtensorMap& map, const Params& p, int row_ctas, cudaSt
         if (arc) return arc;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(row_ctas, p.splits, 1);
+    cfg.gridDim = dim3(grid, 1, 1);
     cfg.blockDim = dim3(THREADS, 1, 1);
     cfg.dynamicSmemBytes = L::SMEM;
     cfg.stream = s;
     cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = p.splits;
-    attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = cluster;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
     B200FC_CUDA(cudaLaunchKernelEx(&cfg, gemv_tma_kernel<W8, NT>, map, p));
@@ -464,8 +701,15 @@ int launch_variant(const CUtensorMap& map, const Params& p, int row_ctas, cudaSt
 
 }  // namespace
 
+#ifdef B200FC_TRACE
+static unsigned long long* g_trace_ptr = nullptr;
+extern "C" void* b200fc_debug_trace_ptr(void) { return g_trace_ptr; }
+#endif
+
+size_t gemv_scratch_bytes() { return (size_t)kGemvMaxCtas * (2 * SLOT_FLOATS * sizeof(float) + sizeof(unsigned)); }
+
 int launch_gemv_tma(const Weight& w, const void* A, int M, int K, int64_t lda, int n0, int n1, const Epilogue& ep,
-                    cudaStream_t s) {
+                    cudaStream_t s, void* scratch) {
     if (M < 1 || M > 16) { set_error("gemv: M must be in [1, 16]"); return B200FC_ERR_INVALID; }
     if (w.dtype == B200FC_U8) { set_error("gemv: unsigned 8-bit weights are not supported with bf16 activations"); return B200FC_ERR_UNSUPPORTED; }
     if (n1 <= n0) return B200FC_OK;
@@ -483,30 +727,72 @@ int launch_gemv_tma(const Weight& w, const void* A, int M, int K, int64_t lda, i
     if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed (%d)", (int)r); return B200FC_ERR_CUDA; }
 
     Params p;
-    p.n_stages_total = (int)(w.ld_bytes() / STAGE_K_BYTES);
+    p.spr = (int)(w.ld_bytes() / STAGE_K_BYTES);
+    const int row_blocks = (n1 - n0 + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
+    p.total = (long long)row_blocks * p.spr;
     p.X = (const unsigned char*)A;
     p.ldx = lda;
     p.M = M; p.K = K;
     p.n0 = n0; p.n1 = n1;
     p.ep = ep;
     p.status = kernel_status_word();
-    const int row_ctas = (n1 - n0 + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
-    // split K over a cluster (<= 8, the portable limit) while the grid still fits the GPU in one wave of two CTAs per
-    // SM and every split keeps at least two stages
-    int S = 1;
-    while (S < 8 && row_ctas * S * 2 <= 148 * 2 && p.n_stages_total >= 4 * S) S *= 2;
-    {
-        static int forced = -1;  // B200FC_GEMV_SPLITS=1|2|4|8 (for experiments)
-        if (forced < 0) {
-            const char* e = getenv("B200FC_GEMV_SPLITS");
-            forced = e ? atoi(e) : 0;
-        }
-        if ((forced == 1 || forced == 2 || forced == 4 || forced == 8) && p.n_stages_total >= 2 * forced) S = forced;
+    if (!p.status) { set_error("gemv: no kernel status word on this device"); return B200FC_ERR_CUDA; }
+    p.wait_limit_ns = wait_limit_ns();
+    static int pf_cap = -1, per_sm = 0, force_stream = 0;   // environment switches, for experiments
+    if (pf_cap < 0) {
+        const char* e = getenv("B200FC_GEMV_PREFETCH");      // stages prefetched into L2 at CTA start (0 = none)
+        pf_cap = e ? atoi(e) : 0;
+        if (pf_cap < 0) pf_cap = 0;
+        if (pf_cap > 64) pf_cap = 64;
+        e = getenv("B200FC_GEMV_CTAS_PER_SM");               // 1 leaves the second resident place to the next kernel
+        per_sm = (e && atoi(e) == 1) ? 1 : 2;
+        e = getenv("B200FC_GEMV_STREAMK");                   // 1: never align pieces with row blocks
+        force_stream = (e && atoi(e) == 1) ? 1 : 0;
     }
-    p.splits = S;
+    p.pf_cap = pf_cap;
+    int sms = device_sms();
+    if (sm_limit() > 0 && sm_limit() < sms) sms = sm_limit();
+    long long gmax = (long long)sms * per_sm;
+    if (gmax > kGemvMaxCtas) gmax = kGemvMaxCtas;
+    // Three ways to cut the work; the cost model counts the stages of the longest CTA plus the time of the reduction
+    // that follows, in units of one stage's streaming time.
+    //   stream-K: equal pieces whatever the shape; a CTA may hold the end of one row block and the start of the next,
+    //             partial sums meet through the global scratch (several round trips to L2, twice for such a CTA);
+    //   aligned:  S pieces per row block, one per CTA.  S = 1 needs no reduction; 2 <= S <= 8 runs as clusters of S CTAs
+    //             whose partial sums meet in distributed shared memory (fast, so this wins for small matrices).
+    long long grid = gmax < p.total / 2 ? gmax : p.total / 2;
+    if (grid < 1) grid = 1;
+    long long best = (p.total + grid - 1) / grid + 6;
+    p.S = 0; p.cluster = 0;
+    if (!force_stream && row_blocks <= gmax) {
+        int S = (int)(gmax / row_blocks);
+        if (S > 8) S = 8;
+        if (S > p.spr / 2) S = p.spr / 2;
+        if (S < 1) S = 1;
+        const long long cost = (p.spr + S - 1) / S + (S > 1 ? 1 : 0);
+        if (cost <= best) { best = cost; p.S = S; p.cluster = S > 1 ? 1 : 0; grid = (long long)row_blocks * S; }
+    }
+#ifdef B200FC_TRACE
+    {
+        static unsigned long long* tr = nullptr;
+        static int launches = 0;
+        if (!tr) {
+            if (cudaMalloc(&tr, 64 * 320 * 8 * 8) != cudaSuccess) { set_error("trace buffer"); return B200FC_ERR_NOMEM; }
+            cudaMemset(tr, 0, 64 * 320 * 8 * 8);
+        }
+        p.trace = tr; p.trace_launch = launches++;
+        g_trace_ptr = tr;
+    }
+#endif
+    if (!scratch) {
+        int rc = get_stream_scratch(gemv_scratch_bytes(), s, 2, &scratch);
+        if (rc) return rc;
+    }
+    p.counters = (unsigned*)scratch;
+    p.slots = (float*)((char*)scratch + (size_t)kGemvMaxCtas * sizeof(unsigned));
     const bool w8 = w.dtype == B200FC_S8;
-    if (M <= 8) return w8 ? launch_variant<true, 1>(map, p, row_ctas, s) : launch_variant<false, 1>(map, p, row_ctas, s);
-    return w8 ? launch_variant<true, 2>(map, p, row_ctas, s) : launch_variant<false, 2>(map, p, row_ctas, s);
+    if (M <= 8) return w8 ? launch_variant<true, 1>(map, p, (int)grid, s) : launch_variant<false, 1>(map, p, (int)grid, s);
+    return w8 ? launch_variant<true, 2>(map, p, (int)grid, s) : launch_variant<false, 2>(map, p, (int)grid, s);
 }
 
 }  // namespace b200fc

@@ -7,6 +7,10 @@
 // cudaMalloc on demand, so those callers cannot use it.  The entry point below does the same computation for
 // decode-shaped batches with the activation held in a fixed device array that is part of this library's image.
 //
+// The decode kernel itself also needs a little global scratch (partial sums of weight-row blocks that two SMs share,
+// and their arrival counters), which the ordinary entry points take from a per-stream allocation; here it is a second
+// fixed device array.
+//
 // It has no counterpart in the reference (whose activation buffer grows inside MLP::run).
 #include <map>
 #include <mutex>
@@ -19,23 +23,31 @@ namespace {
 constexpr size_t kStaticActBytes = (size_t)1 << 20;  // 1 MiB: M * (N / tp) <= 524288 elements, e.g. 16 rows x 28672
 static __device__ __align__(256) unsigned char g_static_act[kStaticActBytes];
 
+// The decode kernel's counters (first, zero from load and left zero by every launch) and partial-sum slots.
+constexpr size_t kStaticGemvBytes = (size_t)b200fc::kGemvMaxCtas * (2 * 16 * 128 * sizeof(float) + sizeof(unsigned));
+static __device__ __align__(256) unsigned char g_static_gemv[kStaticGemvBytes];
+
+struct StaticAddr { void* act; void* gemv; };
 std::mutex g_mu;
-std::map<int, void*> g_addr;  // device ordinal -> device address of g_static_act on that device
+std::map<int, StaticAddr> g_addr;  // device ordinal -> device addresses of the two arrays on that device
 
 // In host code the name g_static_act is only a handle for the symbol, not a device address; the address has to be
 // asked for, once per device, with that device current.
-int static_act_address(void** out) {
+int static_addresses(StaticAddr* out) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return b200fc::cuda_fail(e, "cudaGetDevice");
     std::lock_guard<std::mutex> lk(g_mu);
     auto it = g_addr.find(dev);
     if (it == g_addr.end()) {
-        void* p = nullptr;
-        e = cudaGetSymbolAddress((void**)&p, g_static_act);
+        if (b200fc::gemv_scratch_bytes() > kStaticGemvBytes) { b200fc::set_error("mlp_run_decode_static: internal scratch size mismatch"); return B200FC_ERR_INVALID; }
+        StaticAddr a = {nullptr, nullptr};
+        e = cudaGetSymbolAddress((void**)&a.act, g_static_act);
         if (e != cudaSuccess) return b200fc::cuda_fail(e, "cudaGetSymbolAddress(g_static_act)");
-        if (!p) { b200fc::set_error("mlp_run_decode_static: null symbol address"); return B200FC_ERR_CUDA; }
-        it = g_addr.emplace(dev, p).first;
+        e = cudaGetSymbolAddress((void**)&a.gemv, g_static_gemv);
+        if (e != cudaSuccess) return b200fc::cuda_fail(e, "cudaGetSymbolAddress(g_static_gemv)");
+        if (!a.act || !a.gemv) { b200fc::set_error("mlp_run_decode_static: null symbol address"); return B200FC_ERR_CUDA; }
+        it = g_addr.emplace(dev, a).first;
     }
     *out = it->second;
     return B200FC_OK;
@@ -46,6 +58,7 @@ int static_act_address(void** out) {
 extern "C" {
 
 int64_t b200fc_mlp_decode_static_capacity(void) { return (int64_t)kStaticActBytes; }
+int64_t b200fc_mlp_decode_static_footprint(void) { return (int64_t)(kStaticActBytes + kStaticGemvBytes); }
 
 int b200fc_mlp_run_decode_static(b200fc_mlp_t* h, const void* x, int64_t ldx, int M, void* out, int out_dtype,
                                  int64_t ldo, void* stream) {
@@ -64,18 +77,20 @@ int b200fc_mlp_run_decode_static(b200fc_mlp_t* h, const void* x, int64_t ldx, in
                   M, m.Ns, need, kStaticActBytes);
         return B200FC_ERR_INVALID;
     }
-    void* act = nullptr;
-    int rc = static_act_address(&act);
+    StaticAddr addr;
+    int rc = static_addresses(&addr);
     if (rc) return rc;
+    void* act = addr.act;
     // gate/up projection + SiLU*up writes all M x Ns activation elements before the down projection reads them, and
-    // the down projection reads nothing beyond them, so nothing in the scratch has to be cleared between calls.
+    // the down projection reads nothing beyond them, so nothing in the activation array has to be cleared between
+    // calls.  The decode kernel writes every partial-sum slot before it reads it and returns its counters to zero.
     b200fc_epilogue_t e1 = {};
     e1.steps = B200FC_STEP_SILU_MUL; e1.out_dtype = B200FC_BF16; e1.C = act; e1.ldc_bytes = (int64_t)m.Ns * 2;
-    rc = matmul_device(m.gate_up, nullptr, x, B200FC_BF16, M, m.K, ldx, 0, 2 * m.Ns, &e1, s);
+    rc = matmul_device(m.gate_up, nullptr, x, B200FC_BF16, M, m.K, ldx, 0, 2 * m.Ns, &e1, s, addr.gemv);
     if (rc) return rc;
     b200fc_epilogue_t e2 = {};
     e2.steps = 0; e2.out_dtype = out_dtype; e2.C = out; e2.ldc_bytes = ldo;
-    return matmul_device(m.down, nullptr, act, B200FC_BF16, M, m.Ns, (int64_t)m.Ns * 2, 0, m.K, &e2, s);
+    return matmul_device(m.down, nullptr, act, B200FC_BF16, M, m.Ns, (int64_t)m.Ns * 2, 0, m.K, &e2, s, addr.gemv);
 }
 
 }  // extern "C"

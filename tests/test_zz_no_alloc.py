@@ -23,14 +23,20 @@ def test_decode_static_matches_allocating_entry_point_twice():
     gate, up = H.normal_bf16(rng, (N, K), 0.02), H.normal_bf16(rng, (N, K), 0.02)
     down = H.normal_bf16(rng, (K, N), 0.02)
     mlp = capi.Mlp(gate.ctypes.data, up.ctypes.data, down.ctypes.data, K, N)
-    for M in (16, 3):                       # second call: fewer rows, scratch still holds the first call's rows
+    import torch
+    for call, M in enumerate((16, 3)):      # second call: fewer rows, scratch still holds the first call's rows
         x = H.normal_bf16(rng, (M, K))
         dx = H.Dev(x)
         want = H.Dev(shape=(M, K), dtype=np.uint16)
         mlp.run(dx.ptr, dx.ld, M, want.ptr, want.ld)
         got = H.Dev(shape=(M, K), dtype=np.uint16, fill=0xCD)
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]          # cudaMemGetInfo: bytes the driver could still hand out
         mlp.run_decode_static(dx.ptr, dx.ld, M, got.ptr, capi.BF16, got.ld)
         capi.sync_check()
+        if call == 1:
+            # the first call may make the driver load kernels; by the second nothing at all may be taken from the device
+            assert torch.cuda.mem_get_info()[0] == free_before
         w, g = want.numpy(), got.numpy()
         assert np.isfinite(H.bf16_to_f32(g)).all()
         assert np.array_equal(g, w)         # same kernels, same arithmetic: tolerance zero
