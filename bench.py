@@ -4,18 +4,22 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--M rows] [--workload name]
 
 Workloads (synthetic, seeded; shapes from the reference's own benchmark configuration list):
-  llama7b_mlp   x[M,4096] ~N(0,1), W_gate/W_up [11008,4096], W_down [4096,11008] ~N(0,0.02), bf16, fp32 accumulate,
-                bf16 output.  Default at 1 GPU with M = 2048 (prefill-shaped, tensor-core bound).
-  llama70b_mlp  hidden 8192, intermediate 28672, M = 4096, tensor-parallel over N GPUs (gate/up column split, down
-                row split, one all-reduce on the output: inside the down-projection kernel when torch symmetric
-                memory offers an NVLink multicast mapping, else NCCL; --tp-mode).  Default when N > 1; strong scaling.
-A step is one MLP forward over one batch.  value = 6*M*H*I flops / time, whole job.  Weights (>= 270 MB) exceed the
-126 MB L2, so every step streams them from HBM again.
+  llama70b_mlp  hidden 8192, intermediate 28672, M = 4096 rows, bf16, fp32 accumulate, bf16 output.  The default at
+                every N: one GPU holds the whole MLP (1.41 GB of weights), N > 1 splits it Megatron-style (gate/up
+                column split, down row split, one all-reduce on the output: inside the down-projection kernel when
+                torch symmetric memory offers an NVLink multicast mapping, else NCCL; --tp-mode).  Strong scaling.
+  llama7b_mlp   x[M,4096] ~N(0,1), W_gate/W_up [11008,4096], W_down [4096,11008] ~N(0,0.02), M = 2048; at one GPU it
+                is also measured beside the main workload and reported under the key "llama7b_mlp".
+A step is one MLP forward over one batch.  value = 6*M*H*I flops / time, whole job.  Weights exceed the 126 MB L2,
+so every step streams them from HBM again.
 
-The line also carries: e2e (the same step through the host-buffer C-ABI call, pinned host x in, host out back),
-roofline of the dominant kernel (gate/up GEMM, timed live with CUDA events), a decode-shaped leg (M = 1, weight
-stream GB/s), the CPU baseline (the reference's own AMX kernels on the host cores when the CPU has AMX, else the
-plain C++ oracle port), clocks sampled during the timed region, and the number of kernels this library launched.
+The line also carries: parity (the timed path's output against an fp32 sum of the per-rank contributions over NCCL
+and, for the first rows, against the CPU oracle; a failure exits non-zero), e2e (the same step fed from pinned host
+memory with the result copied back), roofline of the dominant kernel (gate/up GEMM, timed live with CUDA events), a
+sustained leg (the same step repeated for over a second), decode-shaped legs (M = 1 and 16, weight stream GB/s), the
+other single-GPU configurations, the CPU baseline (the reference's own AMX kernels on the host cores when the CPU has
+AMX, else the plain C++ oracle port), clocks sampled during the timed region, and the number of kernels this library
+launched.
 
 --impl reference times only the CPU arm (reference AMX code or port) on the same configuration.
 """
@@ -37,9 +41,18 @@ WORKLOADS = {
     "llama7b_mlp": dict(H=4096, I=11008, M=2048),
     "llama70b_mlp": dict(H=8192, I=28672, M=4096),
 }
-# DRAM traffic of one gate/up GEMM launch (dram__bytes_read.sum + dram__bytes_write.sum), from the ncu capture
-# summarised in the profiles/ file named beside it; None where no capture exists for the workload.
-NCU_TRAFFIC_BYTES = {"llama7b_mlp": 233.73e6, "llama70b_mlp": None}  # profiles/gemm_tc2_kernel_llama7b_mlp_M2048.md
+DEFAULT_WORKLOAD = "llama70b_mlp"
+PARITY_BAR = 1e-2     # max |err| / max |ref| after bf16 output rounding, the bound of the bf16 paths
+
+
+def ncu_traffic_bytes(name, world):
+    """DRAM traffic of one gate/up GEMM launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu capture
+    recorded for this workload and group size, or None when none was taken."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
+            return json.load(f).get("%s_tp%d" % (name, world), {}).get("gate_up_dram_bytes")
+    except (OSError, ValueError):
+        return None
 
 
 _REAL_STDOUT = None
@@ -84,7 +97,6 @@ class ClockSampler:
 
     def __init__(self, index):
         self.index, self.proc, self.lines = index, None, []
-        self.t0 = self.t1 = None
 
     def start(self):
         try:
@@ -100,22 +112,15 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
-    def begin(self):
-        self.t0 = datetime.datetime.now()
-
-    def end(self):
-        self.t1 = datetime.datetime.now()
-
     def stop(self):
         if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.03)   # let the sample that covers the end of the region arrive
+            return
+        time.sleep(0.03)   # let the sample that covers the end of the last region arrive
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except Exception:
             pass
-        return summarise_clock_lines(self.lines, self.t0, self.t1)
 
 
 def summarise_clock_lines(lines, t0, t1):
@@ -162,41 +167,60 @@ def weight_bytes(w):
 
 
 # ------------------------------------------------------------------------------------------------ CPU arm
-def cpu_arm(w, M, budget_s=20.0, min_reps=1):
-    """Times the CPU implementation of the same MLP on the host cores.  Returns (seconds per full step, info)."""
+CPU_SAMPLE_ROWS = 512   # rows of the batch the CPU arm multiplies per repeat when the full batch would take minutes
+
+
+def host_normal_bf16(shape, std, seed):
+    """[rows, cols] of bf16 bit patterns ~N(0, std): numpy generators on all cores, one row slab per thread (numpy
+    releases the GIL while it draws and converts)."""
     import numpy as np
-    from oracle import ref as oref
+    from concurrent.futures import ThreadPoolExecutor
     from oracle._common import bf16_bits
+    out = np.empty(shape, np.uint16)
+    nthr = max(1, min(os.cpu_count() or 1, 32))
+    slab = max(1, (shape[0] + nthr - 1) // nthr)
+    seeds = np.random.SeedSequence(seed).spawn(nthr)
+
+    def fill(i):
+        r0, r1 = i * slab, min(shape[0], (i + 1) * slab)
+        rng = np.random.default_rng(seeds[i])
+        step = max(1, (1 << 22) // shape[1])
+        for r in range(r0, r1, step):
+            blk = rng.standard_normal((min(step, r1 - r), shape[1]), dtype=np.float32) * np.float32(std)
+            out[r:r + blk.shape[0]] = bf16_bits(blk)
+
+    with ThreadPoolExecutor(nthr) as ex:
+        list(ex.map(fill, range(nthr)))
+    return out
+
+
+def cpu_arm(w, M, budget_s=20.0, min_reps=1):
+    """Times the CPU implementation of the same MLP on the host cores.  Returns (seconds per full step, info).
+    A batch larger than CPU_SAMPLE_ROWS is sampled: CPU_SAMPLE_ROWS of its rows are multiplied per repeat (the weights
+    are the full ones, so every repeat streams them once, as a full step does) and the time is scaled by the row ratio."""
+    from oracle import ref as oref
     H, I = w["H"], w["I"]
-    rng = np.random.default_rng(1001)
-
-    def gen(shape, std):
-        out = np.empty(shape, np.uint16)
-        rows = max(1, (1 << 22) // shape[1])
-        for r0 in range(0, shape[0], rows):
-            blk = rng.standard_normal((min(rows, shape[0] - r0), shape[1]), dtype=np.float32) * np.float32(std)
-            out[r0:r0 + blk.shape[0]] = bf16_bits(blk)
-        return out
-
+    gate, up, down = (host_normal_bf16((I, H), 0.02, 1001), host_normal_bf16((I, H), 0.02, 1002),
+                      host_normal_bf16((H, I), 0.02, 1003))
     if oref.available():
         nthr = os.cpu_count() or 1
-        gate, up, down = gen((I, H), 0.02), gen((I, H), 0.02), gen((H, I), 0.02)
+        Ms = min(M, CPU_SAMPLE_ROWS)
         mlp = oref.MLP(gate, up, down, nthr=nthr)
-        x = gen((M, H), 1.0)
+        x = host_normal_bf16((Ms, H), 1.0, 7)
         t0 = time.perf_counter(); mlp.run(x); first = time.perf_counter() - t0   # packs the weights (constB)
         reps, t_acc = 0, 0.0
         while reps < min_reps or (t_acc < budget_s and reps < 50):
             t0 = time.perf_counter(); mlp.run(x); t_acc += time.perf_counter() - t0; reps += 1
-        sec = t_acc / reps
+        sec = t_acc / reps * (M / Ms)
+        what = "full workload M=%d" % M if Ms == M else "%d of the %d rows per repeat (full weights), time scaled by %.0fx" % (Ms, M, M / Ms)
         info = dict(kind="reference", cores=nthr,
-                    sample="full workload M=%d, %d repeats after one packing run (%.1f s); reference AMX Matmul + "
-                           "restated SiLU / split-K down on %d threads" % (M, reps, first, nthr))
+                    sample="%s, %d repeats after one packing run (%.1f s); reference AMX Matmul + restated SiLU / "
+                           "split-K down on %d threads" % (what, reps, first, nthr))
         return sec, info
     # no AMX (or shim not built): the plain C++ port on a reduced number of rows, scaled to the full batch
     from oracle import port
     Ms = min(M, 16)
-    gate, up, down = gen((I, H), 0.02), gen((I, H), 0.02), gen((H, I), 0.02)
-    x = gen((Ms, H), 1.0)
+    x = host_normal_bf16((Ms, H), 1.0, 7)
     t0 = time.perf_counter(); port.mlp(x, gate, up, down); sec_s = time.perf_counter() - t0
     sec = sec_s * (M / Ms)
     info = dict(kind="port", cores=port.threads(),
@@ -213,16 +237,55 @@ def run_reference(args, w, M, name):
     info["value"] = val; info["unit"] = "TFLOP/s"
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
-            "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": name, "M": M, "hidden": w["H"], "intermediate": w["I"],
-                       "cold": "weights larger than last-level cache"},
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": config_of(name, w, M),
             "cpu_baseline": info,
             "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     emit(line)
 
 
+def config_of(name, w, M):
+    """The part of `config` that names the workload; identical in both arms."""
+    return {"workload": name, "M": M, "hidden": w["H"], "intermediate": w["I"]}
+
+
 # ------------------------------------------------------------------------------------------------ GPU arm
+def make_shard(torch, capi, w, world, rank, dev, stream, keep_weights):
+    """This rank's shard of the MLP, generated on the device (synthetic weights: seed 1001 + rank).  Returns the packed
+    object and, if asked, the three bf16 shard matrices (for the oracle check)."""
+    H, Is = w["H"], w["I"] // world
+    g = torch.Generator(device=dev); g.manual_seed(1001 + rank)
+
+    def randn(shape, std):
+        return (torch.randn(shape, generator=g, device=dev, dtype=torch.float32) * std).to(torch.bfloat16)
+    gate, up, down = randn((Is, H), 0.02), randn((Is, H), 0.02), randn((H, Is), 0.02)
+    mlp = capi.Mlp(gate.data_ptr(), up.data_ptr(), down.data_ptr(), H, Is, 0, 1, stream)
+    return mlp, ((gate, up, down) if keep_weights else None)
+
+
+def time_steps(torch, fn, steps, barrier=None):
+    """milliseconds per call of fn over `steps` calls, CUDA events on the current stream"""
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if barrier:
+        barrier()
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    if barrier:
+        barrier()
+    else:
+        torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def bits_of(torch, t):
+    import numpy as np
+    return t.contiguous().cpu().view(torch.int16).numpy().view(np.uint16)
+
+
 def run_ours(args, w, M, name):
+    import numpy as np
     import torch
     import torch.distributed as dist
     from mm_amx_b200 import capi, tp
@@ -242,37 +305,35 @@ def run_ours(args, w, M, name):
     Is = I // world
     stream = torch.cuda.current_stream().cuda_stream
     peaks = measured_peaks()
+    legs = args.legs
 
-    g = torch.Generator(device=dev); g.manual_seed(1001 + rank)
-    def randn(shape, std):
-        return (torch.randn(shape, generator=g, device=dev, dtype=torch.float32) * std).to(torch.bfloat16)
-    # this rank's shard, generated in place (synthetic weights need no global consistency)
-    gate, up, down = randn((Is, H), 0.02), randn((Is, H), 0.02), randn((H, Is), 0.02)
+    mlp, shard = make_shard(torch, capi, w, world, rank, dev, stream, "parity" in legs)
     gx = torch.Generator(device=dev); gx.manual_seed(7)
     x = (torch.randn((M, H), generator=gx, device=dev, dtype=torch.float32)).to(torch.bfloat16)
-    mlp = capi.Mlp(gate.data_ptr(), up.data_ptr(), down.data_ptr(), H, Is, 0, 1, stream)
-    del gate, up, down
     mlp.reserve(M)
     out = torch.empty((M, H), dtype=torch.bfloat16, device=dev)
+
+    class Local:
+        def run_partial(self, xx, oo):
+            dt = capi.F32 if oo.dtype == torch.float32 else capi.BF16
+            mlp.run_partial(xx.data_ptr(), H * 2, xx.shape[0], oo.data_ptr(), dt, oo.stride(0) * oo.element_size(),
+                            torch.cuda.current_stream().cuda_stream)
+
+        def gate_up(self, xx):
+            mlp.gate_up(xx.data_ptr(), H * 2, xx.shape[0], torch.cuda.current_stream().cuda_stream)
+
+        def down_rows(self, row0, rows, oo):
+            dt = capi.F32 if oo.dtype == torch.float32 else capi.BF16
+            mlp.down_rows(row0, rows, oo.data_ptr(), dt, oo.stride(0) * oo.element_size(),
+                          torch.cuda.current_stream().cuda_stream)
 
     if world == 1:
         def step():
             mlp.run(x.data_ptr(), H * 2, M, out.data_ptr(), H * 2, stream)
+            return out
     else:
-        class Local:
-            def run_partial(self, xx, oo):
-                dt = capi.F32 if oo.dtype == torch.float32 else capi.BF16
-                mlp.run_partial(xx.data_ptr(), H * 2, xx.shape[0], oo.data_ptr(), dt, oo.stride(0) * oo.element_size(),
-                                torch.cuda.current_stream().cuda_stream)
-
-            def gate_up(self, xx):
-                mlp.gate_up(xx.data_ptr(), H * 2, xx.shape[0], torch.cuda.current_stream().cuda_stream)
-
-            def down_rows(self, row0, rows, oo):
-                dt = capi.F32 if oo.dtype == torch.float32 else capi.BF16
-                mlp.down_rows(row0, rows, oo.data_ptr(), dt, oo.stride(0) * oo.element_size(),
-                              torch.cuda.current_stream().cuda_stream)
         mode = args.tp_mode
+        pull = None
         if mode == "auto":
             # the in-kernel pull all-reduce needs symmetric memory with an NVLink multicast mapping on every rank
             try:
@@ -304,134 +365,211 @@ def run_ours(args, w, M, name):
             dist.barrier()
         torch.cuda.synchronize()
 
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- parity of the path that is about to be timed (outside the timed region) ----
+    parity = None
+    if "parity" in legs:
+        got = step().clone()
+        capi.sync_check(stream)
+        ref32 = torch.empty((M, H), dtype=torch.float32, device=dev)
+        Local().run_partial(x, ref32)
+        if world > 1:
+            dist.all_reduce(ref32)      # NCCL, fp32: the sum the reference forms before it rounds (tests/amx-mlp.cpp:656-683)
+        ref = ref32.to(torch.bfloat16)
+        del ref32
+        rel = float(((got.float() - ref.float()).abs().max() / ref.float().abs().max()).item())
+        parity = {"vs": "fp32 sum of the per-rank contributions (run_partial -> fp32 -> all-reduce over NCCL -> bf16)",
+                  "max_rel": max_over_ranks(rel), "bar": PARITY_BAR}
+        # first rows against the CPU oracle on the full matrices (rank 0 gathers the shards)
+        rows = min(M, 16)
+        gate, up, down = shard
+        if world > 1:
+            parts = []
+            for t in (gate, up, down):
+                lst = [torch.empty_like(t) for _ in range(world)] if rank == 0 else None
+                dist.gather(t, lst, dst=0)
+                parts.append(lst)
+            if rank == 0:
+                gate, up, down = torch.cat(parts[0], 0), torch.cat(parts[1], 0), torch.cat(parts[2], 1)
+            del parts
+        if rank == 0:
+            from oracle import port
+            t0 = time.perf_counter()
+            want = port.mlp(bits_of(torch, x[:rows]), bits_of(torch, gate), bits_of(torch, up), bits_of(torch, down))
+            want_f = (want.astype(np.uint32) << 16).view(np.float32)
+            got_f = (bits_of(torch, got[:rows]).astype(np.uint32) << 16).view(np.float32)
+            parity["oracle_rows"] = rows
+            parity["oracle_max_rel"] = float(np.abs(got_f - want_f).max() / np.abs(want_f).max())
+            parity["oracle_seconds"] = time.perf_counter() - t0
+        del gate, up, down, got, ref
+        shard = None
+        if world > 1:
+            flag = torch.tensor([parity.get("oracle_max_rel", 0.0)], device=dev, dtype=torch.float64)
+            dist.broadcast(flag, 0)
+            parity["oracle_max_rel"] = float(flag.item())
+        parity["ok"] = bool(parity["max_rel"] <= PARITY_BAR and parity["oracle_max_rel"] <= PARITY_BAR)
+        torch.cuda.empty_cache()
+
+    # ---- the timed region ----
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
     l0 = capi.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    sampler.begin()
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
-    sampler.end()
+    t_begin = datetime.datetime.now()
+    ms = time_steps(torch, step, args.steps, barrier)
+    t_end = datetime.datetime.now()
     launches = capi.launch_count() - l0
-    ms = e0.elapsed_time(e1) / args.steps
     capi.sync_check(stream)
+    ms = max_over_ranks(ms)
     if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
         lt = torch.tensor([launches], device=dev, dtype=torch.int64)
         dist.all_reduce(lt)
         launches = int(lt.item())
-    clocks = sampler.stop() if rank == 0 else None
     value = flops_of(w, M) / (ms * 1e-3) / 1e12
 
-    # ---- dominant kernel alone: gate/up GEMM of this rank, K launches back to back (sustained regime) ----
+    # ---- dominant kernel alone: gate/up GEMM of this rank, K launches back to back ----
     roofline = None
-    for _ in range(3 if "kernel" in args.legs else 0):
-        mlp.gate_up(x.data_ptr(), H * 2, M, stream)
-    if "kernel" in args.legs:
-      torch.cuda.synchronize()
-      k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-      k0.record()
-      for _ in range(args.steps):
-        mlp.gate_up(x.data_ptr(), H * 2, M, stream)
-      k1.record(); torch.cuda.synchronize()
-      k_ms = k0.elapsed_time(k1) / args.steps
-      k_flops = 4.0 * M * H * Is
-      achieved = k_flops / (k_ms * 1e-3) / 1e12
-      roofline = {"kernel": "gemm_tc2_kernel (gate/up projection + SiLU*up epilogue)", "bound": "tensor",
-                "achieved": achieved, "peak": peaks["bf16_burst"], "unit": "TFLOP/s",
-                "frac": achieved / peaks["bf16_burst"],
-                "peak_source": peaks["source"] + " (cuBLAS bf16 burst figure: the kernel is timed alone, in a loop "
-                                                 "far shorter than the power-cap time constant)",
-                "frac_of_sustained_peak": achieved / peaks["bf16_sustained"], "us_per_launch": k_ms * 1e3,
-                "flops_per_launch": k_flops, "traffic": NCU_TRAFFIC_BYTES.get(name)}
+    if "kernel" in legs:
+        def gate_up_only():
+            mlp.gate_up(x.data_ptr(), H * 2, M, stream)
+        for _ in range(3):
+            gate_up_only()
+        torch.cuda.synchronize()
+        k_ms = time_steps(torch, gate_up_only, args.steps)
+        k_flops = 4.0 * M * H * Is
+        achieved = k_flops / (k_ms * 1e-3) / 1e12
+        roofline = {"kernel": "gemm_tc2_kernel (gate/up projection + SiLU*up epilogue)", "bound": "tensor",
+                    "achieved": achieved, "peak": peaks["bf16_burst"], "unit": "TFLOP/s",
+                    "frac": achieved / peaks["bf16_burst"],
+                    "peak_source": peaks["source"] + " (cuBLAS bf16 burst figure: the kernel is timed alone, in a loop "
+                                                     "far shorter than the power-cap time constant)",
+                    "frac_of_sustained_peak": achieved / peaks["bf16_sustained"], "us_per_launch": k_ms * 1e3,
+                    "flops_per_launch": k_flops, "traffic": ncu_traffic_bytes(name, world)}
+
+    sustained = None
+    s_begin = s_end = None
 
     line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": name, "M": M, "hidden": H, "intermediate": I,
-                       "parallelism": ("tp%d (%s all-reduce)" % (world, args.tp_mode)) if world > 1 else "single GPU",
-                       "cold": "weights (%.0f MB per GPU) larger than the 126 MB L2" % (weight_bytes(w) / world / 1e6)},
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": dict(config_of(name, w, M),
+                           parallelism=("tp%d (%s all-reduce)" % (world, args.tp_mode)) if world > 1 else "single GPU",
+                           cold="weights (%.0f MB per GPU) larger than the 126 MB L2" % (weight_bytes(w) / world / 1e6)),
             "gpu_launches": launches, "roofline": roofline}
-
-    if rank == 0:
-        line["clocks"] = clocks
-
-    # ---- end to end through the host-buffer entry point (1 GPU) / host x in + host out back (N GPUs) ----
-    if "e2e" in args.legs:
+    if parity is not None:
+        line["parity"] = parity
+    # ---- end to end: x from pinned host memory in, result back to pinned host memory, every step ----
+    if "e2e" in legs:
         xh = torch.empty((M, H), dtype=torch.bfloat16).pin_memory(); xh.copy_(x.cpu())
         oh = torch.empty((M, H), dtype=torch.bfloat16).pin_memory()
         if world == 1:
             def e2e_step():
                 mlp.run_host(xh.data_ptr(), H * 2, M, oh.data_ptr(), H * 2, stream)
+            h2d = d2h = M * H * 2
+            api = "b200fc_mlp_run_host (pinned host buffers)"
+        elif M % world == 0:
+            # every rank moves only its 1/N of the rows over PCIe; the rows are exchanged over NVLink (all-gather)
+            r0, r1 = rank * (M // world), (rank + 1) * (M // world)
+            def e2e_step():
+                x[r0:r1].copy_(xh[r0:r1], non_blocking=True)
+                dist.all_gather_into_tensor(x, x[r0:r1])
+                oh[r0:r1].copy_(step()[r0:r1], non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+            h2d = d2h = M * H * 2
+            api = ("per rank: 1/N of the rows of x host -> device, all-gather over NVLink, tensor-parallel forward, "
+                   "1/N of the rows of the result device -> host")
         else:
             def e2e_step():
                 x.copy_(xh, non_blocking=True)
                 oh.copy_(step(), non_blocking=True)
                 torch.cuda.current_stream().synchronize()
+            h2d = d2h = M * H * 2 * world
+            api = "per rank: host x -> device, tensor-parallel forward, device out -> host"
         for _ in range(3):
             e2e_step()
-        barrier()
-        e0.record()
-        for _ in range(args.steps):
-            e2e_step()
-        e1.record()
-        barrier()
-        e_ms = e0.elapsed_time(e1) / args.steps
-        if world > 1:
-            t = torch.tensor([e_ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e_ms = float(t.item())
+        e_ms = max_over_ranks(time_steps(torch, e2e_step, args.steps, barrier))
+        capi.sync_check(stream)
         line["e2e"] = {"value": flops_of(w, M) / (e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e_ms,
-                       "h2d_bytes_per_step": M * H * 2 * world, "d2h_bytes_per_step": M * H * 2 * world,
-                       "api": "b200fc_mlp_run_host (pinned host buffers)" if world == 1 else
-                              "host x -> device, tensor-parallel forward, device out -> host, per rank"}
+                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "api": api}
+        del xh, oh
 
-    # ---- decode-shaped leg: M = 1, the weight stream in GB/s against the measured HBM copy bandwidth ----
-    if world == 1 and "decode" in args.legs:
-        x1 = x[:1].contiguous()
-        o1 = torch.empty((1, H), dtype=torch.bfloat16, device=dev)
-        def dstep():
-            mlp.run(x1.data_ptr(), H * 2, 1, o1.data_ptr(), H * 2, stream)
-        for _ in range(5):
-            dstep()
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        reps = 20
-        try:
-            with torch.cuda.graph(graph):
-                s2 = torch.cuda.current_stream().cuda_stream
-                for _ in range(reps):
-                    mlp.run(x1.data_ptr(), H * 2, 1, o1.data_ptr(), H * 2, s2)
-            graph.replay(); torch.cuda.synchronize()
-            e0.record(); graph.replay(); e1.record(); torch.cuda.synchronize()
-            d_ms = e0.elapsed_time(e1) / reps
-            how = "CUDA graph of %d forwards" % reps
-        except Exception as ex:  # graph capture unavailable: plain launches
+    # ---- one GPU only: the Llama-7B MLP beside it, decode-shaped legs, the other configurations, the CPU baseline ----
+    if world == 1:
+        w7, name7 = WORKLOADS["llama7b_mlp"], "llama7b_mlp"
+        if name == name7:
+            mlp7, x7, M7 = mlp, x, M
+        elif legs & {"llama7b", "decode"}:
+            M7 = w7["M"]
+            mlp7, _ = make_shard(torch, capi, w7, 1, 0, dev, stream, False)
+            x7 = x[:M7, :w7["H"]].contiguous()
+            mlp7.reserve(M7)
+        if "llama7b" in legs and name != name7:
+            time.sleep(0.5)     # burst-type measurement: let the power-cap averaging window empty first
+            H7 = w7["H"]
+            out7 = torch.empty((M7, H7), dtype=torch.bfloat16, device=dev)
+            def step7():
+                mlp7.run(x7.data_ptr(), H7 * 2, M7, out7.data_ptr(), H7 * 2, stream)
+            def gate_up7():
+                mlp7.gate_up(x7.data_ptr(), H7 * 2, M7, stream)
+            for _ in range(3):
+                step7()
             torch.cuda.synchronize()
-            e0.record()
-            for _ in range(reps):
-                dstep()
-            e1.record(); torch.cuda.synchronize()
-            d_ms = e0.elapsed_time(e1) / reps
-            how = "plain launches (%s)" % type(ex).__name__
-        gbs = weight_bytes(w) / (d_ms * 1e-3) / 1e9
-        line["decode"] = {"M": 1, "value": gbs, "unit": "GB/s", "us_per_step": d_ms * 1e3, "timing": how,
-                          "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                       "frac": gbs / peaks["hbm_gbs"], "peak_source": peaks["source"]}}
+            ms7 = time_steps(torch, step7, args.steps)
+            for _ in range(3):
+                gate_up7()
+            torch.cuda.synchronize()
+            k7 = time_steps(torch, gate_up7, args.steps)
+            a7 = 4.0 * M7 * H7 * w7["I"] / (k7 * 1e-3) / 1e12
+            xh7 = torch.empty((M7, H7), dtype=torch.bfloat16).pin_memory(); xh7.copy_(x7.cpu())
+            oh7 = torch.empty((M7, H7), dtype=torch.bfloat16).pin_memory()
+            def e2e7():
+                mlp7.run_host(xh7.data_ptr(), H7 * 2, M7, oh7.data_ptr(), H7 * 2, stream)
+            for _ in range(3):
+                e2e7()
+            e7 = time_steps(torch, e2e7, args.steps)
+            line[name7] = {"config": config_of(name7, w7, M7), "value": flops_of(w7, M7) / (ms7 * 1e-3) / 1e12,
+                           "unit": "TFLOP/s", "ms_per_step": ms7,
+                           "e2e": {"value": flops_of(w7, M7) / (e7 * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e7,
+                                   "h2d_bytes_per_step": M7 * H7 * 2, "d2h_bytes_per_step": M7 * H7 * 2},
+                           "roofline": {"kernel": "gemm_tc2_kernel (gate/up projection + SiLU*up epilogue)",
+                                        "bound": "tensor", "achieved": a7, "peak": peaks["bf16_burst"],
+                                        "unit": "TFLOP/s", "frac": a7 / peaks["bf16_burst"], "us_per_launch": k7 * 1e3,
+                                        "traffic": ncu_traffic_bytes(name7, 1)}}
+            del xh7, oh7, out7
+        if "decode" in legs:
+            line["decode"] = decode_legs(torch, mlp7, x7, w7, peaks)
+        if "configs" in legs:
+            line["other_configs"] = other_configs(torch, capi, dev, peaks)
 
-    # ---- the other single-GPU configurations of the reference's list, as extra keys (not the headline) ----
-    if world == 1 and "configs" in args.legs:
-        line["other_configs"] = other_configs(torch, capi, dev, peaks)
+    # ---- the same step repeated for over a second: the power-capped regime ----
+    if "sustained" in legs:
+        n_sus = max(args.steps, int(args.sustain_s * 1e3 / ms) + 1)
+        barrier()
+        s_begin = datetime.datetime.now()
+        s_ms = max_over_ranks(time_steps(torch, step, n_sus, barrier))
+        s_end = datetime.datetime.now()
+        capi.sync_check(stream)
+        sustained = {"value": flops_of(w, M) / (s_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "steps": n_sus,
+                     "ms_per_step": s_ms, "seconds": s_ms * n_sus * 1e-3}
+
+    if sustained is not None:
+        line["sustained"] = sustained
+
+    if rank == 0:
+        sampler.stop()
+        line["clocks"] = summarise_clock_lines(sampler.lines, t_begin, t_end) if sampler.proc else \
+            {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        if sustained is not None and sampler.proc:
+            sustained["clocks"] = summarise_clock_lines(sampler.lines, s_begin, s_end)
 
     # ---- CPU baseline beside it (rank 0, 1 GPU only) ----
-    if rank == 0 and world == 1 and "cpu" in args.legs:
+    if rank == 0 and world == 1 and "cpu" in legs:
         try:
             sec, info = cpu_arm(w, M, budget_s=15.0)
             info["value"] = flops_of(w, M) / sec / 1e12; info["unit"] = "TFLOP/s"
@@ -444,6 +582,47 @@ def run_ours(args, w, M, name):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if parity is not None and not parity["ok"]:
+        sys.stderr.write("parity check failed: %s\n" % json.dumps(parity))
+        sys.exit(1)
+
+
+def decode_legs(torch, mlp, x, w, peaks):
+    """Decode-shaped forwards of the Llama-7B MLP (M = 1 and 16): the weight stream in GB/s against the measured HBM copy
+    bandwidth, timed as one CUDA graph of 20 forwards (plain launches if capture is refused)."""
+    H = w["H"]
+    res = {}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for Md in (1, 16):
+        x1 = x[:Md].contiguous()
+        o1 = torch.empty((Md, H), dtype=torch.bfloat16, device=x.device)
+        for _ in range(5):
+            mlp.run(x1.data_ptr(), H * 2, Md, o1.data_ptr(), H * 2, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        reps = 20
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                s2 = torch.cuda.current_stream().cuda_stream
+                for _ in range(reps):
+                    mlp.run(x1.data_ptr(), H * 2, Md, o1.data_ptr(), H * 2, s2)
+            graph.replay(); torch.cuda.synchronize()
+            e0.record(); graph.replay(); e1.record(); torch.cuda.synchronize()
+            how = "CUDA graph of %d forwards" % reps
+        except Exception as ex:  # graph capture unavailable: plain launches
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(reps):
+                mlp.run(x1.data_ptr(), H * 2, Md, o1.data_ptr(), H * 2, torch.cuda.current_stream().cuda_stream)
+            e1.record(); torch.cuda.synchronize()
+            how = "plain launches (%s)" % type(ex).__name__
+        d_ms = e0.elapsed_time(e1) / reps
+        gbs = weight_bytes(w) / (d_ms * 1e-3) / 1e9
+        res["M%d" % Md] = {"M": Md, "value": gbs, "unit": "GB/s", "us_per_step": d_ms * 1e3, "timing": how,
+                           "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                        "frac": gbs / peaks["hbm_gbs"], "peak_source": peaks["source"]}}
+    res["workload"] = "llama7b_mlp"
+    return res
 
 
 def other_configs(torch, capi, dev, peaks):
@@ -503,6 +682,23 @@ def other_configs(torch, capi, dev, peaks):
             out["int8w_gemv_M%d_4096x%d" % (M, N)] = {"us": t * 1e6, "gbs": nbytes / t / 1e9,
                                                       "hbm_frac": nbytes / t / 1e9 / peaks["hbm_gbs"], "weight_sets": nset}
         del ws
+    # one large int8-weight matrix (a tensor-parallel shard of the Llama-70B gate/up projection), where the kernel's
+    # ramp no longer counts: the weight stream itself
+    K, N = 8192, 28672
+    ws = []
+    for _ in range(3):
+        B = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev, generator=g)
+        sc = torch.rand(N, generator=g, device=dev) * 0.019 + 0.001
+        ws.append(capi.Weight(B.data_ptr(), capi.S8, K, N, K, True, capi.PACK_INT8_CHANNEL, sc.data_ptr())); del B
+    for M in (1, 16):
+        x = torch.randn((M, K), generator=g, device=dev).to(torch.bfloat16)
+        C = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        ep = capi.make_epilogue(C.data_ptr(), N * 2, capi.BF16, capi.STEP_DEQUANT)
+        t = timed_graph(lambda s: [w.matmul(x.data_ptr(), capi.BF16, M, K, K * 2, ep, stream=s) for w in ws], len(ws))
+        nbytes = K * N + N * 4 + M * (K + N) * 2
+        out["int8w_gemv_M%d_8192x28672" % M] = {"us": t * 1e6, "gbs": nbytes / t / 1e9,
+                                                "hbm_frac": nbytes / t / 1e9 / peaks["hbm_gbs"], "weight_sets": len(ws)}
+    del ws
     # config 4: int8 x int8 GEMM with quantised post-ops
     M, K, N = 2048, 4096, 4096
     A = torch.randint(-128, 128, (M, K), dtype=torch.int8, device=dev, generator=g)
@@ -526,6 +722,15 @@ def other_configs(torch, capi, dev, peaks):
     for name, ep in cases.items():
         t = timed_graph(lambda s: [w.matmul(A.data_ptr(), capi.S8, M, K, K, ep, stream=s) for w in ws], len(ws))
         out["int8_gemm_2048x4096x4096_" + name] = {"us": t * 1e6, "tops": 2.0 * M * K * N / t / 1e12}
+    # comparison only (never on the product path): the same int8 product by torch's library kernel, as a measured
+    # yardstick for the int8 tensor-core rate of this GPU
+    try:
+        Bs = [torch.randint(-128, 128, (K, N), dtype=torch.int8, device=dev, generator=g) for _ in range(8)]
+        t = timed_graph(lambda s: [torch._int_mm(A, Bm) for Bm in Bs], len(Bs))
+        out["int8_gemm_2048x4096x4096_library_int_mm"] = {"us": t * 1e6, "tops": 2.0 * M * K * N / t / 1e12,
+                                                         "note": "torch._int_mm (library kernel), comparison row"}
+    except Exception as ex:  # noqa: BLE001 - the comparison row is optional
+        out["int8_gemm_2048x4096x4096_library_int_mm"] = {"unavailable": "%s: %s" % (type(ex).__name__, ex)}
     return out
 
 
@@ -545,8 +750,10 @@ def main():
                          "symmetric memory with multicast is available, else nccl")
     ap.add_argument("--comm-sms", type=int, default=8, help="SMs reserved for the reduction in 'pull' mode")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--legs", default="kernel,e2e,decode,configs,cpu",
-                    help="optional legs after the main timed loop (comma list of kernel,e2e,decode,configs,cpu; '' = none)")
+    ap.add_argument("--legs", default="parity,kernel,sustained,e2e,llama7b,decode,configs,cpu",
+                    help="optional legs around the main timed loop (comma list of parity,kernel,sustained,e2e,llama7b,"
+                         "decode,configs,cpu; '' = none)")
+    ap.add_argument("--sustain-s", type=float, default=1.2, help="length of the sustained leg in seconds")
     args = ap.parse_args()
     claim_stdout()
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -555,7 +762,7 @@ def main():
     args.legs = set(x for x in args.legs.split(",") if x)
     if args.no_cpu:
         args.legs.discard("cpu")
-    name = args.workload or ("llama7b_mlp" if args.gpus == 1 else "llama70b_mlp")
+    name = args.workload or DEFAULT_WORKLOAD
     w = WORKLOADS[name]
     M = args.M or w["M"]
     if args.impl == "reference":

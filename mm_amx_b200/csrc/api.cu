@@ -86,12 +86,57 @@ int get_stream_scratch(size_t bytes, cudaStream_t s, int slot, void** out) {
         if (sc.p) { cudaStreamSynchronize(s); cudaFree(sc.p); sc.p = nullptr; sc.bytes = 0; }
         B200FC_CUDA(cudaMalloc(&sc.p, bytes));
         sc.bytes = bytes;
-        B200FC_CUDA(cudaMemsetAsync(sc.p, 0, bytes, s));
     }
     *out = sc.p;
     return B200FC_OK;
 }
 static int get_scratch(size_t bytes, cudaStream_t s, void** out) { return get_stream_scratch(bytes, s, 0, out); }
+
+// Scratch of the decode kernel (fixed size, counters zero between launches), one per (device, stream).  A stream that
+// first shows up while it is being captured into a CUDA graph cannot allocate (cudaMalloc is refused during capture),
+// so the first call on a device also sets aside a few spare buffers that such streams take over.
+static std::map<ScratchKey, void*> g_gemv_scratch;
+static std::map<int, std::vector<void*>> g_gemv_spare;
+constexpr int kGemvSpareBuffers = 8;
+
+int get_gemv_scratch(cudaStream_t s, void** out) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lk(g_mu);
+    const ScratchKey key{dev, s, 2};
+    auto it = g_gemv_scratch.find(key);
+    if (it != g_gemv_scratch.end()) { *out = it->second; return B200FC_OK; }
+    const size_t bytes = gemv_scratch_bytes();
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &cap) != cudaSuccess) { cudaGetLastError(); cap = cudaStreamCaptureStatusNone; }
+    std::vector<void*>& spare = g_gemv_spare[dev];
+    void* p = nullptr;
+    if (cap != cudaStreamCaptureStatusNone) {
+        if (spare.empty()) {
+            set_error("decode kernel: no scratch for this stream and none can be allocated while it is being captured; "
+                      "run one decode-shaped call on the device (any stream) before capturing");
+            return B200FC_ERR_UNSUPPORTED;
+        }
+        p = spare.back();
+        spare.pop_back();
+    } else {
+        const bool first_on_device = g_gemv_scratch.empty() && spare.empty();
+        B200FC_CUDA(cudaMalloc(&p, bytes));
+        B200FC_CUDA(cudaMemsetAsync(p, 0, bytes, s));
+        if (first_on_device || spare.size() < 2) {
+            // (re)fill the spare set; zeroed with a synchronous memset, whoever takes one over finds it ready
+            while ((int)spare.size() < kGemvSpareBuffers) {
+                void* q = nullptr;
+                if (cudaMalloc(&q, bytes) != cudaSuccess) { cudaGetLastError(); break; }
+                if (cudaMemset(q, 0, bytes) != cudaSuccess) { cudaGetLastError(); cudaFree(q); break; }
+                spare.push_back(q);
+            }
+        }
+    }
+    g_gemv_scratch[key] = p;
+    *out = p;
+    return B200FC_OK;
+}
 
 static int grow(void** p, size_t* have, size_t need, cudaStream_t s) {
     if (*have >= need) return B200FC_OK;
@@ -129,7 +174,7 @@ static int alloc_weight(Weight& w, int K, int N, int dtype) {
 
 static void free_weight(Weight* w) {
     if (!w) return;
-    cudaFree(w->data); cudaFree(w->scale_per_oc); cudaFree(w->dequant_bf16);
+    cudaFree(w->data); cudaFree(w->scale_per_oc);
     cudaFree(w->stage_A); cudaFree(w->stage_C); cudaFree(w->stage_vec);
 }
 
@@ -214,14 +259,35 @@ int matmul_device(const Weight& w, Weight* w_mut, const void* A, int dtypeA, int
         A_use = buf; lda_use = ld2;
     }
     if (w.compressed) {
-        // M > 16 with int8-compressed weights: widen the weights to bf16 once (exact) and run the bf16 GEMM
-        if (!w.dequant_bf16) {
-            if (!w_mut) { set_error("internal: compressed weight without a mutable handle"); return B200FC_ERR_INVALID; }
-            B200FC_CUDA(cudaMalloc(&w_mut->dequant_bf16, (size_t)w.N_pad * w.K_pad * 2));
-            rc = launch_dequant_bf16(w, w_mut->dequant_bf16, w.K_pad, s);
+        // M > 16 with int8-compressed weights.  The reference decompresses 16 weight rows at a time into a reused
+        // buffer right before the tile product (kernels_amx.hpp:1443-1514); here a block of weight rows is widened to
+        // bf16 (exact) into a per-stream scratch of at most 32 MB — small enough to stay in the 126 MB L2 until the
+        // GEMM over those rows, launched right behind it, has read it — so HBM sees the int8 bytes only and no second
+        // copy of the matrix is kept.
+        (void)w_mut;
+        const size_t row_bytes = (size_t)w.K_pad * 2;
+        int blk = (int)(((size_t)32 << 20) / row_bytes) / kRowPad * kRowPad;
+        if (blk < kRowPad) blk = kRowPad;
+        const int r_lo = n0 / kRowPad * kRowPad;                  // packed rows are padded to kRowPad
+        void* wide = nullptr;
+        rc = get_stream_scratch((size_t)blk * row_bytes, s, 3, &wide);
+        if (rc) return rc;
+        for (int r0 = r_lo; r0 < n1; r0 += blk) {
+            const int rows = (w.N_pad - r0 < blk) ? (w.N_pad - r0) : blk;
+            const int c0 = r0 > n0 ? r0 : n0, c1 = (r0 + rows < n1) ? (r0 + rows) : n1;
+            rc = launch_dequant_bf16(w, r0, rows, wide, w.K_pad, s);
+            if (rc) return rc;
+            // the block is addressed as a weight matrix whose row 0 is packed row r0: shift the column range and the
+            // per-column arrays of the epilogue accordingly
+            Epilogue e2 = ep;
+            e2.C = (char*)ep.C + (long long)r0 * (ep.out_dtype == B200FC_F32 ? 4 : (ep.out_dtype == B200FC_BF16 ? 2 : 1));
+            if (e2.bias) e2.bias += r0;
+            if (e2.deq_per_oc) e2.deq_per_oc += r0;
+            if (e2.q_per_oc) e2.q_per_oc += r0;
+            rc = launch_gemm_tc(wide, B200FC_BF16, w.K_pad, rows, A_use, B200FC_BF16, M, K, lda_use, c0 - r0, c1 - r0, e2, s);
             if (rc) return rc;
         }
-        return launch_gemm_tc(w.dequant_bf16, B200FC_BF16, w.K_pad, w.N_pad, A_use, B200FC_BF16, M, K, lda_use, n0, n1, ep, s);
+        return B200FC_OK;
     }
     return launch_gemm_tc(w.data, w.dtype, w.K_pad, w.N_pad, A_use, dtypeA, M, K, lda_use, n0, n1, ep, s);
 }
@@ -480,7 +546,7 @@ int b200fc_weight_import(const void* host_src, size_t bytes, b200fc_weight_t** o
 int b200fc_matmul(const b200fc_weight_t* W, const void* A, int dtypeA, int M, int K, int64_t lda_bytes, int n0, int n1,
                   const b200fc_epilogue_t* ep, void* stream) {
     if (!W || !A) { set_error("matmul: null pointer"); return B200FC_ERR_INVALID; }
-    return matmul_device(W->w, const_cast<Weight*>(&W->w), A, dtypeA, M, K, lda_bytes, n0, n1, ep, (cudaStream_t)stream);
+    return matmul_device(W->w, nullptr, A, dtypeA, M, K, lda_bytes, n0, n1, ep, (cudaStream_t)stream);
 }
 
 int b200fc_matmul_host(b200fc_weight_t* W, const void* A, int dtypeA, int M, int K, int64_t lda, int n0, int n1,

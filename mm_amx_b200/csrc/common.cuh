@@ -27,7 +27,6 @@ struct Weight {
     void* data = nullptr;           // [N_pad, K_pad]
     float* scale_per_oc = nullptr;  // optional [N_pad] per-output-channel dequant scales
     // lazily created scratch / staging owned by the object
-    void* dequant_bf16 = nullptr;   // [N_pad, K_pad64] bf16 copy of compressed weights for the tensor-core path
     void* stage_A = nullptr; size_t stage_A_bytes = 0;
     void* stage_C = nullptr; size_t stage_C_bytes = 0;
     float* stage_vec = nullptr; size_t stage_vec_floats = 0;
@@ -87,9 +86,10 @@ void count_launch(int n = 1);
 int* kernel_status_word();  // device int, 0 = OK; kernels store a non-zero code when a bounded wait runs out
 int check_kernel_status(cudaStream_t s);  // synchronises and reads it
 // growing device scratch owned by (device, stream, slot): work on one stream is ordered, so kernels launched on it
-// may share it; slot 0 = re-strided activations, slot 1 = split-K partial tiles of the GEMM, slot 2 = counters and
-// partial sums of the decode kernel (fixed size), slot 3 = fused-MLP activation.  A fresh allocation is zero-filled.
+// may share it; slot 0 = re-strided activations, slot 1 = split-K partial tiles of the GEMM
 int get_stream_scratch(size_t bytes, cudaStream_t s, int slot, void** out);
+// the decode kernel's scratch for stream s (gemv_scratch_bytes(), counters zero); never re-allocated once handed out
+int get_gemv_scratch(cudaStream_t s, void** out);
 // time limit of every bounded device-side wait (b200fc_set_wait_limit_ns; 2 s unless changed)
 unsigned long long wait_limit_ns();
 
@@ -99,8 +99,7 @@ unsigned long long wait_limit_ns();
         if (e__ != cudaSuccess) return ::b200fc::cuda_fail(e__, #call);     \
     } while (0)
 
-// api.cu: validated dispatch of one Matmul call on device pointers (w_mut: the same object when the call may create
-// its lazily built bf16 copy of compressed weights, else null)
+// api.cu: validated dispatch of one Matmul call on device pointers (w_mut is unused and kept for call-site symmetry)
 // gemv_scratch: counters + partial-sum slots for the decode kernel (gemv_scratch_bytes(), counters zero), or null to
 // use the stream's own
 int matmul_device(const Weight& w, Weight* w_mut, const void* A, int dtypeA, int M, int K, int64_t lda, int n0, int n1,
@@ -115,7 +114,7 @@ int launch_pack_gate_up(const void* gate, const void* up, int64_t ld_bytes, int 
 int launch_quant_pack(const void* B_dev, int K, int N, int64_t ldb, int transposeB, Weight& w, float* absmax_dev,
                       cudaStream_t s);
 int launch_absmax(const void* B_dev, int rows, int cols, int64_t ldb, float* absmax_dev, cudaStream_t s);
-int launch_dequant_bf16(const Weight& w, void* dst_bf16, int dst_K_pad, cudaStream_t s);
+int launch_dequant_bf16(const Weight& w, int row0, int rows, void* dst_bf16, int dst_K_pad, cudaStream_t s);
 int launch_copy2d(const void* src, int64_t lds, void* dst, int64_t ldd, int rows, int row_bytes, int dst_row_bytes,
                   cudaStream_t s);
 int launch_add_round_bf16(const float* a, const float* b, void* out, int64_t n, cudaStream_t s);

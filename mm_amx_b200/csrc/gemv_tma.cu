@@ -134,6 +134,12 @@ __device__ __forceinline__ float ld_peer_f32(unsigned addr, unsigned rank) {
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
     return v;
 }
+// strong (coherent at GPU scope) 16-byte load: partial sums written by other SMs during this launch
+__device__ __forceinline__ float4 ld_gpu_f4(const float4* p) {
+    float4 v;
+    asm volatile("ld.relaxed.gpu.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CTHREADS) : "memory"); }
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
@@ -443,8 +449,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
 #pragma unroll
                     for (int h = 0; h < 2; h++)
                         w[rb][h] = *(const uint4*)(sbase + (row_base + rb * 16 + h * 8) * STAGE_K_BYTES + (((2 * t + kh) ^ g) << 4));
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_empty + 8 * stage);
+                const int rel_stage = stage;
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
 
                 const int j = kh;
@@ -482,6 +487,11 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
                         }
                     }
                 }
+                // Release the stage only now that its bytes have gone through the MMAs.  Arriving right after the copies to
+                // registers had been issued (or even after folding them into a dummy value) let the refill overtake them
+                // now and then: single rows of a warp's share then held bytes of the stage four positions later.
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_empty + 8 * rel_stage);
             }
             it += ks1 - ks0;
             if (threadIdx.x == 0 && it == it_end) TRACE_STAMP(3);   // last stage multiplied
@@ -536,6 +546,9 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
                     const float4 a = ((const float4*)part)[v], b = ((const float4*)(part + PART_HALF))[v];
                     slot[v] = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
                 }
+                // every writer fences its own stores: a release by thread 0 alone (after the barrier) was observed NOT to
+                // cover the other warps' stores — now and then a reader summed a slot before all of it had arrived
+                __threadfence();
                 consumer_sync();
                 const long long s_first = (long long)rbk * p.spr;
                 c_first = piece_of(p, G, s_first);
@@ -556,6 +569,8 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
                     // Sum the slots of the CTAs that share the row block, in CTA order, into part[token][row].  Only the
                     // first of them can hold the row block as the piece that CLOSES its range (slot 1); for all others it
                     // opens their range (slot 0).  Eight slots are read at a time so that the L2 round trips overlap.
+                    // every reader fences too: thread 0's acquire alone does not cover the other warps' loads
+                    __threadfence();
                     const int which_first = piece_begin(p, G, c_first) < s_first ? 1 : 0;
                     const float4* base = (const float4*)p.slots;
                     for (int v = ctid; v < nvec; v += CTHREADS) {
@@ -566,7 +581,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
                             for (int u = 0; u < 8; u++) {
                                 const int cc = c + u;
                                 const int which = cc == c_first ? which_first : 0;
-                                t4[u] = cc <= c_last ? __ldcg(base + (size_t)(2 * cc + which) * (SLOT_FLOATS / 4) + v)
+                                t4[u] = cc <= c_last ? ld_gpu_f4(base + (size_t)(2 * cc + which) * (SLOT_FLOATS / 4) + v)
                                                      : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                             }
 #pragma unroll
@@ -738,7 +753,7 @@ int launch_gemv_tma(const Weight& w, const void* A, int M, int K, int64_t lda, i
     p.status = kernel_status_word();
     if (!p.status) { set_error("gemv: no kernel status word on this device"); return B200FC_ERR_CUDA; }
     p.wait_limit_ns = wait_limit_ns();
-    static int pf_cap = -1, per_sm = 0, force_stream = 0;   // environment switches, for experiments
+    static int pf_cap = -1, per_sm = 0, force_stream = 0, force_aligned = 0;   // environment switches, for experiments
     if (pf_cap < 0) {
         const char* e = getenv("B200FC_GEMV_PREFETCH");      // stages prefetched into L2 at CTA start (0 = none)
         pf_cap = e ? atoi(e) : 0;
@@ -748,6 +763,7 @@ int launch_gemv_tma(const Weight& w, const void* A, int M, int K, int64_t lda, i
         per_sm = (e && atoi(e) == 1) ? 1 : 2;
         e = getenv("B200FC_GEMV_STREAMK");                   // 1: never align pieces with row blocks
         force_stream = (e && atoi(e) == 1) ? 1 : 0;
+        force_aligned = (e && atoi(e) == 2) ? 1 : 0;         // 2: align whenever the row blocks fit the grid
     }
     p.pf_cap = pf_cap;
     int sms = device_sms();
@@ -770,7 +786,7 @@ int launch_gemv_tma(const Weight& w, const void* A, int M, int K, int64_t lda, i
         if (S > p.spr / 2) S = p.spr / 2;
         if (S < 1) S = 1;
         const long long cost = (p.spr + S - 1) / S + (S > 1 ? 1 : 0);
-        if (cost <= best) { best = cost; p.S = S; p.cluster = S > 1 ? 1 : 0; grid = (long long)row_blocks * S; }
+        if (cost <= best || force_aligned) { best = cost; p.S = S; p.cluster = S > 1 ? 1 : 0; grid = (long long)row_blocks * S; }
     }
 #ifdef B200FC_TRACE
     {
@@ -785,7 +801,7 @@ int launch_gemv_tma(const Weight& w, const void* A, int M, int K, int64_t lda, i
     }
 #endif
     if (!scratch) {
-        int rc = get_stream_scratch(gemv_scratch_bytes(), s, 2, &scratch);
+        int rc = get_gemv_scratch(s, &scratch);
         if (rc) return rc;
     }
     p.counters = (unsigned*)scratch;

@@ -194,12 +194,13 @@ int launch_quant_pack(const void* B, int K, int N, int64_t ldb, int transposeB, 
     return B200FC_OK;
 }
 
-int launch_dequant_bf16(const Weight& w, void* dst, int dst_K_pad, cudaStream_t s) {
-    long long total16 = (long long)w.N_pad * (w.K_pad / 16);
+int launch_dequant_bf16(const Weight& w, int row0, int rows, void* dst, int dst_K_pad, cudaStream_t s) {
+    // rows [row0, row0 + rows) of the packed matrix -> dst rows [0, rows)
+    long long total16 = (long long)rows * (w.K_pad / 16);
     int block = 256;
     long long grid = (total16 + block - 1) / block;
-    dequant_bf16_kernel<<<(unsigned)grid, block, 0, s>>>((const signed char*)w.data, w.K_pad, total16,
-                                                         (unsigned short*)dst, dst_K_pad);
+    dequant_bf16_kernel<<<(unsigned)grid, block, 0, s>>>((const signed char*)w.data + (size_t)row0 * w.K_pad, w.K_pad,
+                                                         total16, (unsigned short*)dst, dst_K_pad);
     count_launch();
     B200FC_CUDA(cudaGetLastError());
     return B200FC_OK;

@@ -93,3 +93,11 @@ def test_argument_checks_need_no_gpu():
     assert rc == capi.ERR_INVALID
     with pytest.raises(capi.B200FCError):
         capi.check(rc)
+
+
+def test_reference_module_name_is_importable():
+    """a script written against the reference's extension does `import amx_mlp` (torch-ext/setup.py:10-13)"""
+    import importlib
+    m = importlib.import_module("amx_mlp")
+    from mm_amx_b200 import amx_mlp as inner
+    assert m.LinearNxN is inner.LinearNxN and m.MLP is inner.MLP and m.clflush is inner.clflush

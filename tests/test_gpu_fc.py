@@ -64,6 +64,87 @@ def test_compressed_two_valued_exact(M, K, N):
     assert np.array_equal(got, ref)
 
 
+@pytest.mark.parametrize("K,N,transposeB", [(256, 320, False), (1000, 77, True), (4096, 512, True)])
+def test_weight_quantiser_bit_exact_on_normal_data(K, N, transposeB):
+    """The quantised bytes are integer work: on N(0, 0.02) data (ties, all 255 levels in use) the GPU quantiser must
+    produce the bytes and the scale of the reference's get_min_max + bf16_to_i8_tensor (kernels_amx.hpp:465-523)."""
+    rng = np.random.default_rng(K * 7 + N)
+    B = H.normal_bf16(rng, (N, K) if transposeB else (K, N), 0.02)
+    Wq, qs, dq = port.quantize_weight(B)
+    w = H.pack(B, transposeB, capi.PACK_QUANT_TENSOR)
+    assert w.info()["deq_scale"] == np.float32(dq)
+    unp = H.Dev(shape=(N, K), dtype=np.int8)
+    w.unpack(unp.ptr, K)
+    want = Wq if transposeB else Wq.T
+    assert len(np.unique(want)) > 100          # the case really exercises the rounding, unlike two-valued data
+    assert np.array_equal(unp.numpy(), want)
+
+
+@pytest.mark.parametrize("M,K,N,n0,n1", [(40, 256, 1024, 0, 1024), (130, 8192, 2600, 0, 2600), (64, 8192, 2600, 512, 2304)])
+def test_compressed_weights_prefill_blocks(M, K, N, n0, n1):
+    """M > 16 with int8-compressed weights: blocks of weight rows are widened into a scratch and multiplied block by
+    block (K = 8192 makes a block 2048 rows, so N = 2600 takes two); per-channel scales, bias and a column range."""
+    rng = np.random.default_rng(M + K + N + n0)
+    A = H.normal_bf16(rng, (M, K))
+    Wq = rng.integers(-127, 128, (N, K), dtype=np.int8)
+    scale = rng.uniform(0.001, 0.02, N).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    w = H.pack(Wq, True, capi.PACK_INT8_CHANNEL, scales=scale)
+    got = H.run_matmul(w, A, capi.F32, steps=capi.STEP_DEQUANT | capi.STEP_BIAS, bias=bias, n0=n0, n1=n1)
+    ref = port.postops(port.gemm_bf16_w8(A, np.ascontiguousarray(Wq.T)), port.DEQUANT | port.BIAS, port.F32, bias=bias,
+                       deq_scale_per_oc=scale)
+    assert H.rel_to_max(got[:, n0:n1], ref[:, n0:n1]) < 1e-5
+    sentinel = np.frombuffer(b"\xcd\xcd\xcd\xcd", np.float32)[0]
+    if n0 > 0:
+        assert (got[:, :n0].view(np.uint32) == sentinel.view(np.uint32)).all()
+    if n1 < N:
+        assert (got[:, n1:].view(np.uint32) == sentinel.view(np.uint32)).all()
+
+
+def test_bounded_wait_runs_out_and_the_library_recovers(monkeypatch):
+    """A device-side wait that nothing will satisfy gives up after the configured limit, the kernel ends cleanly, the
+    host sees B200FC_ERR_KERNEL once, and the next ordinary call works.  The wait is the reduce role of the fused
+    all-reduce kernel waiting for arrivals of a second rank that does not exist: its counters stay zero, and a CTA that
+    gives up leaves before it touches any multicast address (none exists here either)."""
+    import torch
+    rng = np.random.default_rng(5)
+    K, N, M = 256, 512, 300
+    gate, up = H.normal_bf16(rng, (N, K), 0.02), H.normal_bf16(rng, (N, K), 0.02)
+    down = H.normal_bf16(rng, (K, N), 0.02)
+    mlp = capi.Mlp(gate.ctypes.data, up.ctypes.data, down.ctypes.data, K, N)
+    x = H.Dev(H.normal_bf16(rng, (M, K)))
+    out = H.Dev(shape=(M, K), dtype=np.uint16)
+    mlp.run(x.ptr, x.ld, M, out.ptr, out.ld)
+    capi.sync_check()
+    good = out.numpy()
+    partial = torch.zeros((M, K), dtype=torch.bfloat16, device="cuda")
+    result = torch.zeros((M, K), dtype=torch.bfloat16, device="cuda")
+    flags = torch.zeros(4096, dtype=torch.int32, device="cuda")
+    ar = capi.AllReduce()
+    ar.world, ar.rank = 2, 0
+    ar.partial_local, ar.partial_mc, ar.out_mc = partial.data_ptr(), partial.data_ptr(), result.data_ptr()
+    ar.ld_bytes = K * 2
+    ar.flags[0] = flags.data_ptr(); ar.flags[1] = flags.data_ptr()
+    ar.max_tiles, ar.comm_sms = 4096, 8
+    monkeypatch.setenv("B200FC_AR_PHASES", "2")      # reduce role only: nobody multiplies, nobody signals
+    capi.set_wait_limit_ns(3_000_000)                # 3 ms
+    try:
+        mlp.gate_up(x.ptr, x.ld, M)
+        mlp.down_allreduce(M, ar)
+        with pytest.raises(capi.B200FCError) as e:
+            capi.sync_check()
+        assert e.value.code == capi.ERR_KERNEL
+    finally:
+        capi.set_wait_limit_ns(2_000_000_000)
+        monkeypatch.delenv("B200FC_AR_PHASES")
+    capi.sync_check()                                # the status word was cleared by the failing check
+    assert not result.any()                          # the reduce role left before it wrote anything
+    out2 = H.Dev(shape=(M, K), dtype=np.uint16)
+    mlp.run(x.ptr, x.ld, M, out2.ptr, out2.ld)
+    capi.sync_check()
+    assert np.array_equal(out2.numpy(), good)
+
+
 @pytest.mark.parametrize("M", [1, 2, 3, 8, 9, 16, 17, 64, 200])
 def test_bf16_random_tolerance(M):
     """uniform[-1,1] data: fp32 accumulation order differs from the oracle's, so compare within 1e-2 of max|ref|

@@ -10,6 +10,7 @@ fp64 matmuls, not this library) and through properties that do not depend on the
     bit for bit.
 The reference builders are plain functions of torch tensors so that a CPU test can run them on tiny shapes.
 """
+import numpy as np
 import pytest
 import torch
 
@@ -101,6 +102,63 @@ def test_config4_int8_2048x4096x4096_exact():
     capi.sync_check()
     ref = (A.double() @ B.double().T).to(torch.int64)      # exact: |acc| <= 2^26
     assert torch.equal(C.to(torch.int64), ref)
+
+
+@pytest.mark.gpu
+def test_config4_int8_2048x4096x4096_quantised_postops():
+    """dequantise by sA * sB[n], add bias -> fp32; then requantise to int8 with a q_scale that saturates about 1 % of the
+    outputs (round to nearest even + saturation, kernels_amx.hpp:631-664).  Reference: the exact int32 accumulators (fp64
+    product) pushed through the same fp32 steps in torch."""
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev); g.manual_seed(2004)
+    M, K, N = 2048, 4096, 4096
+    A = torch.randint(-128, 128, (M, K), generator=g, device=dev, dtype=torch.int8)
+    B = torch.randint(-128, 128, (N, K), generator=g, device=dev, dtype=torch.int8)
+    sA = 0.013
+    sB = torch.rand(N, generator=g, device=dev) * 0.049 + 0.001
+    bias = torch.randn(N, generator=g, device=dev)
+    w = capi.Weight(B.data_ptr(), capi.S8, K, N, K, True)
+    acc = (A.double() @ B.double().T).to(torch.int32)
+    ref_f = (acc.float() * (np.float32(sA) * sB)[None, :]) + bias[None, :]
+    Cf = torch.empty((M, N), dtype=torch.float32, device=dev)
+    ep = capi.make_epilogue(Cf.data_ptr(), N * 4, capi.F32, capi.STEP_DEQUANT | capi.STEP_BIAS, bias.data_ptr(), sA,
+                            sB.data_ptr())
+    w.matmul(A.data_ptr(), capi.S8, M, K, K, ep)
+    capi.sync_check()
+    # same fp32 operations in the same order; only the fused multiply-add contraction of `* scale + bias` may differ
+    assert rel_to_max(Cf, ref_f) < 1e-6
+    q = float(127.0 / (2.576 * ref_f.std().item()))          # |z| > 2.576 sigma: about 1 % of a normal distribution
+    C8 = torch.empty((M, N), dtype=torch.int8, device=dev)
+    ep8 = capi.make_epilogue(C8.data_ptr(), N, capi.S8, capi.STEP_DEQUANT | capi.STEP_BIAS | capi.STEP_QUANT,
+                             bias.data_ptr(), sA, sB.data_ptr(), q)
+    w.matmul(A.data_ptr(), capi.S8, M, K, K, ep8)
+    capi.sync_check()
+    ref8 = torch.clamp(torch.round(Cf * np.float32(q)), -128, 127).to(torch.int8)     # torch.round: half to even
+    sat = float(((ref8 == 127) | (ref8 == -128)).float().mean().item())
+    assert 0.002 < sat < 0.05, sat
+    assert torch.equal(C8, ref8)
+
+
+@pytest.mark.gpu
+def test_config5_llama70b_mlp_whole_on_one_gpu():
+    """tensor-parallel size 1, M = 4096: the shape the scaling run starts from.  Rows 0..63 against torch fp32 on the
+    GPU; the decode kernel (M = 1, 16) and the GEMM path must agree on the rows they share."""
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev); g.manual_seed(3005)
+    H, I, M = 8192, 28672, 4096
+    gate, up, down = randn_bf16((I, H), 0.02, g, dev), randn_bf16((I, H), 0.02, g, dev), randn_bf16((H, I), 0.02, g, dev)
+    x = randn_bf16((M, H), 1.0, g, dev)
+    mlp = capi.Mlp(gate.data_ptr(), up.data_ptr(), down.data_ptr(), H, I)
+    out = torch.empty((M, H), dtype=torch.bfloat16, device=dev)
+    mlp.run(x.data_ptr(), H * 2, M, out.data_ptr(), H * 2)
+    capi.sync_check()
+    for r0 in (0, M - 64):
+        assert rel_to_max(out[r0:r0 + 64], mlp_reference(x[r0:r0 + 64], gate, up, down)) < BAR
+    for Md in (1, 16, 128):
+        o = torch.empty((Md, H), dtype=torch.bfloat16, device=dev)
+        mlp.run(x.data_ptr(), H * 2, Md, o.data_ptr(), H * 2)
+        capi.sync_check()
+        assert rel_to_max(o, out[:Md]) < BAR
 
 
 @pytest.mark.gpu
