@@ -90,6 +90,7 @@ int get_stream_scratch(size_t bytes, cudaStream_t s, int slot, void** out) {
     *out = sc.p;
     return B200FC_OK;
 }
+
 static int get_scratch(size_t bytes, cudaStream_t s, void** out) { return get_stream_scratch(bytes, s, 0, out); }
 
 // Scratch of the decode kernel (fixed size, counters zero between launches), one per (device, stream).  A stream that

@@ -35,13 +35,17 @@ constexpr int EPI_WARP0 = 2;
 #endif
 constexpr int EPI_SLEEP_NS = B200FC_EPI_SLEEP_NS;
 
+// staging tiles of the four epilogue warps: 32 rows x 32 four-byte columns each, rows padded to 33 words
+constexpr int EPI_TILE_WORDS = 32 * 33;
+constexpr int EPI_TILE_BYTES = 4 * EPI_TILE_WORDS * 4;
+
 template <int BN> struct Cfg {
     static constexpr int STAGES = BN == 256 ? 4 : 6;
     static constexpr int A_BYTES = BM * SLAB_BYTES;
     static constexpr int B_BYTES = BN * SLAB_BYTES;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + EPI_TILE_BYTES;
 };
 
 struct GemmParams {
@@ -169,10 +173,41 @@ __device__ __forceinline__ unsigned long long make_smem_desc(unsigned smem_addr)
 }
 
 // ---- epilogue on 32 consecutive columns of one output row ------------------------------------------------------------
-__device__ __forceinline__ void epilogue_chunk(const unsigned (&r)[32], int m, int n, const GemmParams& p, bool row_ok,
+struct EpiArgs {       // what the epilogue of one 32-column chunk needs to know
+    const Epilogue* ep;
+    int vec_ok, acc_is_int, n1;
+    int M;             // rows of the output
+    unsigned* tile;    // this warp's staging tile in shared memory (EPI_TILE_WORDS words)
+};
+// 32 rows x 32 four-byte values, one row per lane in registers -> global memory with full-line stores: the tile goes
+// through shared memory and comes back with eight lanes per row (16 bytes each), so that one store instruction writes
+// four whole 128-byte row segments instead of 32 scattered 16-byte pieces.  Called by all lanes of the warp.
+__device__ __forceinline__ void store_tile_4b(const unsigned (&val)[32], unsigned* tile, char* C, long long ldc, int m, int n,
+                                              int M) {
+    const int lane = threadIdx.x & 31, m0 = m - lane;
+#pragma unroll
+    for (int j = 0; j < 32; j++) tile[lane * 33 + j] = val[j];
+    __syncwarp();
+    const int c = (lane & 7) * 4;
+#pragma unroll
+    for (int it = 0; it < 8; it++) {
+        const int rr = it * 4 + (lane >> 3);
+        const unsigned* t = tile + rr * 33 + c;
+        const uint4 q = make_uint4(t[0], t[1], t[2], t[3]);
+        if (m0 + rr < M) *(uint4*)(C + (long long)(m0 + rr) * ldc + (long long)(n + c) * 4) = q;
+    }
+    __syncwarp();
+}
+__device__ __forceinline__ void epilogue_chunk(const unsigned (&r)[32], int m, int n, const EpiArgs p, bool row_ok,
                                                long long c_offset = 0) {
-    const Epilogue& ep = p.ep;
-    if (!row_ok) return;
+    const Epilogue& ep = *p.ep;
+    const bool staged = p.vec_ok && n + 32 <= p.n1 && !ep.mc_reduce;   // warp-uniform
+    if (ep.out_dtype == B200FC_S32 && staged) {
+        store_tile_4b(r, p.tile, (char*)ep.C + c_offset, ep.ldc, m, n, p.M);
+        return;
+    }
+    const bool staged_f32 = ep.out_dtype == B200FC_F32 && staged && !(ep.steps & B200FC_STEP_SILU_MUL);   // warp-uniform
+    if (!row_ok && !staged_f32) return;   // (rows beyond M take part in the staged store's shuffle through shared memory)
     char* crow = (char*)ep.C + c_offset + (long long)m * ep.ldc;
     if (ep.out_dtype == B200FC_S32) {  // raw accumulators
         if (p.vec_ok && n + 32 <= p.n1) {
@@ -275,7 +310,12 @@ __device__ __forceinline__ void epilogue_chunk(const unsigned (&r)[32], int m, i
         }
     }
     const bool full = p.vec_ok && n + 32 <= p.n1;
-    if (ep.out_dtype == B200FC_F32) {
+    if (staged_f32) {
+        unsigned u[32];
+#pragma unroll
+        for (int j = 0; j < 32; j++) u[j] = __float_as_uint(v[j]);
+        store_tile_4b(u, p.tile, (char*)ep.C + c_offset, ep.ldc, m, n, p.M);
+    } else if (ep.out_dtype == B200FC_F32) {
         if (full) {
             float4* dst = (float4*)(crow + (long long)n * 4);
 #pragma unroll
@@ -419,6 +459,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else {
         // ---------------- epilogue warps ----------------
         const int quarter = warp & 3;  // TMEM lanes this warp may read: [32*quarter, 32*quarter + 32)
+        unsigned* epi_tile = (unsigned*)(smem + C::STAGES * C::STAGE_BYTES + 256) + quarter * EPI_TILE_WORDS;
         int it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, it++) {
@@ -437,7 +478,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 unsigned r[32];
                 tc_ld32(taddr + (unsigned)(c * 32), r);
                 tc_wait_ld();
-                epilogue_chunk(r, m, n, p, row_ok);
+                epilogue_chunk(r, m, n, EpiArgs{&p.ep, p.vec_ok, p.acc_is_int, p.n1, p.M, epi_tile}, row_ok);
             }
             tc_fence_before();
             __syncwarp();
@@ -483,7 +524,7 @@ template <int BN> struct Cfg2 {
     static constexpr int B_BYTES = (BN / 2) * SLAB_BYTES;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + EPI_TILE_BYTES;
 };
 
 __device__ __forceinline__ unsigned cluster_ctarank() {
@@ -650,6 +691,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     __syncthreads();
     cluster_sync_all();  // both CTAs' barriers exist before anyone signals them
     tc_fence_after();
+    // a kernel launched as a programmatic dependent (the split-K reduction) may become resident from here on
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const unsigned tmem_base = *tmem_holder;
 
     if (comm_role) {
@@ -716,6 +759,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     } else {
         // ---------------- epilogue warps (both CTAs, own 128 rows) ----------------
         const int quarter = warp & 3;
+        unsigned* epi_tile = (unsigned*)(smem + C::STAGES * C::STAGE_BYTES + 256) + quarter * EPI_TILE_WORDS;
         int it = 0;
         bool ok = true;
         const unsigned leader_acc_empty = mapa_rank(bar_acc_empty, 0);
@@ -737,7 +781,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 unsigned r[32];
                 tc_ld32(taddr + (unsigned)(c * 32), r);
                 tc_wait_ld();
-                epilogue_chunk(r, m, n, p, row_ok, c_offset);
+                epilogue_chunk(r, m, n, EpiArgs{&p.ep, p.vec_ok, p.acc_is_int, p.n1, p.M, epi_tile}, row_ok, c_offset);
             }
             tc_fence_before();
             if (p.ar_world) __threadfence_system();  // this warp's part of the tile is visible to every GPU ...
@@ -784,6 +828,8 @@ __global__ void splitk_reduce_kernel(const unsigned* __restrict__ ws, long long 
     const bool silu = (ep.steps & B200FC_STEP_SILU_MUL) != 0;
     const int cols = silu ? (n1 - n0) / 2 : (n1 - n0);
     const long long total = (long long)M * cols;
+    // launched as a programmatic dependent of the GEMM: resident early, waits here for the slabs
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int m = (int)(i / cols), c = (int)(i % cols);
         const unsigned* row = ws + (long long)m * pitch;
@@ -946,11 +992,20 @@ int launch_cfg2(const CUtensorMap& ma, const CUtensorMap& mw, GemmParams p, cuda
         const long long total = (long long)p.M * (p.n1 - p.n0);
         long long blocks = (total + 255) / 256;
         if (blocks > 148 * 8) blocks = 148 * 8;
-        splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, s>>>((const unsigned*)((char*)p.ep.C + (long long)p.n0 * 4),
-                                                             (long long)p.M * pitch, pitch, splits, p.M, p.n0, p.n1,
-                                                             p.acc_is_int, final_ep);
+        // programmatic dependent launch: the reduction's blocks become resident while the GEMM drains (the GEMM
+        // triggers its dependents at its start) and wait inside the kernel, which hides the launch latency
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)blocks, 1, 1);
+        cfg.blockDim = dim3(256, 1, 1);
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        B200FC_CUDA(cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, (const unsigned*)((char*)p.ep.C + (long long)p.n0 * 4),
+                                       (long long)p.M * pitch, pitch, splits, p.M, p.n0, p.n1, p.acc_is_int, final_ep));
         count_launch();
-        B200FC_CUDA(cudaGetLastError());
     }
     (void)final_vec;
     return B200FC_OK;
