@@ -625,18 +625,29 @@ def decode_legs(torch, mlp, x, w, peaks):
     return res
 
 
-def other_configs(torch, capi, dev, peaks):
+def other_configs(torch, capi, dev, peaks, only=None):
     """Single bf16 Linear (M=256, +bias, fp32 out), int8-weight decode GEMV (K=4096, N in {4096, 11008}, M in
     {1, 4, 16}), int8 GEMM 2048x4096x4096 with quantised post-ops.  Each case rotates over enough independently packed
-    weight sets to exceed L2 several times and is timed as one CUDA graph (kernels of a few microseconds)."""
+    weight sets to exceed L2 several times and is timed as one CUDA graph (kernels of a few microseconds).
+    `only` (--case): run just the case of that name, with plain launches (no graph) — the form a profiler is pointed at."""
     out = {}
     side = torch.cuda.Stream()
     g = torch.Generator(device=dev); g.manual_seed(1002)
+
+    def want(key):
+        return only is None or key == only
 
     def timed_graph(launch_all, n_launch, reps=5):
         with torch.cuda.stream(side):
             s = side.cuda_stream
             launch_all(s); side.synchronize()
+            if only is not None:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(2):
+                    launch_all(s)
+                e1.record(); side.synchronize()
+                return e0.elapsed_time(e1) * 1e-3 / 2 / n_launch
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=side):
                 launch_all(torch.cuda.current_stream().cuda_stream)
@@ -650,30 +661,35 @@ def other_configs(torch, capi, dev, peaks):
 
     # config 1: A[256,4096] x B[4096,4096] + bias -> fp32
     M, K, N = 256, 4096, 4096
-    A = (torch.rand((M, K), generator=g, device=dev) * 2 - 1).to(torch.bfloat16)
-    bias = torch.randn(N, generator=g, device=dev)
-    C = torch.empty((M, N), dtype=torch.float32, device=dev)
-    ws = []
-    for _ in range(16):
-        B = (torch.rand((K, N), generator=g, device=dev) * 2 - 1).to(torch.bfloat16)
-        ws.append(capi.Weight(B.data_ptr(), capi.BF16, K, N, N * 2, False)); del B
-    ep = capi.make_epilogue(C.data_ptr(), N * 4, capi.F32, capi.STEP_BIAS, bias.data_ptr())
-    t = timed_graph(lambda s: [w.matmul(A.data_ptr(), capi.BF16, M, K, K * 2, ep, stream=s) for w in ws], len(ws))
-    nbytes = M * K * 2 + K * N * 2 + M * N * 4 + N * 4
-    out["bf16_linear_256x4096x4096_bias_f32"] = {"us": t * 1e6, "tflops": 2.0 * M * K * N / t / 1e12,
-                                                   "gbs": nbytes / t / 1e9, "hbm_frac": nbytes / t / 1e9 / peaks["hbm_gbs"],
-                                                   "weight_sets": len(ws)}
-    del ws
+    if want("bf16_linear_256x4096x4096_bias_f32"):
+        A = (torch.rand((M, K), generator=g, device=dev) * 2 - 1).to(torch.bfloat16)
+        bias = torch.randn(N, generator=g, device=dev)
+        C = torch.empty((M, N), dtype=torch.float32, device=dev)
+        ws = []
+        for _ in range(16 if only is None else 4):
+            B = (torch.rand((K, N), generator=g, device=dev) * 2 - 1).to(torch.bfloat16)
+            ws.append(capi.Weight(B.data_ptr(), capi.BF16, K, N, N * 2, False)); del B
+        ep = capi.make_epilogue(C.data_ptr(), N * 4, capi.F32, capi.STEP_BIAS, bias.data_ptr())
+        t = timed_graph(lambda s: [w.matmul(A.data_ptr(), capi.BF16, M, K, K * 2, ep, stream=s) for w in ws], len(ws))
+        nbytes = M * K * 2 + K * N * 2 + M * N * 4 + N * 4
+        out["bf16_linear_256x4096x4096_bias_f32"] = {"us": t * 1e6, "tflops": 2.0 * M * K * N / t / 1e12,
+                                                       "gbs": nbytes / t / 1e9, "hbm_frac": nbytes / t / 1e9 / peaks["hbm_gbs"],
+                                                       "weight_sets": len(ws)}
+        del ws
     # config 3: int8-weight decode GEMV
     K = 4096
     for N in (4096, 11008):
-        nset = int(600e6 / (K * N)) + 1
+        if not any(want("int8w_gemv_M%d_4096x%d" % (M, N)) for M in (1, 4, 16)):
+            continue
+        nset = int(600e6 / (K * N)) + 1 if only is None else 4
         ws, keep = [], []
         for _ in range(nset):
             B = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev, generator=g)
             sc = torch.rand(N, generator=g, device=dev) * 0.019 + 0.001
             ws.append(capi.Weight(B.data_ptr(), capi.S8, K, N, K, True, capi.PACK_INT8_CHANNEL, sc.data_ptr())); del B
         for M in (1, 4, 16):
+            if not want("int8w_gemv_M%d_4096x%d" % (M, N)):
+                continue
             x = torch.randn((M, K), generator=g, device=dev).to(torch.bfloat16)
             C = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
             ep = capi.make_epilogue(C.data_ptr(), N * 2, capi.BF16, capi.STEP_DEQUANT)
@@ -686,11 +702,13 @@ def other_configs(torch, capi, dev, peaks):
     # ramp no longer counts: the weight stream itself
     K, N = 8192, 28672
     ws = []
-    for _ in range(3):
+    for _ in range(3 if any(want("int8w_gemv_M%d_8192x28672" % M) for M in (1, 16)) else 0):
         B = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev, generator=g)
         sc = torch.rand(N, generator=g, device=dev) * 0.019 + 0.001
         ws.append(capi.Weight(B.data_ptr(), capi.S8, K, N, K, True, capi.PACK_INT8_CHANNEL, sc.data_ptr())); del B
     for M in (1, 16):
+        if not want("int8w_gemv_M%d_8192x28672" % M):
+            continue
         x = torch.randn((M, K), generator=g, device=dev).to(torch.bfloat16)
         C = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
         ep = capi.make_epilogue(C.data_ptr(), N * 2, capi.BF16, capi.STEP_DEQUANT)
@@ -701,9 +719,11 @@ def other_configs(torch, capi, dev, peaks):
     del ws
     # config 4: int8 x int8 GEMM with quantised post-ops
     M, K, N = 2048, 4096, 4096
+    if only is not None and not only.startswith("int8_gemm_2048x4096x4096_"):
+        return out
     A = torch.randint(-128, 128, (M, K), dtype=torch.int8, device=dev, generator=g)
     ws = []
-    for _ in range(8):
+    for _ in range(8 if only is None else 3):
         B = torch.randint(-128, 128, (K, N), dtype=torch.int8, device=dev, generator=g)
         ws.append(capi.Weight(B.data_ptr(), capi.S8, K, N, N, False)); del B
     sB = torch.rand(N, generator=g, device=dev) * 0.049 + 0.001
@@ -720,10 +740,14 @@ def other_configs(torch, capi, dev, peaks):
                                                       bias.data_ptr(), 0.02, sB.data_ptr(), 0.05),
     }
     for name, ep in cases.items():
+        if not want("int8_gemm_2048x4096x4096_" + name):
+            continue
         t = timed_graph(lambda s: [w.matmul(A.data_ptr(), capi.S8, M, K, K, ep, stream=s) for w in ws], len(ws))
         out["int8_gemm_2048x4096x4096_" + name] = {"us": t * 1e6, "tops": 2.0 * M * K * N / t / 1e12}
     # comparison only (never on the product path): the same int8 product by torch's library kernel, as a measured
     # yardstick for the int8 tensor-core rate of this GPU
+    if not want("int8_gemm_2048x4096x4096_library_int_mm"):
+        return out
     try:
         Bs = [torch.randint(-128, 128, (K, N), dtype=torch.int8, device=dev, generator=g) for _ in range(8)]
         t = timed_graph(lambda s: [torch._int_mm(A, Bm) for Bm in Bs], len(Bs))
@@ -753,6 +777,9 @@ def main():
     ap.add_argument("--legs", default="parity,kernel,sustained,e2e,llama7b,decode,configs,cpu",
                     help="optional legs around the main timed loop (comma list of parity,kernel,sustained,e2e,llama7b,"
                          "decode,configs,cpu; '' = none)")
+    ap.add_argument("--case", default=None,
+                    help="run ONE of the other single-GPU configurations by its key in `other_configs` (e.g. "
+                         "int8w_gemv_M16_8192x28672) with plain launches and print its record: what a profiler is pointed at")
     ap.add_argument("--sustain-s", type=float, default=1.2, help="length of the sustained leg in seconds")
     args = ap.parse_args()
     claim_stdout()
@@ -765,7 +792,18 @@ def main():
     name = args.workload or DEFAULT_WORKLOAD
     w = WORKLOADS[name]
     M = args.M or w["M"]
-    if args.impl == "reference":
+    if args.case:
+        import torch
+        from mm_amx_b200 import capi
+        torch.cuda.set_device(0)
+        capi.lib()
+        res = other_configs(torch, capi, torch.device("cuda", 0), measured_peaks(), only=args.case)
+        capi.sync_check()
+        if not res:
+            sys.stderr.write("unknown case %r\n" % args.case)
+            sys.exit(2)
+        emit({"case": args.case, "result": res[args.case], "gpu_launches": capi.launch_count()})
+    elif args.impl == "reference":
         run_reference(args, w, M, name)
     else:
         run_ours(args, w, M, name)

@@ -210,6 +210,18 @@ int b200fc_mlp_run_decode_static(b200fc_mlp_t* mlp, const void* x, int64_t ldx_b
                                  int64_t ldo_bytes, void* stream);
 int64_t b200fc_mlp_decode_static_capacity(void);
 int64_t b200fc_mlp_decode_static_footprint(void);
+/* ---- the steps either side of the MLP in a Llama block -------------------------------------------------------------- */
+/* out[M,K] bf16 = RMSNorm(x): y = x * rsqrt(mean(x^2) + eps) in fp32, rounded to bf16 — the weight-less LlamaRMSNorm
+ * the reference's benchmark script puts in front of every MLP (torch-ext/test.py:161-176).  `weight` (bf16 [K], may be
+ * NULL) multiplies the rounded value, rounded again (the form with a learned scale). */
+int b200fc_rmsnorm(const void* x, int64_t ldx_bytes, int M, int K, const void* weight, float eps, void* out,
+                   int64_t ldo_bytes, void* stream);
+/* One MLP block of a Llama layer: out = (add_residual ? x : 0) + MLP(RMSNorm(x)).  The reference chains
+ * LlamaRMSNorm -> MLP per layer (torch-ext/test.py:178-189); the residual add has no reference counterpart.  The
+ * normalisation is one small kernel ahead of gate/up; the residual is added in the down projection's epilogue, in fp32,
+ * before the single bf16 rounding of the output.  tp_size must be 1; out must not alias x. */
+int b200fc_mlp_run_block(b200fc_mlp_t* mlp, const void* x, int64_t ldx_bytes, int M, float eps, const void* norm_weight,
+                         int add_residual, void* out, int64_t ldo_bytes, void* stream);
 /* device pointer to the [M, N/tp] bf16 activation of the last run (debug / layer-wise parity) */
 const void* b200fc_mlp_act(const b200fc_mlp_t* mlp);
 

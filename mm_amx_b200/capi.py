@@ -63,6 +63,9 @@ SIGNATURES = {
     "b200fc_mlp_down_allreduce": (c_int, [c_void_p, c_int, ctypes.POINTER(AllReduce), c_void_p]),
     "b200fc_mlp_run_host": (c_int, [c_void_p, c_void_p, c_i64, c_int, c_void_p, c_i64, c_void_p]),
     "b200fc_mlp_run_decode_static": (c_int, [c_void_p, c_void_p, c_i64, c_int, c_void_p, c_int, c_i64, c_void_p]),
+    "b200fc_rmsnorm": (c_int, [c_void_p, c_i64, c_int, c_int, c_void_p, ctypes.c_float, c_void_p, c_i64, c_void_p]),
+    "b200fc_mlp_run_block": (c_int, [c_void_p, c_void_p, c_i64, c_int, ctypes.c_float, c_void_p, c_int, c_void_p, c_i64,
+                                     c_void_p]),
     "b200fc_mlp_decode_static_capacity": (c_i64, []),
     "b200fc_mlp_decode_static_footprint": (c_i64, []),
     "b200fc_mlp_act": (c_void_p, [c_void_p]),
@@ -225,6 +228,11 @@ class Mlp:
     def run_host(self, x_ptr, ldx_bytes, M, out_ptr, ldo_bytes, stream=None):
         check(lib().b200fc_mlp_run_host(self.h, x_ptr, ldx_bytes, M, out_ptr, ldo_bytes, stream))
 
+    def run_block(self, x_ptr, ldx_bytes, M, eps, out_ptr, ldo_bytes, norm_weight_ptr=None, add_residual=True, stream=None):
+        """out = (x if add_residual else 0) + MLP(RMSNorm(x)); see b200fc_mlp_run_block in include/b200fc.h."""
+        check(lib().b200fc_mlp_run_block(self.h, x_ptr, ldx_bytes, M, eps, norm_weight_ptr, 1 if add_residual else 0,
+                                         out_ptr, ldo_bytes, stream))
+
     def run_decode_static(self, x_ptr, ldx_bytes, M, out_ptr, out_dtype, ldo_bytes, stream=None):
         """Allocation-free forward for 1 <= M <= 16; see b200fc_mlp_run_decode_static in include/b200fc.h."""
         check(lib().b200fc_mlp_run_decode_static(self.h, x_ptr, ldx_bytes, M, out_ptr, out_dtype, ldo_bytes, stream))
@@ -254,6 +262,10 @@ def matvec_host(A_ptr, dtype, M, K, lda_bytes, b_ptr, c_ptr, stream=None):
 
 def memcpy(dst_ptr, src_ptr, nbytes, stream=None):
     check(lib().b200fc_memcpy(dst_ptr, src_ptr, nbytes, stream))
+
+
+def rmsnorm(x_ptr, ldx_bytes, M, K, eps, out_ptr, ldo_bytes, weight_ptr=None, stream=None):
+    check(lib().b200fc_rmsnorm(x_ptr, ldx_bytes, M, K, weight_ptr, eps, out_ptr, ldo_bytes, stream))
 
 
 def add_round_bf16(a_ptr, b_ptr, out_ptr, n, stream=None):

@@ -216,7 +216,8 @@ static int validate_epilogue(const b200fc_epilogue_t* ep, bool int_acc) {
 }
 
 int matmul_device(const Weight& w, Weight* w_mut, const void* A, int dtypeA, int M, int K, int64_t lda, int n0,
-                  int n1, const b200fc_epilogue_t* ep_in, cudaStream_t s, void* gemv_scratch) {
+                  int n1, const b200fc_epilogue_t* ep_in, cudaStream_t s, void* gemv_scratch, const void* residual,
+                  int64_t ld_res) {
     if (M < 0 || K != w.K) { set_error("matmul: K=%d does not match the packed weights (K=%d) or M<0", K, w.K); return B200FC_ERR_INVALID; }
     if (n0 < 0 || n1 > w.N || n0 > n1) { set_error("matmul: column range [%d,%d) outside [0,%d)", n0, n1, w.N); return B200FC_ERR_INVALID; }
     const bool a8 = dtypeA == B200FC_S8 || dtypeA == B200FC_U8;
@@ -233,6 +234,13 @@ int matmul_device(const Weight& w, Weight* w_mut, const void* A, int dtypeA, int
     ep.bias = ep_in->bias; ep.deq_scale = ep_in->deq_scale; ep.deq_per_oc = ep_in->deq_scale_per_oc;
     ep.q_scale = ep_in->q_scale; ep.q_per_oc = ep_in->q_scale_per_oc;
     ep.mc_reduce = g_mc_reduce;
+    if (residual) {
+        if ((ep.steps & B200FC_STEP_SILU_MUL) || (ep.out_dtype != B200FC_BF16 && ep.out_dtype != B200FC_F32) || g_mc_reduce) {
+            set_error("matmul: a residual needs a bf16 or fp32 output without SILU_MUL");
+            return B200FC_ERR_INVALID;
+        }
+        ep.residual = residual; ep.ld_res = ld_res;
+    }
     if (ep.mc_reduce && M <= 16) { set_error("multicast-reduce output needs the tensor-core path (M > 16)"); return B200FC_ERR_UNSUPPORTED; }
     if (w.compressed) {
         if (!(ep.steps & B200FC_STEP_DEQUANT)) { set_error("matmul: compressed weights need STEP_DEQUANT"); return B200FC_ERR_INVALID; }
@@ -285,6 +293,7 @@ int matmul_device(const Weight& w, Weight* w_mut, const void* A, int dtypeA, int
             if (e2.bias) e2.bias += r0;
             if (e2.deq_per_oc) e2.deq_per_oc += r0;
             if (e2.q_per_oc) e2.q_per_oc += r0;
+            if (e2.residual) e2.residual = (const char*)e2.residual + (long long)r0 * 2;
             rc = launch_gemm_tc(wide, B200FC_BF16, w.K_pad, rows, A_use, B200FC_BF16, M, K, lda_use, c0 - r0, c1 - r0, e2, s);
             if (rc) return rc;
         }
@@ -780,6 +789,34 @@ int b200fc_mlp_run_host(b200fc_mlp_t* h, const void* x, int64_t ldx, int M, void
     B200FC_CUDA(cudaEventRecord(m.ev_join, s_out));
     B200FC_CUDA(cudaStreamWaitEvent(s, m.ev_join, 0));
     return check_kernel_status(s);
+}
+
+int b200fc_rmsnorm(const void* x, int64_t ldx, int M, int K, const void* weight, float eps, void* out, int64_t ldo,
+                   void* stream) {
+    if (!x || !out || M < 0 || K <= 0) { set_error("rmsnorm: null pointer or bad shape"); return B200FC_ERR_INVALID; }
+    if (ldx < (int64_t)K * 2 || ldo < (int64_t)K * 2) { set_error("rmsnorm: leading dimension smaller than a row"); return B200FC_ERR_INVALID; }
+    return launch_rmsnorm(x, ldx, M, K, weight, eps, out, ldo, (cudaStream_t)stream);
+}
+
+int b200fc_mlp_run_block(b200fc_mlp_t* h, const void* x, int64_t ldx, int M, float eps, const void* norm_weight,
+                         int add_residual, void* out, int64_t ldo, void* stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!h || !x || !out) { set_error("mlp_run_block: null pointer"); return B200FC_ERR_INVALID; }
+    Mlp& m = h->m;
+    if (m.tp_size != 1) { set_error("mlp_run_block: tensor-parallel shard"); return B200FC_ERR_INVALID; }
+    if (M < 0) { set_error("mlp_run_block: M < 0"); return B200FC_ERR_INVALID; }
+    if (M == 0) return B200FC_OK;
+    // normalised activations: per-stream scratch (kernels on one stream are ordered)
+    void* xn = nullptr;
+    const int64_t ldn = (int64_t)m.K * 2;
+    int rc = get_stream_scratch((size_t)M * ldn, s, 4, &xn);
+    if (!rc) rc = launch_rmsnorm(x, ldx, M, m.K, norm_weight, eps, xn, ldn, s);
+    if (!rc) rc = mlp_gate_up_device(m, xn, ldn, M, s);
+    if (rc) return rc;
+    b200fc_epilogue_t e2 = {};
+    e2.steps = 0; e2.out_dtype = B200FC_BF16; e2.C = out; e2.ldc_bytes = ldo;
+    return matmul_device(m.down, nullptr, m.act, B200FC_BF16, M, m.Ns, (int64_t)m.Ns * 2, 0, m.K, &e2, s, nullptr,
+                         add_residual ? x : nullptr, ldx);
 }
 
 const void* b200fc_mlp_act(const b200fc_mlp_t* h) { return h ? h->m.act : nullptr; }

@@ -45,6 +45,9 @@ struct Epilogue {
     float q_scale;
     const float* q_per_oc;
     int mc_reduce = 0;  // 1: C is an NVLink multicast address; the store is a multimem.red.add (in-switch all-reduce)
+    // optional residual, added in fp32 right before the output is rounded: C[m, n] = round(post-ops(...) + residual[m, n])
+    const void* residual = nullptr;   // [M, N] bf16
+    long long ld_res = 0;             // bytes
 };
 
 // Fused Llama MLP object (b200fc_mlp_t)
@@ -102,8 +105,10 @@ unsigned long long wait_limit_ns();
 // api.cu: validated dispatch of one Matmul call on device pointers (w_mut is unused and kept for call-site symmetry)
 // gemv_scratch: counters + partial-sum slots for the decode kernel (gemv_scratch_bytes(), counters zero), or null to
 // use the stream's own
+// residual: optional [M, N] bf16 matrix added to the result before the output rounding (not with SILU_MUL)
 int matmul_device(const Weight& w, Weight* w_mut, const void* A, int dtypeA, int M, int K, int64_t lda, int n0, int n1,
-                  const b200fc_epilogue_t* ep, cudaStream_t s, void* gemv_scratch = nullptr);
+                  const b200fc_epilogue_t* ep, cudaStream_t s, void* gemv_scratch = nullptr,
+                  const void* residual = nullptr, int64_t ld_res = 0);
 
 // ---- launchers -------------------------------------------------------------------------------------------------
 // pack.cu
@@ -119,6 +124,8 @@ int launch_copy2d(const void* src, int64_t lds, void* dst, int64_t ldd, int rows
                   cudaStream_t s);
 int launch_add_round_bf16(const float* a, const float* b, void* out, int64_t n, cudaStream_t s);
 int launch_fill(void* p, size_t bytes, cudaStream_t s);
+int launch_rmsnorm(const void* x, int64_t ldx, int M, int K, const void* weight, float eps, void* out, int64_t ldo,
+                   cudaStream_t s);
 // gemv_tma.cu: M <= 16, bf16 activations, bf16 or int8 weights streamed by TMA through a shared-memory ring.
 // `scratch`: gemv_scratch_bytes() of device memory whose first kGemvMaxCtas words are zero (the kernel leaves them
 // zero), shared by the launches of one stream; null = the stream's own (allocated on first use).
@@ -202,7 +209,13 @@ __device__ __forceinline__ float postop_scalar(float v, int n, const Epilogue& e
     return v;
 }
 
+__device__ __forceinline__ float residual_at(const Epilogue& ep, int m, int n) {
+    const unsigned short b = ((const unsigned short*)((const char*)ep.residual + (long long)m * ep.ld_res))[n];
+    return __uint_as_float((unsigned)b << 16);
+}
+
 __device__ __forceinline__ void store_scalar(float v, int m, int n, const Epilogue& ep) {
+    if (ep.residual) v += residual_at(ep, m, n);
     char* row = (char*)ep.C + (long long)m * ep.ldc;
     if (ep.out_dtype == B200FC_F32) ((float*)row)[n] = v;
     else if (ep.out_dtype == B200FC_BF16) ((unsigned short*)row)[n] = f32_to_bf16_bits(v);

@@ -310,6 +310,26 @@ __device__ __forceinline__ void epilogue_chunk(const unsigned (&r)[32], int m, i
         }
     }
     const bool full = p.vec_ok && n + 32 <= p.n1;
+    if (ep.residual && row_ok) {
+        // residual added in fp32, before the one rounding of the output
+        const char* rrow = (const char*)ep.residual + (long long)m * ep.ld_res;
+        if (full && (((uintptr_t)rrow + (size_t)n * 2) & 15) == 0) {
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const int4 t = __ldg((const int4*)(rrow + (long long)n * 2) + q);
+                const unsigned w4[4] = {(unsigned)t.x, (unsigned)t.y, (unsigned)t.z, (unsigned)t.w};
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    v[8 * q + 2 * e] += __uint_as_float(w4[e] << 16);
+                    v[8 * q + 2 * e + 1] += __uint_as_float(w4[e] & 0xffff0000u);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+                v[j] += __uint_as_float((unsigned)((const unsigned short*)rrow)[min(n + j, p.n1 - 1)] << 16);
+        }
+    }
     if (staged_f32) {
         unsigned u[32];
 #pragma unroll
@@ -978,6 +998,7 @@ int launch_cfg2(const CUtensorMap& ma, const CUtensorMap& mw, GemmParams p, cuda
         if (rc) return rc;
         p.split_stride = (long long)slab;
         p.ep.steps = 0;
+        p.ep.residual = nullptr;                    // (the reduction kernel adds it, with the caller's post-ops)
         p.ep.out_dtype = I8 ? B200FC_S32 : B200FC_F32;
         p.ep.C = (char*)ws - (long long)p.n0 * 4;   // the kernel indexes columns by the global n
         p.ep.ldc = (long long)pitch * 4;

@@ -146,6 +146,37 @@ __global__ void add_round_bf16_kernel(const float* __restrict__ a, const float* 
     for (; i < n; i += stride) out[i] = f32_to_bf16_bits(b ? a[i] + b[i] : a[i]);
 }
 
+// RMS normalisation of one row per block, the LlamaRMSNorm the reference's benchmark script puts in front of every MLP
+// (torch-ext/test.py:161-176): fp32 arithmetic, y = x * rsqrt(mean(x^2) + eps), rounded to bf16; an optional bf16
+// weight vector multiplies the rounded value (the transformers form), rounded again.
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const unsigned short* __restrict__ x, long long ldx, int K,
+                                                      const unsigned short* __restrict__ weight, float eps,
+                                                      unsigned short* __restrict__ out, long long ldo) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const unsigned short* row = (const unsigned short*)((const char*)x + (long long)blockIdx.x * ldx);
+    unsigned short* orow = (unsigned short*)((char*)out + (long long)blockIdx.x * ldo);
+    float ss = 0.0f;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) {
+        const float v = __uint_as_float((unsigned)row[k] << 16);
+        ss = fmaf(v, v, ss);
+    }
+    __shared__ float red[8];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) tot += red[i];      // same order in every thread
+    const float r = rsqrtf(tot / (float)K + eps);
+    for (int k = threadIdx.x; k < K; k += blockDim.x) {
+        unsigned short y = f32_to_bf16_bits(__uint_as_float((unsigned)row[k] << 16) * r);
+        if (weight) y = f32_to_bf16_bits(__uint_as_float((unsigned)y << 16) * __uint_as_float((unsigned)weight[k] << 16));
+        orow[k] = y;
+    }
+}
+
 __global__ void fill_kernel(int4* __restrict__ p, long long n16, int v) {
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     long long stride = (long long)gridDim.x * blockDim.x;
@@ -228,6 +259,16 @@ int launch_add_round_bf16(const float* a, const float* b, void* out, int64_t n, 
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (blocks < 1) blocks = 1;
     add_round_bf16_kernel<<<(unsigned)blocks, 256, 0, s>>>(a, b, (unsigned short*)out, n);
+    count_launch();
+    B200FC_CUDA(cudaGetLastError());
+    return B200FC_OK;
+}
+
+int launch_rmsnorm(const void* x, int64_t ldx, int M, int K, const void* weight, float eps, void* out, int64_t ldo,
+                   cudaStream_t s) {
+    if (M <= 0) return B200FC_OK;
+    rmsnorm_kernel<<<M, 256, 0, s>>>((const unsigned short*)x, ldx, K, (const unsigned short*)weight, eps,
+                                     (unsigned short*)out, ldo);
     count_launch();
     B200FC_CUDA(cudaGetLastError());
     return B200FC_OK;

@@ -3,7 +3,7 @@ import ctypes
 import os
 import subprocess
 import numpy as np
-from ._common import ptr, c_contig, c_int, c_int64, c_float, c_void_p
+from ._common import ptr, c_contig, c_int, c_int64, c_float, c_void_p, bf16_bits, bf16_to_f32
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB = None
@@ -138,3 +138,25 @@ def mlp(x, gate, up, down, want_act=False, want_partial=False):
     if want_partial:
         res += (part,)
     return res[0] if len(res) == 1 else res
+
+
+def rmsnorm(x, eps, weight=None):
+    """LlamaRMSNorm as the reference's benchmark script defines it (torch-ext/test.py:161-176): the row is widened to
+    fp32, scaled by rsqrt(mean(x^2) + eps), rounded back to the input type (bf16).  `weight` (bf16 bits [K]) multiplies
+    the rounded value and the product is rounded again (the form with a learned scale).  x: bf16 bits [M, K]."""
+    xf = bf16_to_f32(np.ascontiguousarray(x, np.uint16))
+    var = np.mean(xf.astype(np.float64) ** 2, axis=-1, keepdims=True).astype(np.float32)   # fp32 mean, summed exactly
+    y = bf16_bits(xf * (np.float32(1.0) / np.sqrt(var + np.float32(eps))))
+    if weight is not None:
+        y = bf16_bits(bf16_to_f32(y) * bf16_to_f32(np.ascontiguousarray(weight, np.uint16))[None, :])
+    return y
+
+
+def mlp_block(x, gate, up, down, eps, norm_weight=None, add_residual=True):
+    """out = (x if add_residual else 0) + MLP(RMSNorm(x)), the layer step of torch-ext/test.py:178-189 plus the residual
+    of a Llama block; the sum is formed in fp32 from the MLP's fp32 result and rounded to bf16 once."""
+    xn = rmsnorm(x, eps, norm_weight)
+    _, part = mlp(xn, gate, up, down, want_partial=True)
+    if add_residual:
+        part = part + bf16_to_f32(np.ascontiguousarray(x, np.uint16))
+    return bf16_bits(part)

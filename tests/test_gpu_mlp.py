@@ -157,3 +157,38 @@ def test_matvec(M, K):
     c = np.zeros(M, np.float32)
     capi.matvec_host(A.ctypes.data, capi.BF16, M, K, A.strides[0], b.ctypes.data, c.ctypes.data)
     assert np.array_equal(c, port.matvec_bf16(A, b))
+
+
+@pytest.mark.parametrize("M", [1, 5, 16, 40, 300])
+@pytest.mark.parametrize("with_weight,residual", [(False, True), (True, False), (True, True)])
+def test_rmsnorm_and_mlp_block(M, with_weight, residual):
+    """RMSNorm in front of the MLP and the residual behind it (the layer step of torch-ext/test.py:161-189) against
+    the oracle: the normalised activations within one bf16 ulp (rsqrt vs 1/sqrt), the block within the 1e-2 bar."""
+    rng = np.random.default_rng(M * 3 + with_weight + 2 * residual)
+    K, N = 512, 1280
+    gate, up = H.normal_bf16(rng, (N, K), 0.02), H.normal_bf16(rng, (N, K), 0.02)
+    down = H.normal_bf16(rng, (K, N), 0.02)
+    x = H.normal_bf16(rng, (M, K), 1.5)
+    wn = H.normal_bf16(rng, (K,), 1.0) if with_weight else None
+    eps = 1e-6
+    dx = H.Dev(x)
+    dw = H.Dev(wn) if with_weight else None
+    dn = H.Dev(shape=(M, K), dtype=np.uint16, fill=0xCD)
+    capi.rmsnorm(dx.ptr, dx.ld, M, K, eps, dn.ptr, dn.ld, dw.ptr if dw else None)
+    capi.sync_check()
+    want_n = port.rmsnorm(x, eps, wn)
+    got_n = dn.numpy()
+    ulp = np.abs(got_n.astype(np.int32) - want_n.astype(np.int32))
+    assert ulp.max() <= (2 if with_weight else 1), ulp.max()
+    mlp = capi.Mlp(gate.ctypes.data, up.ctypes.data, down.ctypes.data, K, N)
+    out = H.Dev(shape=(M, K), dtype=np.uint16, fill=0xCD)
+    mlp.run_block(dx.ptr, dx.ld, M, eps, out.ptr, out.ld, dw.ptr if dw else None, residual)
+    capi.sync_check()
+    want = port.mlp_block(x, gate, up, down, eps, wn, residual)
+    assert H.rel_to_max(bf16_to_f32(out.numpy()), bf16_to_f32(want)) < 1e-2
+    # the block is the three public steps in a row: normalise, MLP, add (bit for bit when no residual is added)
+    if not residual:
+        plain = H.Dev(shape=(M, K), dtype=np.uint16)
+        mlp.run(dn.ptr, dn.ld, M, plain.ptr, plain.ld)
+        capi.sync_check()
+        assert np.array_equal(plain.numpy(), out.numpy())

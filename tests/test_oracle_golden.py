@@ -12,7 +12,7 @@ import numpy as np
 import pytest
 
 from oracle import port
-from oracle._common import bf16_to_f32
+from oracle._common import bf16_bits, bf16_to_f32
 import golden_cases as gc
 
 GOLD = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "golden_v1.npz"))
@@ -107,3 +107,20 @@ def test_silu_port_close_to_reference():
     assert np.array_equal(np.isfinite(got), ok)
     err = np.abs(got[ok] - ref[ok])
     assert (err <= np.abs(ref[ok]) * 2.0 ** -13 + 1e-37).all()
+
+
+def test_rmsnorm_oracle_matches_the_reference_script_definition():
+    """port.rmsnorm against the LlamaRMSNorm of the reference's benchmark script (torch-ext/test.py:161-176), evaluated
+    with torch on the CPU: identical up to the last bf16 bit (torch.mean sums in fp32, the oracle exactly)."""
+    import torch
+    rng = np.random.default_rng(11)
+    x = (rng.standard_normal((7, 384)) * 2.0).astype(np.float32)
+    xb = bf16_bits(x)
+    t = torch.from_numpy(bf16_to_f32(xb)).to(torch.bfloat16)
+    h = t.to(torch.float32)
+    var = h.pow(2).mean(-1, keepdim=True)
+    want = (h * torch.rsqrt(var + 1e-6)).to(torch.bfloat16)
+    want_bits = want.view(torch.int16).numpy().view(np.uint16)
+    got = port.rmsnorm(xb, 1e-6)
+    assert np.abs(got.astype(np.int32) - want_bits.astype(np.int32)).max() <= 1
+    assert (got == want_bits).mean() > 0.99
