@@ -717,6 +717,27 @@ def other_configs(torch, capi, dev, peaks, only=None):
         out["int8w_gemv_M%d_8192x28672" % M] = {"us": t * 1e6, "gbs": nbytes / t / 1e9,
                                                 "hbm_frac": nbytes / t / 1e9 / peaks["hbm_gbs"], "weight_sets": len(ws)}
     del ws
+    # 4-bit group-quantised weights (bf16 matrix quantised by the library: one fp32 scale per 128 K and output channel),
+    # same kernel family; bytes = the stored nibbles + the group scales + activations in and out
+    for K, N in ((4096, 11008), (8192, 28672)):
+        if not any(want("int4w_gemv_M%d_%dx%d" % (M, K, N)) for M in (1, 16)):
+            continue
+        nset = max(3, int(600e6 / (K * N // 2)) + 1) if only is None else 3
+        ws = []
+        for _ in range(nset):
+            B = (torch.randn((N, K), generator=g, device=dev) * 0.02).to(torch.bfloat16)
+            ws.append(capi.Weight(B.data_ptr(), capi.BF16, K, N, K * 2, True, capi.PACK_INT4_GROUP)); del B
+        for M in (1, 16):
+            if not want("int4w_gemv_M%d_%dx%d" % (M, K, N)):
+                continue
+            x = torch.randn((M, K), generator=g, device=dev).to(torch.bfloat16)
+            C = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+            ep = capi.make_epilogue(C.data_ptr(), N * 2, capi.BF16, capi.STEP_DEQUANT)
+            t = timed_graph(lambda s: [w.matmul(x.data_ptr(), capi.BF16, M, K, K * 2, ep, stream=s) for w in ws], nset)
+            nbytes = K * N // 2 + N * (K // 128) * 4 + M * (K + N) * 2
+            out["int4w_gemv_M%d_%dx%d" % (M, K, N)] = {"us": t * 1e6, "gbs": nbytes / t / 1e9,
+                                                       "hbm_frac": nbytes / t / 1e9 / peaks["hbm_gbs"], "weight_sets": nset}
+        del ws
     # config 4: int8 x int8 GEMM with quantised post-ops
     M, K, N = 2048, 4096, 4096
     if only is not None and not only.startswith("int8_gemm_2048x4096x4096_"):

@@ -31,7 +31,10 @@ typedef enum {
     B200FC_ERR_KERNEL = 5       /* a kernel reported a bounded wait that ran out */
 } b200fc_status_t;
 
-typedef enum { B200FC_BF16 = 0, B200FC_S8 = 1, B200FC_U8 = 2, B200FC_F32 = 3, B200FC_S32 = 4 } b200fc_dtype_t;
+typedef enum {
+    B200FC_BF16 = 0, B200FC_S8 = 1, B200FC_U8 = 2, B200FC_F32 = 3, B200FC_S32 = 4,
+    B200FC_S4 = 5   /* only as the stored type of B200FC_PACK_INT4_GROUP weights (two values per byte) */
+} b200fc_dtype_t;
 
 /* Post-op steps, executed in this fixed order (amx_kernel::PP::Steps, include/kernels_amx.hpp:540-550, and
  * PP::BiasGeluStore::operator(), :586-672):  [int32 accumulator -> fp32] -> DEQUANT -> BIAS -> GELU -> QUANT -> store.
@@ -88,8 +91,15 @@ typedef enum {
     B200FC_PACK_PLAIN = 0,       /* keep the dtype of B (bf16 / s8 / u8): repackB_1x2, kernels_amx.hpp:761-816 */
     B200FC_PACK_QUANT_TENSOR = 1,/* bf16 B -> int8 with one absmax scale, the compressed-weight path
                                     Matmul<bf16,int8_t,float>, kernels_amx.hpp:1363-1377 */
-    B200FC_PACK_INT8_CHANNEL = 2 /* s8 B + caller's per-output-channel fp32 scales [N] (no reference counterpart) */
+    B200FC_PACK_INT8_CHANNEL = 2,/* s8 B + caller's per-output-channel fp32 scales [N] (no reference counterpart) */
+    B200FC_PACK_INT4_GROUP = 3   /* bf16 B -> 4-bit values in [-7, 7] with one fp32 absmax scale per output channel and
+                                    group of B200FC_INT4_GROUP consecutive K.  The reference reserves this precision
+                                    (Weight_INT4, main.cpp:36) and measures its upper bound with a dequantisation that
+                                    does no arithmetic (fake_dequant_i4_16x32, weight_compression/wcompress.hpp:122-134)
+                                    but defines no algorithm; the scheme is the int8 one of kernels_amx.hpp:1363-1377
+                                    per group: q = rne(w * (7 / absmax)), dequantised value = q * (absmax / 7). */
 } b200fc_pack_mode_t;
+#define B200FC_INT4_GROUP 128
 
 /* Packs B once.  transposeB = 0: B is [K, N]; 1: B is [N, K] (Matmul ctor flag, kernels_amx.hpp:1071, getSubMatB
  * :699-705).  B may be a host or a device pointer.  `scales`: B200FC_PACK_INT8_CHANNEL needs the [N] per-channel
@@ -101,8 +111,12 @@ int b200fc_weight_pack(const void* B, int dtypeB, int K, int N, int64_t ldb_byte
 int b200fc_weight_free(b200fc_weight_t* w);
 /* K, N, dtype of the stored weights (B200FC_BF16/S8/U8), whether they are dequantised on the fly, tensor scale */
 int b200fc_weight_info(const b200fc_weight_t* w, int* K, int* N, int* dtype, int* compressed, float* deq_scale);
-/* copies the packed weights back as a plain row-major [N, K] matrix of their stored dtype (host or device dst) */
+/* copies the packed weights back as a plain row-major [N, K] matrix of their stored dtype (host or device dst);
+ * 4-bit weights come back as one int8 per value */
 int b200fc_weight_unpack(const b200fc_weight_t* w, void* dst, int64_t ld_bytes, void* stream);
+/* the dequant scales of B200FC_PACK_INT4_GROUP weights as a row-major fp32 matrix [N, ceil(K / B200FC_INT4_GROUP)]
+ * in HOST memory (ld_bytes >= 4 * groups); synchronises the stream */
+int b200fc_weight_group_scales(const b200fc_weight_t* w, float* host_dst, int64_t ld_bytes, void* stream);
 
 /* Serialised packed weights: a self-describing blob in HOST memory (64-byte header, the packed matrix as it lies in
  * HBM, then the per-channel scales if the object has them) that b200fc_weight_import turns back into an identical
@@ -117,7 +131,8 @@ int b200fc_weight_import(const void* host_src, size_t bytes, b200fc_weight_t** o
 /* ---- Matmul::operator()(A, B, n0, n1, ppkernel), include/kernels_amx.hpp:1169-1314 and :1343-1516 ------------- */
 /* C[:, n0:n1) = postops(A[M,K] * W[:, n0:n1)).  dtypeA: B200FC_BF16 with bf16 or compressed weights, B200FC_S8 /
  * B200FC_U8 with s8 / u8 weights.  With compressed weights STEP_DEQUANT is required and the weight's own scale(s)
- * replace ep->deq_scale, as the reference's set_deq_scale() call does (kernels_amx.hpp:1379). */
+ * replace ep->deq_scale, as the reference's set_deq_scale() call does (kernels_amx.hpp:1379).  4-bit weights: the
+ * group scales are applied to the group sums inside the kernel, and n0 must be a multiple of 128. */
 int b200fc_matmul(const b200fc_weight_t* W, const void* A, int dtypeA, int M, int K, int64_t lda_bytes, int n0, int n1,
                   const b200fc_epilogue_t* ep, void* stream);
 /* Same call with A, ep->C, ep->bias and the per-channel scale arrays in HOST memory: stages them through device

@@ -6,9 +6,10 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libb200fc.so")
 
 OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_NOMEM, ERR_KERNEL = range(6)
-BF16, S8, U8, F32, S32 = range(5)
+BF16, S8, U8, F32, S32, S4 = range(6)
 STEP_NONE, STEP_DEQUANT, STEP_BIAS, STEP_GELU, STEP_QUANT, STEP_SILU_MUL = 0, 1, 2, 4, 8, 16
-PACK_PLAIN, PACK_QUANT_TENSOR, PACK_INT8_CHANNEL = 0, 1, 2
+PACK_PLAIN, PACK_QUANT_TENSOR, PACK_INT8_CHANNEL, PACK_INT4_GROUP = 0, 1, 2, 3
+INT4_GROUP = 128
 
 c_int, c_i64, c_float, c_void_p = ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p
 
@@ -41,6 +42,7 @@ SIGNATURES = {
     "b200fc_weight_info": (c_int, [c_void_p, ctypes.POINTER(c_int), ctypes.POINTER(c_int), ctypes.POINTER(c_int),
                                    ctypes.POINTER(c_int), ctypes.POINTER(c_float)]),
     "b200fc_weight_unpack": (c_int, [c_void_p, c_void_p, c_i64, c_void_p]),
+    "b200fc_weight_group_scales": (c_int, [c_void_p, c_void_p, c_i64, c_void_p]),
     "b200fc_weight_export_size": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_size_t)]),
     "b200fc_weight_export": (c_int, [c_void_p, c_void_p, ctypes.c_size_t, c_void_p]),
     "b200fc_weight_import": (c_int, [c_void_p, ctypes.c_size_t, ctypes.POINTER(c_void_p), c_void_p]),
@@ -148,6 +150,10 @@ class Weight:
 
     def unpack(self, dst_ptr, ld_bytes, stream=None):
         check(lib().b200fc_weight_unpack(self.h, dst_ptr, ld_bytes, stream))
+
+    def group_scales(self, host_dst_ptr, ld_bytes, stream=None):
+        """fp32 [N, ceil(K / INT4_GROUP)] dequant scales of 4-bit weights, into HOST memory."""
+        check(lib().b200fc_weight_group_scales(self.h, host_dst_ptr, ld_bytes, stream))
 
     def export(self, stream=None):
         """Serialised form of the packed weights (bytearray); Weight.from_blob() rebuilds the object from it."""

@@ -165,17 +165,23 @@ static bool is_device_ptr(const void* p) {
 static int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
 static int alloc_weight(Weight& w, int K, int N, int dtype) {
-    const int es = elem_size(dtype);
     w.K = K; w.N = N; w.dtype = dtype;
-    w.K_pad = round_up(K * es, kKPadBytes) / es;
     w.N_pad = round_up(N, kRowPad);
-    B200FC_CUDA(cudaMalloc(&w.data, (size_t)w.N_pad * w.K_pad * es));
+    if (dtype == B200FC_S4) {
+        w.K_pad = round_up(K, 2 * kKPadBytes);
+        B200FC_CUDA(cudaMalloc(&w.data, w.data_bytes()));
+        B200FC_CUDA(cudaMalloc(&w.scale_grp, w.scale_grp_floats() * sizeof(float)));
+        return B200FC_OK;
+    }
+    const int es = elem_size(dtype);
+    w.K_pad = round_up(K * es, kKPadBytes) / es;
+    B200FC_CUDA(cudaMalloc(&w.data, w.data_bytes()));
     return B200FC_OK;
 }
 
 static void free_weight(Weight* w) {
     if (!w) return;
-    cudaFree(w->data); cudaFree(w->scale_per_oc);
+    cudaFree(w->data); cudaFree(w->scale_per_oc); cudaFree(w->scale_grp);
     cudaFree(w->stage_A); cudaFree(w->stage_C); cudaFree(w->stage_vec);
 }
 
@@ -246,6 +252,7 @@ int matmul_device(const Weight& w, Weight* w_mut, const void* A, int dtypeA, int
         if (!(ep.steps & B200FC_STEP_DEQUANT)) { set_error("matmul: compressed weights need STEP_DEQUANT"); return B200FC_ERR_INVALID; }
         ep.deq_scale = w.deq_scale;          // the weight's scale replaces the caller's (kernels_amx.hpp:1379)
         ep.deq_per_oc = w.scale_per_oc;
+        if (w.dtype == B200FC_S4 && (n0 % 128)) { set_error("matmul: 4-bit weights need n0 to be a multiple of 128"); return B200FC_ERR_INVALID; }
     }
     if ((ep.steps & B200FC_STEP_SILU_MUL) && ((n0 % 32) || ((n1 - n0) % 32))) {
         set_error("matmul: SILU_MUL needs n0 and n1 multiples of 32");
@@ -268,9 +275,10 @@ int matmul_device(const Weight& w, Weight* w_mut, const void* A, int dtypeA, int
         A_use = buf; lda_use = ld2;
     }
     if (w.compressed) {
-        // M > 16 with int8-compressed weights.  The reference decompresses 16 weight rows at a time into a reused
+        // M > 16 with compressed weights.  The reference decompresses 16 weight rows at a time into a reused
         // buffer right before the tile product (kernels_amx.hpp:1443-1514); here a block of weight rows is widened to
-        // bf16 (exact) into a per-stream scratch of at most 32 MB — small enough to stay in the 126 MB L2 until the
+        // bf16 (exact for int8; 4-bit values are multiplied by their group scale and rounded to bf16, the one place
+        // where the group scale cannot wait for the epilogue) into a per-stream scratch of at most 32 MB — small enough to stay in the 126 MB L2 until the
         // GEMM over those rows, launched right behind it, has read it — so HBM sees the int8 bytes only and no second
         // copy of the matrix is kept.
         (void)w_mut;
@@ -368,7 +376,8 @@ int b200fc_weight_pack(const void* B, int dtypeB, int K, int N, int64_t ldb, int
     if (ldb < (int64_t)cols * es) { set_error("weight_pack: ldb smaller than a row"); return B200FC_ERR_INVALID; }
     if (pack_mode == B200FC_PACK_QUANT_TENSOR && dtypeB != B200FC_BF16) { set_error("weight_pack: QUANT_TENSOR needs bf16 weights"); return B200FC_ERR_INVALID; }
     if (pack_mode == B200FC_PACK_INT8_CHANNEL && (dtypeB != B200FC_S8 || !scales)) { set_error("weight_pack: INT8_CHANNEL needs s8 weights and scales"); return B200FC_ERR_INVALID; }
-    if (pack_mode < 0 || pack_mode > 2) { set_error("weight_pack: unknown pack mode"); return B200FC_ERR_INVALID; }
+    if (pack_mode == B200FC_PACK_INT4_GROUP && dtypeB != B200FC_BF16) { set_error("weight_pack: INT4_GROUP needs bf16 weights"); return B200FC_ERR_INVALID; }
+    if (pack_mode < 0 || pack_mode > 3) { set_error("weight_pack: unknown pack mode"); return B200FC_ERR_INVALID; }
 
     b200fc_weight_t* h = new (std::nothrow) b200fc_weight_t;
     if (!h) { set_error("out of host memory"); return B200FC_ERR_NOMEM; }
@@ -377,9 +386,20 @@ int b200fc_weight_pack(const void* B, int dtypeB, int K, int N, int64_t ldb, int
     {
         DevSrc src;
         rc = to_device(B, ldb, rows, (size_t)cols * es, s, src);
-        if (!rc) rc = alloc_weight(w, K, N, pack_mode == B200FC_PACK_QUANT_TENSOR ? B200FC_S8 : dtypeB);
+        if (!rc) rc = alloc_weight(w, K, N, pack_mode == B200FC_PACK_QUANT_TENSOR ? B200FC_S8 : (pack_mode == B200FC_PACK_INT4_GROUP ? B200FC_S4 : dtypeB));
         if (!rc) {
-            if (pack_mode == B200FC_PACK_QUANT_TENSOR) {
+            if (pack_mode == B200FC_PACK_INT4_GROUP) {
+                // two passes: the bf16 matrix in packed row order (zero padded), then one warp per group of 128 K
+                Weight wide;
+                wide.K = K; wide.N = N; wide.dtype = B200FC_BF16; wide.K_pad = w.K_pad; wide.N_pad = w.N_pad;
+                if (cudaMalloc(&wide.data, wide.data_bytes()) != cudaSuccess) rc = B200FC_ERR_NOMEM;
+                if (!rc) rc = launch_pack(src.p, B200FC_BF16, K, N, src.ld, transposeB, wide, false, s);
+                if (!rc) rc = launch_quant4(wide.data, w, s);
+                if (!rc && cudaStreamSynchronize(s) != cudaSuccess) rc = B200FC_ERR_CUDA;
+                cudaFree(wide.data);
+                w.compressed = true;
+                w.deq_scale = 1.0f;
+            } else if (pack_mode == B200FC_PACK_QUANT_TENSOR) {
                 float* absmax = nullptr;
                 rc = cudaMalloc(&absmax, sizeof(float)) == cudaSuccess ? 0 : B200FC_ERR_NOMEM;
                 if (!rc && scales) {  // caller-supplied absmax (e.g. of a larger matrix this one is a slice of)
@@ -438,6 +458,17 @@ int b200fc_weight_unpack(const b200fc_weight_t* h, void* dst, int64_t ld_bytes, 
     const Weight& w = h->w;
     const int es = elem_size(w.dtype);
     cudaStream_t s = (cudaStream_t)stream;
+    if (w.dtype == B200FC_S4) {
+        void* tmp = nullptr;
+        B200FC_CUDA(cudaMalloc(&tmp, (size_t)w.N * w.K));
+        int rc = launch_unpack4(w, tmp, w.K, s);
+        cudaError_t e = rc ? cudaSuccess : cudaMemcpy2DAsync(dst, (size_t)ld_bytes, tmp, (size_t)w.K, (size_t)w.K, (size_t)w.N, cudaMemcpyDefault, s);
+        cudaStreamSynchronize(s);
+        cudaFree(tmp);
+        if (rc) return rc;
+        B200FC_CUDA(e);
+        return B200FC_OK;
+    }
     if (w.compressed) {  // stored offset-binary: hand back two's complement
         void* tmp = nullptr;
         B200FC_CUDA(cudaMalloc(&tmp, (size_t)w.N * w.K));
@@ -455,6 +486,25 @@ int b200fc_weight_unpack(const b200fc_weight_t* h, void* dst, int64_t ld_bytes, 
     return B200FC_OK;
 }
 
+int b200fc_weight_group_scales(const b200fc_weight_t* h, float* host_dst, int64_t ld_bytes, void* stream) {
+    if (!h || !host_dst) { set_error("weight_group_scales: null pointer"); return B200FC_ERR_INVALID; }
+    const Weight& w = h->w;
+    if (w.dtype != B200FC_S4 || !w.scale_grp) { set_error("weight_group_scales: not a 4-bit weight"); return B200FC_ERR_INVALID; }
+    const int groups = (w.K + B200FC_INT4_GROUP - 1) / B200FC_INT4_GROUP;
+    if (ld_bytes < (int64_t)groups * 4) { set_error("weight_group_scales: ld smaller than a row"); return B200FC_ERR_INVALID; }
+    std::vector<float> tmp(w.scale_grp_floats());
+    cudaStream_t s = (cudaStream_t)stream;
+    B200FC_CUDA(cudaMemcpyAsync(tmp.data(), w.scale_grp, tmp.size() * sizeof(float), cudaMemcpyDeviceToHost, s));
+    B200FC_CUDA(cudaStreamSynchronize(s));
+    const int spr = w.K_pad / 256;
+    for (int n = 0; n < w.N; n++) {
+        float* row = (float*)((char*)host_dst + (int64_t)n * ld_bytes);
+        for (int j = 0; j < groups; j++)
+            row[j] = tmp[((((size_t)(n >> 7) * spr) + (j >> 1)) * 2 + (j & 1)) * 128 + (n & 127)];
+    }
+    return B200FC_OK;
+}
+
 // ---- serialised packed weights ----------------------------------------------------------------------------------
 namespace {
 struct BlobHeader {           // 64 bytes, little endian
@@ -469,16 +519,21 @@ struct BlobHeader {           // 64 bytes, little endian
 static_assert(sizeof(BlobHeader) == 64, "blob header layout");
 const char kBlobMagic[8] = {'B', '2', 'F', 'C', 'W', 'G', 'T', '1'};
 
+uint64_t blob_scale_bytes(int has_scales, const Weight& w) {
+    if (has_scales == 2) return (uint64_t)w.scale_grp_floats() * sizeof(float);
+    return has_scales ? (uint64_t)w.N_pad * sizeof(float) : 0;
+}
+
 void fill_blob_header(const Weight& w, BlobHeader* hd) {
     memset(hd, 0, sizeof(*hd));
     memcpy(hd->magic, kBlobMagic, 8);
     hd->header_bytes = 64;
     hd->dtype = w.dtype; hd->K = w.K; hd->N = w.N; hd->K_pad = w.K_pad; hd->N_pad = w.N_pad;
     hd->compressed = w.compressed ? 1 : 0;
-    hd->has_scales = w.scale_per_oc ? 1 : 0;
+    hd->has_scales = w.scale_grp ? 2 : (w.scale_per_oc ? 1 : 0);   // 1: per output channel, 2: per group (4-bit weights)
     hd->deq_scale = w.deq_scale;
-    hd->data_bytes = (uint64_t)w.N_pad * (uint64_t)w.K_pad * (uint64_t)elem_size(w.dtype);
-    hd->total_bytes = 64 + hd->data_bytes + (hd->has_scales ? (uint64_t)w.N_pad * sizeof(float) : 0);
+    hd->data_bytes = (uint64_t)w.data_bytes();
+    hd->total_bytes = 64 + hd->data_bytes + blob_scale_bytes(hd->has_scales, w);
 }
 }  // namespace
 
@@ -504,8 +559,8 @@ int b200fc_weight_export(const b200fc_weight_t* h, void* host_dst, size_t capaci
     memcpy(dst, &hd, sizeof(hd));
     B200FC_CUDA(cudaMemcpyAsync(dst + 64, w.data, (size_t)hd.data_bytes, cudaMemcpyDeviceToHost, s));
     if (hd.has_scales)
-        B200FC_CUDA(cudaMemcpyAsync(dst + 64 + hd.data_bytes, w.scale_per_oc, (size_t)w.N_pad * sizeof(float),
-                                    cudaMemcpyDeviceToHost, s));
+        B200FC_CUDA(cudaMemcpyAsync(dst + 64 + hd.data_bytes, hd.has_scales == 2 ? w.scale_grp : w.scale_per_oc,
+                                    (size_t)blob_scale_bytes(hd.has_scales, w), cudaMemcpyDeviceToHost, s));
     B200FC_CUDA(cudaStreamSynchronize(s));
     return B200FC_OK;
 }
@@ -519,13 +574,20 @@ int b200fc_weight_import(const void* host_src, size_t bytes, b200fc_weight_t** o
         set_error("weight_import: not a packed-weight blob of this library version");
         return B200FC_ERR_INVALID;
     }
-    const int es = (hd.dtype == B200FC_BF16 || hd.dtype == B200FC_S8 || hd.dtype == B200FC_U8) ? elem_size(hd.dtype) : 0;
-    if (!es || hd.K <= 0 || hd.N <= 0) { set_error("weight_import: bad dtype or shape in the header"); return B200FC_ERR_INVALID; }
-    const int K_pad = round_up(hd.K * es, kKPadBytes) / es, N_pad = round_up(hd.N, kRowPad);
-    const uint64_t data_bytes = (uint64_t)N_pad * (uint64_t)K_pad * (uint64_t)es;
-    const uint64_t total = 64 + data_bytes + (hd.has_scales ? (uint64_t)N_pad * sizeof(float) : 0);
+    const bool known = hd.dtype == B200FC_BF16 || hd.dtype == B200FC_S8 || hd.dtype == B200FC_U8 || hd.dtype == B200FC_S4;
+    if (!known || hd.K <= 0 || hd.N <= 0) { set_error("weight_import: bad dtype or shape in the header"); return B200FC_ERR_INVALID; }
+    Weight shape;   // what alloc_weight would make of (K, N, dtype), without allocating
+    shape.K = hd.K; shape.N = hd.N; shape.dtype = hd.dtype;
+    shape.N_pad = round_up(hd.N, kRowPad);
+    shape.K_pad = hd.dtype == B200FC_S4 ? round_up(hd.K, 2 * kKPadBytes) : round_up(hd.K * elem_size(hd.dtype), kKPadBytes) / elem_size(hd.dtype);
+    const int K_pad = shape.K_pad, N_pad = shape.N_pad;
+    const uint64_t data_bytes = (uint64_t)shape.data_bytes();
+    const bool scales_ok = hd.has_scales == 0 || (hd.has_scales == 1 && hd.dtype == B200FC_S8) || (hd.has_scales == 2 && hd.dtype == B200FC_S4);
+    const uint64_t scale_bytes = scales_ok ? blob_scale_bytes(hd.has_scales, shape) : 0;
+    const uint64_t total = 64 + data_bytes + scale_bytes;
     if (hd.K_pad != K_pad || hd.N_pad != N_pad || hd.data_bytes != data_bytes || hd.total_bytes != total || bytes < total ||
-        (hd.compressed && hd.dtype != B200FC_S8) || (hd.has_scales && !hd.compressed)) {
+        (hd.compressed && hd.dtype != B200FC_S8 && hd.dtype != B200FC_S4) || (hd.has_scales && !hd.compressed) || !scales_ok ||
+        (hd.dtype == B200FC_S4 && (hd.has_scales != 2 || !hd.compressed))) {
         set_error("weight_import: header does not describe a blob this library wrote (or the buffer is truncated)");
         return B200FC_ERR_INVALID;
     }
@@ -536,11 +598,14 @@ int b200fc_weight_import(const void* host_src, size_t bytes, b200fc_weight_t** o
     const char* src = (const char*)host_src;
     int rc = alloc_weight(w, hd.K, hd.N, hd.dtype);
     if (!rc && cudaMemcpyAsync(w.data, src + 64, (size_t)data_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess) rc = B200FC_ERR_CUDA;
-    if (!rc && hd.has_scales) {
+    if (!rc && hd.has_scales == 1) {
         if (cudaMalloc(&w.scale_per_oc, (size_t)N_pad * sizeof(float)) != cudaSuccess) rc = B200FC_ERR_NOMEM;
         if (!rc && cudaMemcpyAsync(w.scale_per_oc, src + 64 + data_bytes, (size_t)N_pad * sizeof(float), cudaMemcpyHostToDevice, s) != cudaSuccess)
             rc = B200FC_ERR_CUDA;
     }
+    if (!rc && hd.has_scales == 2 &&
+        cudaMemcpyAsync(w.scale_grp, src + 64 + data_bytes, (size_t)scale_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess)
+        rc = B200FC_ERR_CUDA;
     if (!rc && cudaStreamSynchronize(s) != cudaSuccess) rc = B200FC_ERR_CUDA;
     if (rc) {
         if (rc == B200FC_ERR_NOMEM) set_error("weight_import: out of device memory");

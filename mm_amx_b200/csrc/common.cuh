@@ -13,7 +13,9 @@ namespace b200fc {
 // Packed weights.  One layout serves every kernel: a row-major [N_pad, K_pad] matrix with K contiguous
 // ("K-major"), zero padded.  A 2-D TMA box of it with 128-byte swizzle lands in shared memory in the canonical
 // tcgen05 K-major operand layout; the decode kernels stream its rows with 16-byte loads.
-//   K_pad: multiple of 128 bytes of elements (64 bf16 / 128 int8)     N_pad: multiple of 256 rows
+//   K_pad: multiple of 128 bytes of elements (64 bf16 / 128 int8 / 256 four-bit)     N_pad: multiple of 256 rows
+// 4-bit weights (dtype B200FC_S4) keep the row-major byte matrix, two values per byte, with K permuted inside every
+// 128-byte piece of a row for the decode kernel (see quant4_kernel in pack.cu), and carry group scales.
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int kRowPad = 256;
 constexpr int kKPadBytes = 128;
@@ -26,11 +28,15 @@ struct Weight {
     float deq_scale = 1.0f;         // per-tensor dequant scale of compressed weights
     void* data = nullptr;           // [N_pad, K_pad]
     float* scale_per_oc = nullptr;  // optional [N_pad] per-output-channel dequant scales
+    float* scale_grp = nullptr;     // 4-bit weights: [N_pad / 128][K_pad / 256][2][128] dequant scales, i.e. for every
+                                    // 128-row x 128-byte piece of the packed matrix the 2 x 128 scales it needs, contiguous
     // lazily created scratch / staging owned by the object
     void* stage_A = nullptr; size_t stage_A_bytes = 0;
     void* stage_C = nullptr; size_t stage_C_bytes = 0;
     float* stage_vec = nullptr; size_t stage_vec_floats = 0;
-    int64_t ld_bytes() const { return (int64_t)K_pad * (dtype == B200FC_BF16 ? 2 : 1); }
+    int64_t ld_bytes() const { return dtype == B200FC_S4 ? (int64_t)K_pad / 2 : (int64_t)K_pad * (dtype == B200FC_BF16 ? 2 : 1); }
+    size_t data_bytes() const { return (size_t)N_pad * (size_t)ld_bytes(); }
+    size_t scale_grp_floats() const { return dtype == B200FC_S4 ? (size_t)N_pad * (size_t)(K_pad / 128) : 0; }
 };
 
 // Post-op description handed to kernels (device pointers).
@@ -120,6 +126,9 @@ int launch_quant_pack(const void* B_dev, int K, int N, int64_t ldb, int transpos
                       cudaStream_t s);
 int launch_absmax(const void* B_dev, int rows, int cols, int64_t ldb, float* absmax_dev, cudaStream_t s);
 int launch_dequant_bf16(const Weight& w, int row0, int rows, void* dst_bf16, int dst_K_pad, cudaStream_t s);
+// 4-bit weights: bf16 [N_pad, K_pad] K-major (zero padded) -> w.data / w.scale_grp; and back to one int8 per value
+int launch_quant4(const void* wide_bf16, Weight& w, cudaStream_t s);
+int launch_unpack4(const Weight& w, void* dst_s8, int64_t ldd, cudaStream_t s);
 int launch_copy2d(const void* src, int64_t lds, void* dst, int64_t ldd, int rows, int row_bytes, int dst_row_bytes,
                   cudaStream_t s);
 int launch_add_round_bf16(const float* a, const float* b, void* out, int64_t n, cudaStream_t s);

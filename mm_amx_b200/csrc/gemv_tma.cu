@@ -17,6 +17,12 @@
 //   1024 + v + 128, one subtraction leaves v — one instruction per weight, next to the consumer (the role of the
 //   reference's ping-pong dequantisation buffer).  fp16 because only its 11-bit significand holds all 8 bits; the
 //   activations are converted to fp16 per staged chunk after an exact power-of-two scaling per row.
+//   4-bit weights (two values per byte, a stage holds 256 K of 128 rows = two quantisation groups): masks and one shift
+//   per word build the fp16 numbers 1024 + n and 1024 + 16 n of the nibbles n = v + 8, a subtraction resp. a fused
+//   multiply-add leaves v.  The packing keeps the four lanes of an MMA inside one group, so every stage is multiplied
+//   into a fresh accumulator that is added to the running one times the group's fp32 scale (integer-valued partial
+//   sums: the scale is applied once per group, exactly as the definition of the format says).  The stage's 2 x 128
+//   scales travel beside it (one 1 KB bulk copy on the same barrier).
 //   A piece that ends inside a row block leaves a partial sum: it goes to a slot of a small global scratch, the CTAs
 //   that share the row block count themselves on a counter, and the last one to arrive adds the slots in CTA order
 //   (deterministic) and runs the post-ops.  Nobody waits for anybody.
@@ -63,6 +69,7 @@ struct Params {
     int cluster;          // 1: launched as clusters of S CTAs (S <= 8); the pieces of a row block meet in distributed
                           // shared memory instead of the global scratch
     int pf_cap;           // stages beyond the ring that the producer prefetches into L2 when the CTA starts
+    const float* scales;  // 4-bit weights: [row block][stage][2][128] group scales, row block 0 = packed rows [0, 128)
 #ifdef B200FC_TRACE
     unsigned long long* trace;   // [launch % 64][gridDim.x <= 320][8] globaltimer stamps (timeline studies only)
     int trace_launch;
@@ -167,17 +174,44 @@ __device__ __forceinline__ unsigned u8x2_to_f16x2(unsigned w, unsigned sel) {
     return *(unsigned*)&r;
 }
 
-template <bool W8, int NT> struct Layout {
+__device__ __forceinline__ void bulk_load_1d(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+// (w & mask) | 0x64006400: the two nibbles selected by `mask` as the low bits of two fp16 numbers 1024 + ...
+__device__ __forceinline__ unsigned nib_or_magic(unsigned w, unsigned mask) {
+    unsigned r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xea;" : "=r"(r) : "r"(w), "r"(mask), "r"(0x64006400u));   // (a & b) | c
+    return r;
+}
+// nibbles n at bits [0,4) and [16,20) of w -> f16x2 of n - 8:  (1024 + n) - 1032
+__device__ __forceinline__ unsigned nib_lo_to_f16x2(unsigned w) {
+    const unsigned p = nib_or_magic(w, 0x000f000fu), off = 0x64086408u;   // 1032.0 twice
+    __half2 r = __hsub2(*(const __half2*)&p, *(const __half2*)&off);
+    return *(unsigned*)&r;
+}
+// nibbles n at bits [4,8) and [20,24) of w -> f16x2 of n - 8:  (1024 + 16 n) / 16 - 72
+__device__ __forceinline__ unsigned nib_hi_to_f16x2(unsigned w) {
+    const unsigned p = nib_or_magic(w, 0x00f000f0u), mul = 0x2c002c00u, add = 0xd480d480u;   // 1/16 and -72 twice
+    __half2 r = __hfma2(*(const __half2*)&p, *(const __half2*)&mul, *(const __half2*)&add);
+    return *(unsigned*)&r;
+}
+
+template <int WB, int NT> struct Layout {
+    static constexpr bool WQ = WB != 16;   // quantised weights: activations are staged as fp16
     static constexpr int STAGES = NT == 1 ? 5 : 4;
     static constexpr int MP = 8 * NT;
     // bytes per staged activation row; the pad makes rows g and g + 1 fall into different bank halves for the
     // access pattern of each variant (see the fragment loads in the kernel)
-    static constexpr int XROW = CHUNK_K * 2 + (W8 ? 64 : 16);
+    static constexpr int XROW = CHUNK_K * 2 + (WQ ? 64 : 16);
     static constexpr int RING = STAGES * STAGE_BYTES;
     static constexpr int X_OFF = RING;
     static constexpr int AUX_OFF = X_OFF + MP * XROW;          // smax [MP][CWARPS], sexp [MP]
     static constexpr int EP_OFF = AUX_OFF + MP * (CWARPS + 1) * 4;   // dequant scale, bias, quant scale of 128 rows
-    static constexpr int BAR_OFF = EP_OFF + 3 * ROWS_PER_CTA * 4;
+    static constexpr int SC_OFF = EP_OFF + 3 * ROWS_PER_CTA * 4;     // 4-bit weights: group scales of every ring stage
+    static constexpr int SC_STAGE_BYTES = 2 * ROWS_PER_CTA * 4;
+    static constexpr int BAR_OFF = SC_OFF + (WB == 4 ? STAGES * SC_STAGE_BYTES : 0);
     static constexpr int SMEM = BAR_OFF + 2 * STAGES * 8 + 16 + 1024;  // + barriers, abort flag, last flag, alignment slack
 };
 
@@ -205,13 +239,14 @@ __device__ __forceinline__ float postop_staged(float v, int row, int steps, cons
     return v;
 }
 
-template <bool W8, int NT>
+template <int WB, int NT>
 __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
-    using L = Layout<W8, NT>;
+    using L = Layout<WB, NT>;
+    constexpr bool W8 = WB == 8, W4 = WB == 4, WQ = WB != 16;
     constexpr int MP = L::MP, XROW = L::XROW, STAGES = L::STAGES;
-    constexpr int KE = W8 ? 128 : 64;                 // K elements per stage
+    constexpr int KE = STAGE_K_BYTES * 8 / WB;        // K elements per stage: 64 / 128 / 256
     constexpr int STAGES_PER_CHUNK = CHUNK_K / KE;
-    constexpr int MMA_PER_LOAD = W8 ? 4 : 2;
+    constexpr int MMA_PER_LOAD = 32 / WB;             // MMAs (16 K each) fed by one 16-byte piece of two rows
 
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -262,9 +297,13 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
                     }
                 }
                 if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, limit)) break;
-                mbar_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
+                mbar_expect_tx(bar_full + 8 * stage, STAGE_BYTES + (W4 ? L::SC_STAGE_BYTES : 0));
                 tma_load_2d(smem_u32(smem + stage * STAGE_BYTES), &map_w, bar_full + 8 * stage, ks * STAGE_K_BYTES,
                             p.n0 + rb * ROWS_PER_CTA);
+                if constexpr (W4)
+                    bulk_load_1d(smem_u32(smem + L::SC_OFF + stage * L::SC_STAGE_BYTES),
+                                 p.scales + ((size_t)(p.n0 / ROWS_PER_CTA + rb) * p.spr + ks) * (2 * ROWS_PER_CTA),
+                                 L::SC_STAGE_BYTES, bar_full + 8 * stage);
                 if (++ks == p.spr) { ks = 0; rb++; }
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
@@ -326,7 +365,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
             uint4 v[PASSES];
 #pragma unroll
             for (int i = 0; i < PASSES; i++) v[i] = need ? load_x_unit(row0 + i * ROWS_PER_PASS, k) : make_uint4(0, 0, 0, 0);
-            if constexpr (W8) {
+            if constexpr (WQ) {
 #pragma unroll
                 for (int i = 0; i < PASSES; i++) {
                     const unsigned w4[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
@@ -342,7 +381,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
             for (int i = 0; i < PASSES; i++) {
                 const int row = row0 + i * ROWS_PER_PASS;
                 uint4 o4 = v[i];
-                if constexpr (W8) {
+                if constexpr (WQ) {
                     // the four warps that hold this row: warps 4 * row0 .. 4 * row0 + 3
                     unsigned m = 0;
 #pragma unroll
@@ -362,13 +401,15 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
                     }
                     o4 = make_uint4(o[0], o[1], o[2], o[3]);
                 }
-                // compressed weights: the 16 units of a stage are stored transposed as a 4 x 4 grid, so that the
-                // four lanes t of a fragment load (units 4t + i) touch four neighbouring 16-byte slots
-                const int slot = W8 ? ((unit & ~15) | ((unit & 3) << 2) | ((unit >> 2) & 3)) : unit;
+                // int8 weights: the 16 units of a stage are stored transposed as a 4 x 4 grid, so that the four lanes t
+                // of a fragment load (units 4t + i) touch four neighbouring 16-byte slots; 4-bit weights: the 32 units
+                // of a stage as a 4 x 8 grid (a lane reads units 4 (4h + t) + i, i = 0..3)
+                const int slot = W8 ? ((unit & ~15) | ((unit & 3) << 2) | ((unit >> 2) & 3))
+                               : W4 ? ((unit & ~31) | ((unit & 3) << 3) | ((unit >> 2) & 7)) : unit;
                 if (need) *(uint4*)(xbuf + row * XROW + slot * 16) = o4;
             }
             consumer_sync();
-            if constexpr (W8) {
+            if constexpr (WQ) {
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
                     const int e0 = sexp[nt * 8 + 2 * t], e1 = sexp[nt * 8 + 2 * t + 1];
@@ -453,6 +494,51 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
 
                 const int j = kh;
+                if constexpr (W4) {
+                    // this thread's 32 K of the stage, [128 j + 32 t, +32) — all of group j — sit in four slots 128 bytes apart
+                    const int xoff = it_in_chunk * KE * 2 + (4 * j + t) * 16;
+                    unsigned xb[NT][16];
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) {
+                        const unsigned char* xs = xbuf + (nt * 8 + g) * XROW + xoff;
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const uint4 a = *(const uint4*)(xs + i * 128);
+                            xb[nt][4 * i] = a.x; xb[nt][4 * i + 1] = a.y; xb[nt][4 * i + 2] = a.z; xb[nt][4 * i + 3] = a.w;
+                        }
+                    }
+                    const float* sc = (const float*)(smem + L::SC_OFF + rel_stage * L::SC_STAGE_BYTES) + j * ROWS_PER_CTA + row_base;
+#pragma unroll
+                    for (int rb = 0; rb < RB; rb++) {
+                        const unsigned wa[4] = {w[rb][0].x, w[rb][0].y, w[rb][0].z, w[rb][0].w};
+                        const unsigned wb[4] = {w[rb][1].x, w[rb][1].y, w[rb][1].z, w[rb][1].w};
+                        float grp[NT][4];
+#pragma unroll
+                        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                            for (int c = 0; c < 4; c++) grp[nt][c] = 0.0f;
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+#pragma unroll
+                            for (int hw = 0; hw < 2; hw++) {        // values 0..3 and 4..7 of word i
+                                const unsigned qa = wa[i] >> (8 * hw), qb = wb[i] >> (8 * hw);
+                                const unsigned a0 = nib_lo_to_f16x2(qa), a2 = nib_hi_to_f16x2(qa);
+                                const unsigned a1 = nib_lo_to_f16x2(qb), a3 = nib_hi_to_f16x2(qb);
+#pragma unroll
+                                for (int nt = 0; nt < NT; nt++)
+                                    mma_f16(grp[nt], a0, a1, a2, a3, xb[nt][4 * i + 2 * hw], xb[nt][4 * i + 2 * hw + 1]);
+                            }
+                        }
+                        const float s0 = sc[rb * 16], s1 = sc[rb * 16 + 8];
+#pragma unroll
+                        for (int nt = 0; nt < NT; nt++) {
+                            acc[0][rb][nt][0] = fmaf(grp[nt][0], s0, acc[0][rb][nt][0]);
+                            acc[0][rb][nt][1] = fmaf(grp[nt][1], s0, acc[0][rb][nt][1]);
+                            acc[0][rb][nt][2] = fmaf(grp[nt][2], s1, acc[0][rb][nt][2]);
+                            acc[0][rb][nt][3] = fmaf(grp[nt][3], s1, acc[0][rb][nt][3]);
+                        }
+                    }
+                } else {
                 // activations matching this thread's weight bytes: K elements [(2t + j) * (W8 ? 16 : 8), ...) of the stage
                 const int xoff = W8 ? it_in_chunk * KE * 2 + (8 * j + t) * 16 : (it_in_chunk * KE + (2 * t + j) * 8) * 2;
                 unsigned xb[NT][W8 ? 8 : 4];
@@ -487,6 +573,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
                         }
                     }
                 }
+                }
                 // Release the stage only now that its bytes have gone through the MMAs.  Arriving right after the copies to
                 // registers had been issued (or even after folding them into a dummy value) let the refill overtake them
                 // now and then: single rows of a warp's share then held bytes of the stage four positions later.
@@ -504,7 +591,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
                     for (int nt = 0; nt < NT; nt++)
 #pragma unroll
                         for (int i = 0; i < 4; i++) acc[0][rb][nt][i] += acc[as][rb][nt][i];
-            if constexpr (W8) {
+            if constexpr (WQ) {
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++)
 #pragma unroll
@@ -682,15 +769,15 @@ int device_sms() {
     return n > 0 ? n : 148;
 }
 
-template <bool W8, int NT>
+template <int WB, int NT>
 int launch_variant(const CUtensorMap& map, const Params& p, int grid, cudaStream_t s) {
     const int cluster = p.cluster ? p.S : 1;
-    using L = Layout<W8, NT>;
+    using L = Layout<WB, NT>;
     static_assert(L::MP * L::XROW >= 2 * ROWS_PER_CTA * L::MP * 4, "partial tiles must fit the activation buffer");
     static std::atomic<unsigned long long> attr_devices{0};
     {
         const int arc = once_per_device(attr_devices, [] {
-            B200FC_CUDA(cudaFuncSetAttribute(gemv_tma_kernel<W8, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM));
+            B200FC_CUDA(cudaFuncSetAttribute(gemv_tma_kernel<WB, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM));
             return (int)B200FC_OK;
         });
         if (arc) return arc;
@@ -709,7 +796,7 @@ int launch_variant(const CUtensorMap& map, const Params& p, int grid, cudaStream
     attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    B200FC_CUDA(cudaLaunchKernelEx(&cfg, gemv_tma_kernel<W8, NT>, map, p));
+    B200FC_CUDA(cudaLaunchKernelEx(&cfg, gemv_tma_kernel<WB, NT>, map, p));
     count_launch();
     return B200FC_OK;
 }
@@ -806,9 +893,14 @@ int launch_gemv_tma(const Weight& w, const void* A, int M, int K, int64_t lda, i
     }
     p.counters = (unsigned*)scratch;
     p.slots = (float*)((char*)scratch + (size_t)kGemvMaxCtas * sizeof(unsigned));
+    p.scales = w.scale_grp;
+    if (w.dtype == B200FC_S4) {
+        if (!w.scale_grp || (n0 % ROWS_PER_CTA)) { set_error("gemv: 4-bit weights need group scales and n0 %% 128 == 0"); return B200FC_ERR_INVALID; }
+        return M <= 8 ? launch_variant<4, 1>(map, p, (int)grid, s) : launch_variant<4, 2>(map, p, (int)grid, s);
+    }
     const bool w8 = w.dtype == B200FC_S8;
-    if (M <= 8) return w8 ? launch_variant<true, 1>(map, p, (int)grid, s) : launch_variant<false, 1>(map, p, (int)grid, s);
-    return w8 ? launch_variant<true, 2>(map, p, (int)grid, s) : launch_variant<false, 2>(map, p, (int)grid, s);
+    if (M <= 8) return w8 ? launch_variant<8, 1>(map, p, (int)grid, s) : launch_variant<16, 1>(map, p, (int)grid, s);
+    return w8 ? launch_variant<8, 2>(map, p, (int)grid, s) : launch_variant<16, 2>(map, p, (int)grid, s);
 }
 
 }  // namespace b200fc

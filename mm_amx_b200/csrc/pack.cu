@@ -123,6 +123,85 @@ __global__ void dequant_bf16_kernel(const signed char* __restrict__ src, int K_p
     d[1] = *(int4*)&o[8];
 }
 
+// ---- 4-bit group-quantised weights -----------------------------------------------------------------------------------
+// Stored form: the byte matrix [N_pad, K_pad / 2]; a value v in [-7, 7] is the nibble v + 8.  Every 128-byte piece of a
+// row (256 values, one stage of the decode kernel) holds two groups of 128 K; its eight 16-byte units alternate between
+// them (unit u holds values [32 * (u >> 1), +32) of group u & 1), so that the four lanes whose fragments one MMA of the
+// decode kernel combines (units 2t + h, t = 0..3) stay inside ONE group and the group's scale can be applied to the
+// MMA's sum.  Inside a 32-bit word the eight values k .. k + 7 sit at nibble positions 0, 4, 1, 5, 2, 6, 3, 7: masking
+// with 0x000f000f / 0x00f000f0 (and once more after a shift by 8) then yields K-neighbours as the two halves of a
+// 16-bit pair, the order the MMA fragment wants.
+__device__ __forceinline__ int nibble_pos(int e) { return (e >> 1) + 4 * (e & 1); }
+// first K of the eight values held by the word at byte offset `off` of a packed row
+__device__ __forceinline__ int word_k0(int off) {
+    const int ks = off >> 7, u = (off >> 4) & 7, wq = (off >> 2) & 3;
+    return ks * 256 + (u & 1) * 128 + (u >> 1) * 32 + wq * 8;
+}
+
+// One warp quantises one group (128 consecutive K of one row) of the zero-padded bf16 matrix `wide` [N_pad, K_pad]:
+// absmax -> quant scale 7 / absmax (fp32 division; 0 for an all-zero group) -> round to nearest even, and stores the
+// dequant scale absmax / 7 where the decode kernel's stage finds it.
+__global__ void __launch_bounds__(256) quant4_kernel(const unsigned short* __restrict__ wide, int K_pad, long long groups,
+                                                     unsigned* __restrict__ dst, float* __restrict__ scale_grp) {
+    const long long gi = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (gi >= groups) return;
+    const int lane = threadIdx.x & 31;
+    const int gpr = K_pad / 128;
+    const long long n = gi / gpr;
+    const int j = (int)(gi % gpr);
+    const uint2 raw = *(const uint2*)(wide + n * K_pad + j * 128 + lane * 4);
+    const float f[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u), __uint_as_float(raw.y << 16),
+                        __uint_as_float(raw.y & 0xffff0000u)};
+    float m = fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(fabsf(f[2]), fabsf(f[3])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float qs = m > 0.0f ? __fdiv_rn(7.0f, m) : 0.0f;
+    unsigned word = 0;
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        int v = f32_to_s8(__fmul_rn(f[e], qs));
+        v = v > 7 ? 7 : (v < -7 ? -7 : v);
+        word |= (unsigned)((v + 8) & 15) << (4 * nibble_pos(4 * (lane & 1) + e));
+    }
+    word |= __shfl_xor_sync(0xffffffffu, word, 1);
+    const int ks = j >> 1, gh = j & 1;
+    if (!(lane & 1)) {
+        const int wi = lane >> 1, b = wi >> 2, wq = wi & 3;
+        dst[(n * (K_pad / 2) + ks * 128 + (b * 2 + gh) * 16 + wq * 4) >> 2] = word;
+    }
+    if (lane == 0) scale_grp[((((n >> 7) * (K_pad / 256)) + ks) * 2 + gh) * 128 + (n & 127)] = __fdiv_rn(m, 7.0f);
+}
+
+__device__ __forceinline__ float scale4_at(const float* scale_grp, int K_pad, long long n, int k) {
+    return scale_grp[((((n >> 7) * (K_pad / 256)) + (k >> 8)) * 2 + ((k >> 7) & 1)) * 128 + (n & 127)];
+}
+
+// packed rows [row0, row0 + rows) -> one int8 per value (dst_s8, rows x K) or value * group scale rounded to bf16
+// (dst_bf16, rows x dst_K_pad, zero padded like the source); one 32-bit word (8 values) per thread
+__global__ void unpack4_kernel(const unsigned* __restrict__ src, int K_pad, const float* __restrict__ scale_grp, int row0,
+                               long long words, signed char* __restrict__ dst_s8, long long ldd, int N, int K,
+                               unsigned short* __restrict__ dst_bf16, int dst_K_pad) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= words) return;
+    const int wpr = K_pad / 8;
+    const long long r = i / wpr, n = row0 + r;
+    const int off = (int)(i % wpr) * 4;
+    const unsigned word = src[(n * (K_pad / 2) + off) >> 2];
+    const int k0 = word_k0(off);
+    if (dst_s8) {
+        if (n >= N) return;
+#pragma unroll
+        for (int e = 0; e < 8; e++)
+            if (k0 + e < K) dst_s8[n * ldd + k0 + e] = (signed char)((int)((word >> (4 * nibble_pos(e))) & 15) - 8);
+    } else {
+        const float sc = scale4_at(scale_grp, K_pad, n, k0);
+        __align__(16) unsigned short o[8];
+#pragma unroll
+        for (int e = 0; e < 8; e++) o[e] = f32_to_bf16_bits((float)((int)((word >> (4 * nibble_pos(e))) & 15) - 8) * sc);
+        *(int4*)(dst_bf16 + r * dst_K_pad + k0) = *(int4*)o;
+    }
+}
+
 // row-wise copy with zero fill of [row_bytes, dst_row_bytes): re-strides an activation matrix whose leading
 // dimension or base address does not meet the 16-byte rules of a TMA descriptor.
 __global__ void copy2d_kernel(const char* __restrict__ src, long long lds, char* __restrict__ dst, long long ldd,
@@ -225,8 +304,35 @@ int launch_quant_pack(const void* B, int K, int N, int64_t ldb, int transposeB, 
     return B200FC_OK;
 }
 
+int launch_quant4(const void* wide_bf16, Weight& w, cudaStream_t s) {
+    const long long groups = (long long)w.N_pad * (w.K_pad / 128);
+    quant4_kernel<<<(unsigned)((groups * 32 + 255) / 256), 256, 0, s>>>((const unsigned short*)wide_bf16, w.K_pad, groups,
+                                                                        (unsigned*)w.data, w.scale_grp);
+    count_launch();
+    B200FC_CUDA(cudaGetLastError());
+    return B200FC_OK;
+}
+
+int launch_unpack4(const Weight& w, void* dst_s8, int64_t ldd, cudaStream_t s) {
+    const long long words = (long long)w.N_pad * (w.K_pad / 8);
+    unpack4_kernel<<<(unsigned)((words + 255) / 256), 256, 0, s>>>((const unsigned*)w.data, w.K_pad, w.scale_grp, 0, words,
+                                                                   (signed char*)dst_s8, ldd, w.N, w.K, nullptr, 0);
+    count_launch();
+    B200FC_CUDA(cudaGetLastError());
+    return B200FC_OK;
+}
+
 int launch_dequant_bf16(const Weight& w, int row0, int rows, void* dst, int dst_K_pad, cudaStream_t s) {
     // rows [row0, row0 + rows) of the packed matrix -> dst rows [0, rows)
+    if (w.dtype == B200FC_S4) {
+        const long long words = (long long)rows * (w.K_pad / 8);
+        unpack4_kernel<<<(unsigned)((words + 255) / 256), 256, 0, s>>>((const unsigned*)w.data, w.K_pad, w.scale_grp, row0,
+                                                                       words, nullptr, 0, w.N, w.K, (unsigned short*)dst,
+                                                                       dst_K_pad);
+        count_launch();
+        B200FC_CUDA(cudaGetLastError());
+        return B200FC_OK;
+    }
     long long total16 = (long long)rows * (w.K_pad / 16);
     int block = 256;
     long long grid = (total16 + block - 1) / block;

@@ -160,3 +160,49 @@ def mlp_block(x, gate, up, down, eps, norm_weight=None, add_residual=True):
     if add_residual:
         part = part + bf16_to_f32(np.ascontiguousarray(x, np.uint16))
     return bf16_bits(part)
+
+
+# ---- 4-bit group-quantised weights ------------------------------------------------------------------------------------
+# The reference reserves a Weight_INT4 precision (main.cpp:36) and measures only an upper bound with a dequantisation
+# that does no arithmetic (fake_dequant_i4_16x32, weight_compression/wcompress.hpp:122-134); it defines no 4-bit
+# algorithm.  PARITY UNPINNED: the scheme below is this library's own, the per-tensor int8 scheme of
+# Matmul<bf16,int8_t,float> (include/kernels_amx.hpp:1363-1377: absmax, quant scale = range / absmax, round to
+# nearest even, dequant scale = absmax / range) applied per output channel and group of 128 consecutive K.
+INT4_GROUP = 128
+
+
+def quantize_weight_int4(W, group=INT4_GROUP):
+    """bf16 bits [N, K] -> (int8 [N, K] with values in [-7, 7], fp32 dequant scales [N, ceil(K / group)])."""
+    w = bf16_to_f32(np.ascontiguousarray(W, np.uint16))
+    N, K = w.shape
+    G = (K + group - 1) // group
+    wp = np.zeros((N, G * group), np.float32)
+    wp[:, :K] = w
+    wp = wp.reshape(N, G, group)
+    a = np.abs(wp).max(axis=2)                                            # fp32, exact
+    with np.errstate(divide="ignore"):
+        qs = np.where(a > 0, np.float32(7.0) / a, np.float32(0.0)).astype(np.float32)   # fp32 division
+    q = np.clip(np.rint(wp * qs[:, :, None]), -7, 7).astype(np.int8)      # fp32 product, round to nearest even
+    d = (a / np.float32(7.0)).astype(np.float32)
+    return q.reshape(N, G * group)[:, :K].copy(), d
+
+
+def dequant_int4(q, scales, group=INT4_GROUP):
+    """(int8 [N, K], fp32 [N, G]) -> fp32 [N, K]: value * scale of its group (one fp32 product)."""
+    N, K = q.shape
+    s = np.repeat(scales, group, axis=1)[:, :K]
+    return q.astype(np.float32) * s
+
+
+def gemm_bf16_w4(A, q, scales, group=INT4_GROUP):
+    """bf16 bits A [M, K] x 4-bit weights (q [N, K], scales [N, G]) -> fp32 [M, N]: the integer-valued products of a
+    group are summed first (exactly, float64), each group sum is scaled once, the scaled sums are added."""
+    a = bf16_to_f32(np.ascontiguousarray(A, np.uint16)).astype(np.float64)
+    M, K = a.shape
+    N = q.shape[0]
+    G = scales.shape[1]
+    acc = np.zeros((M, N), np.float64)
+    for j in range(G):
+        k0, k1 = j * group, min(K, (j + 1) * group)
+        acc += (a[:, k0:k1] @ q[:, k0:k1].astype(np.float64).T) * scales[:, j].astype(np.float64)[None, :]
+    return acc.astype(np.float32)

@@ -14,6 +14,7 @@ import pytest
 from oracle import port
 from oracle._common import bf16_bits, bf16_to_f32
 import golden_cases as gc
+import helpers as H
 
 GOLD = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "golden_v1.npz"))
 
@@ -124,3 +125,29 @@ def test_rmsnorm_oracle_matches_the_reference_script_definition():
     got = port.rmsnorm(xb, 1e-6)
     assert np.abs(got.astype(np.int32) - want_bits.astype(np.int32)).max() <= 1
     assert (got == want_bits).mean() > 0.99
+
+
+def test_int4_group_quantiser_properties():
+    """The 4-bit scheme has no reference counterpart (parity unpinned); pin the restatement to its definition:
+    group absmax maps to +-7, every value is within half a step of the original, zero groups stay zero."""
+    rng = np.random.default_rng(44)
+    N, K = 24, 300                                   # last group ragged (300 = 2 * 128 + 44)
+    W = H.normal_bf16(rng, (N, K), std=0.02)
+    W[3, 128:256] = 0                                # an all-zero group
+    q, d = port.quantize_weight_int4(W)
+    w = bf16_to_f32(W)
+    assert q.shape == (N, K) and q.dtype == np.int8 and d.shape == (N, 3) and d.dtype == np.float32
+    assert q.min() >= -7 and q.max() <= 7
+    assert d[3, 1] == 0 and not q[3, 128:256].any()
+    for j, (k0, k1) in enumerate([(0, 128), (128, 256), (256, 300)]):
+        a = np.abs(w[:, k0:k1]).max(axis=1)
+        assert np.array_equal(d[:, j], a / np.float32(7))
+        hit = np.abs(q[:, k0:k1]).max(axis=1)
+        assert np.all(hit[a > 0] == 7)
+        err = np.abs(port.dequant_int4(q, d)[:, k0:k1] - w[:, k0:k1])
+        assert np.all(err <= 0.5 * d[:, j][:, None] * (1 + 1e-6))
+    # the product: per-group integer sums scaled once == a plain product with the dequantised matrix (fp64 both)
+    x = H.normal_bf16(rng, (5, K))
+    ref = bf16_to_f32(x).astype(np.float64) @ port.dequant_int4(q, d).astype(np.float64).T
+    got = port.gemm_bf16_w4(x, q, d)
+    assert np.allclose(got, ref, rtol=1e-5, atol=1e-6)
