@@ -240,6 +240,29 @@ int b200fc_mlp_run_block(b200fc_mlp_t* mlp, const void* x, int64_t ldx_bytes, in
 /* device pointer to the [M, N/tp] bf16 activation of the last run (debug / layer-wise parity) */
 const void* b200fc_mlp_act(const b200fc_mlp_t* mlp);
 
+/* ---- decode attention: one query token per sequence against a bf16 key/value cache --------------------------------- */
+/* out[b, h, :] = sum_n softmax_n(scale * q[b, h, :] . k[b, h / G, n, :]) * v[b, h / G, n, :],  n < len(b),  G = H / Hkv.
+ * The reference's pieces grown into one kernel: w = query x Key^T on the AMX unit (MatMulVec_AMX, test_jit.cpp:17-95;
+ * MatmulVector, include/kernels_amx.hpp:959-1042) and the one-token attention that cuts the key range into blocks,
+ * encodes each into a sub-state (score maximum, sum of exponentials, weighted values) and combines the sub-states
+ * (MHA2Kernels, include/kernels_mha.hpp:146-270: fp32, q {B,1,H,K}, k and v {B,H,N,K}, softmax without a scale
+ * factor — pass scale = 1 for that).  Here q, k, v are bf16, the softmax runs in fp32, G query heads may share one kv
+ * head (G <= 16; the reference has G = 1), sequences may have their own lengths, and all strides are explicit.
+ * D must be 64 or 128; k, v and their strides 16-byte aligned.  A sequence of length 0 yields zeros. */
+typedef struct {
+    int B, H, Hkv, N, D;            /* sequences, query heads, kv heads, cache length (tokens), head size */
+    const void* q;                  /* [B, H, D] bf16 */
+    int64_t q_batch_stride, q_head_stride;                 /* bytes */
+    const void* k; const void* v;   /* [B, Hkv, N, D] bf16 each */
+    int64_t kv_batch_stride, kv_head_stride, kv_token_stride;   /* bytes, the same for k and v */
+    void* out;                      /* [B, H, D] in out_dtype (B200FC_BF16 or B200FC_F32) */
+    int64_t out_batch_stride, out_head_stride;
+    int out_dtype;
+    const int32_t* seq_lens;        /* optional device array [B]: tokens of sequence b (clamped to [0, N]); NULL = N */
+    float scale;
+} b200fc_attention_t;
+int b200fc_decode_attention(const b200fc_attention_t* a, void* stream);
+
 /* ---- device memory for callers that do not link the CUDA runtime themselves ------------------------------------ */
 int b200fc_device_malloc(void** ptr, int64_t bytes);
 int b200fc_device_free(void* ptr);

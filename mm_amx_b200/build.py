@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libb200fc.so")
-SOURCES = ["api.cu", "pack.cu", "gemv_tma.cu", "gemm_tc.cu", "matvec.cu", "mlp_static.cu"]
+SOURCES = ["api.cu", "pack.cu", "gemv_tma.cu", "gemm_tc.cu", "matvec.cu", "mlp_static.cu", "attention.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 HOST_CXX = "/usr/bin/g++"
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

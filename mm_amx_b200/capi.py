@@ -28,6 +28,15 @@ class AllReduce(ctypes.Structure):
                 ("comm_sms", c_int)]
 
 
+class Attention(ctypes.Structure):
+    """b200fc_attention_t"""
+    _fields_ = [("B", c_int), ("H", c_int), ("Hkv", c_int), ("N", c_int), ("D", c_int), ("q", c_void_p),
+                ("q_batch_stride", c_i64), ("q_head_stride", c_i64), ("k", c_void_p), ("v", c_void_p),
+                ("kv_batch_stride", c_i64), ("kv_head_stride", c_i64), ("kv_token_stride", c_i64), ("out", c_void_p),
+                ("out_batch_stride", c_i64), ("out_head_stride", c_i64), ("out_dtype", c_int), ("seq_lens", c_void_p),
+                ("scale", c_float)]
+
+
 # name -> (restype, argtypes); every symbol include/b200fc.h declares
 SIGNATURES = {
     "b200fc_last_error": (ctypes.c_char_p, []),
@@ -71,6 +80,7 @@ SIGNATURES = {
     "b200fc_mlp_decode_static_capacity": (c_i64, []),
     "b200fc_mlp_decode_static_footprint": (c_i64, []),
     "b200fc_mlp_act": (c_void_p, [c_void_p]),
+    "b200fc_decode_attention": (c_int, [ctypes.POINTER(Attention), c_void_p]),
     "b200fc_device_malloc": (c_int, [ctypes.POINTER(c_void_p), c_i64]),
     "b200fc_device_free": (c_int, [c_void_p]),
     "b200fc_memcpy": (c_int, [c_void_p, c_void_p, c_i64, c_void_p]),
@@ -272,6 +282,11 @@ def memcpy(dst_ptr, src_ptr, nbytes, stream=None):
 
 def rmsnorm(x_ptr, ldx_bytes, M, K, eps, out_ptr, ldo_bytes, weight_ptr=None, stream=None):
     check(lib().b200fc_rmsnorm(x_ptr, ldx_bytes, M, K, weight_ptr, eps, out_ptr, ldo_bytes, stream))
+
+
+def decode_attention(desc, stream=None):
+    """desc: capi.Attention; see b200fc_decode_attention in include/b200fc.h."""
+    check(lib().b200fc_decode_attention(ctypes.byref(desc), stream))
 
 
 def add_round_bf16(a_ptr, b_ptr, out_ptr, n, stream=None):

@@ -886,6 +886,11 @@ int b200fc_mlp_run_block(b200fc_mlp_t* h, const void* x, int64_t ldx, int M, flo
 
 const void* b200fc_mlp_act(const b200fc_mlp_t* h) { return h ? h->m.act : nullptr; }
 
+int b200fc_decode_attention(const b200fc_attention_t* a, void* stream) {
+    if (!a) { set_error("decode_attention: null descriptor"); return B200FC_ERR_INVALID; }
+    return launch_decode_attention(*a, (cudaStream_t)stream);
+}
+
 int b200fc_device_malloc(void** ptr, int64_t bytes) {
     if (!ptr || bytes < 0) { set_error("device_malloc: bad argument"); return B200FC_ERR_INVALID; }
     B200FC_CUDA(cudaMalloc(ptr, (size_t)(bytes > 0 ? bytes : 1)));

@@ -95,7 +95,8 @@ void count_launch(int n = 1);
 int* kernel_status_word();  // device int, 0 = OK; kernels store a non-zero code when a bounded wait runs out
 int check_kernel_status(cudaStream_t s);  // synchronises and reads it
 // growing device scratch owned by (device, stream, slot): work on one stream is ordered, so kernels launched on it
-// may share it; slot 0 = re-strided activations, slot 1 = split-K partial tiles of the GEMM
+// may share it; slot 0 = re-strided activations, slot 1 = split-K partial tiles of the GEMM, 3 = widened weight
+// rows, 4 = normalised activations of the MLP block, 5 = sub-states of the decode attention
 int get_stream_scratch(size_t bytes, cudaStream_t s, int slot, void** out);
 // the decode kernel's scratch for stream s (gemv_scratch_bytes(), counters zero); never re-allocated once handed out
 int get_gemv_scratch(cudaStream_t s, void** out);
@@ -158,6 +159,8 @@ struct AllReduceDesc {
 };
 int launch_gemm_tc_allreduce(const void* W_data, int W_K_pad, int W_N_pad, const void* A, int M, int K, int64_t lda,
                              int N, const AllReduceDesc& ar, cudaStream_t s);
+// attention.cu
+int launch_decode_attention(const b200fc_attention_t& a, cudaStream_t s);
 // matvec.cu
 int launch_matvec(const void* A, int dtype, int M, int K, int64_t lda, const void* b, void* c, cudaStream_t s);
 

@@ -206,3 +206,28 @@ def gemm_bf16_w4(A, q, scales, group=INT4_GROUP):
         k0, k1 = j * group, min(K, (j + 1) * group)
         acc += (a[:, k0:k1] @ q[:, k0:k1].astype(np.float64).T) * scales[:, j].astype(np.float64)[None, :]
     return acc.astype(np.float32)
+
+
+# ---- decode attention ---------------------------------------------------------------------------------------------------
+def decode_attention(q, k, v, scale=1.0, seq_lens=None):
+    """One query token per sequence: q [B, H, D], k and v [B, Hkv, N, D] (bf16 bits) -> fp32 [B, H, D].
+    Restates one_head_attention of the reference (include/kernels_mha.hpp:325-355: scores = q k^T, softmax over the
+    keys, weighted sum of the values; the reference applies no scale, i.e. scale = 1) in float64, with query head h
+    reading kv head h // (H // Hkv) and an optional per-sequence length.  PARITY UNPINNED: the reference's kernel is
+    fp32 AVX2 code outside the compiled oracle; this is the textbook definition it implements."""
+    qf = bf16_to_f32(np.ascontiguousarray(q, np.uint16)).astype(np.float64)
+    kf = bf16_to_f32(np.ascontiguousarray(k, np.uint16)).astype(np.float64)
+    vf = bf16_to_f32(np.ascontiguousarray(v, np.uint16)).astype(np.float64)
+    B, H, D = qf.shape
+    Hkv, N = kf.shape[1], kf.shape[2]
+    G = H // Hkv
+    out = np.zeros((B, H, D), np.float64)
+    for b in range(B):
+        n = N if seq_lens is None else int(min(max(seq_lens[b], 0), N))
+        if n == 0:
+            continue
+        for h in range(H):
+            s = scale * (kf[b, h // G, :n] @ qf[b, h])
+            p = np.exp(s - s.max())
+            out[b, h] = (p / p.sum()) @ vf[b, h // G, :n]
+    return out.astype(np.float32)
