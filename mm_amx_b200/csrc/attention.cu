@@ -87,7 +87,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) decode_attention_kernel(const 
     constexpr int CHUNKS = D / 8;          // 16-byte chunks per token row
     constexpr int KSTEPS = D / 16;
     extern __shared__ unsigned char att_smem_raw[];
-    unsigned char* smem = (unsigned char*)(((uintptr_t)att_smem_raw + 127) & ~(uintptr_t)127);
+    // aligned by pointer arithmetic on the __shared__ array (an integer round trip would turn every access generic)
+    unsigned char* smem = att_smem_raw + (((smem_addr(att_smem_raw) + 127u) & ~127u) - smem_addr(att_smem_raw));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;

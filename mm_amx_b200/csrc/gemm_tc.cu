@@ -386,7 +386,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     using C = Cfg<BN>;
     extern __shared__ unsigned char smem_raw[];
     // operand stages need 1024-byte alignment (128-byte swizzle atom = 8 rows x 128 bytes)
-    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // (pointer arithmetic on the __shared__ array, not an integer round trip: the accesses stay shared-space loads / stores)
+    unsigned char* smem = smem_raw + (((smem_u32(smem_raw) + 1023u) & ~1023u) - smem_u32(smem_raw));
     unsigned long long* bars = (unsigned long long*)(smem + C::STAGES * C::STAGE_BYTES);
     // barrier slots: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
     const unsigned bar_full = smem_u32(bars);
@@ -670,7 +671,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const GemmParams p) {
     using C = Cfg2<BN>;
     extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // (pointer arithmetic on the __shared__ array, not an integer round trip: the accesses stay shared-space loads / stores)
+    unsigned char* smem = smem_raw + (((smem_u32(smem_raw) + 1023u) & ~1023u) - smem_u32(smem_raw));
     unsigned long long* bars = (unsigned long long*)(smem + C::STAGES * C::STAGE_BYTES);
     const unsigned bar_full = smem_u32(bars);
     const unsigned bar_empty = smem_u32(bars + C::STAGES);

@@ -48,7 +48,6 @@ constexpr int ROWS_PER_WARP = 32;               // a warp owns 32 rows x one 64-
 constexpr int ROWS_PER_CTA = (CWARPS / 2) * ROWS_PER_WARP;  // 128
 constexpr int STAGE_K_BYTES = 128;              // bytes of K per row and stage (one swizzle atom)
 constexpr int STAGE_BYTES = ROWS_PER_CTA * STAGE_K_BYTES;  // 16 KB
-constexpr int CHUNK_K = 1024;                   // activation elements staged per chunk
 constexpr int THREADS = (CWARPS + 1) * 32;
 constexpr int SLOT_FLOATS = 16 * ROWS_PER_CTA;  // one partial-sum slot: [16 activation rows][128 weight rows] fp32
 
@@ -108,13 +107,20 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
         : "memory");
     return ok != 0;
 }
+// Bounded wait.  try_wait itself suspends the thread for a while, so the loop is not hot; the clock and the abort flag
+// are looked at only after a batch of failed attempts (reading %globaltimer is slow, and doing it after every failed
+// attempt delayed the moment a consumer notices its stage by that much).
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, unsigned long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer();
+    unsigned long long t0 = 0;
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+        for (int i = 0; i < 16; i++)
+            if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (globaltimer() - t0 > limit) {
+        const unsigned long long now = globaltimer();
+        if (t0 == 0) t0 = now;
+        if (now - t0 > limit) {
             *abort_flag = 1;
             return false;
         }
@@ -174,6 +180,9 @@ __device__ __forceinline__ unsigned u8x2_to_f16x2(unsigned w, unsigned sel) {
     return *(unsigned*)&r;
 }
 
+__device__ __forceinline__ void cp_async16(unsigned dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
 __device__ __forceinline__ void bulk_load_1d(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
@@ -200,18 +209,23 @@ __device__ __forceinline__ unsigned nib_hi_to_f16x2(unsigned w) {
 
 template <int WB, int NT> struct Layout {
     static constexpr bool WQ = WB != 16;   // quantised weights: activations are staged as fp16
-    static constexpr int STAGES = NT == 1 ? 5 : 4;
+    static constexpr int STAGES = (NT == 1 && !WQ) ? 5 : 4;
     static constexpr int MP = 8 * NT;
+    // activation elements staged per chunk; quantised weights keep a second, raw copy of the NEXT chunk (see RAW_OFF)
+    static constexpr int CHUNK = (WQ && NT == 2) ? 512 : 1024;
     // bytes per staged activation row; the pad makes rows g and g + 1 fall into different bank halves for the
     // access pattern of each variant (see the fragment loads in the kernel)
-    static constexpr int XROW = CHUNK_K * 2 + (WQ ? 64 : 16);
+    static constexpr int XROW = CHUNK * 2 + (WQ ? 64 : 16);
     static constexpr int RING = STAGES * STAGE_BYTES;
     static constexpr int X_OFF = RING;
     static constexpr int AUX_OFF = X_OFF + MP * XROW;          // smax [MP][CWARPS], sexp [MP]
     static constexpr int EP_OFF = AUX_OFF + MP * (CWARPS + 1) * 4;   // dequant scale, bias, quant scale of 128 rows
     static constexpr int SC_OFF = EP_OFF + 3 * ROWS_PER_CTA * 4;     // 4-bit weights: group scales of every ring stage
     static constexpr int SC_STAGE_BYTES = 2 * ROWS_PER_CTA * 4;
-    static constexpr int BAR_OFF = SC_OFF + (WB == 4 ? STAGES * SC_STAGE_BYTES : 0);
+    // quantised weights: the next chunk's activations as they lie in global memory (bf16), fetched with cp.async while
+    // the current chunk is multiplied; every thread copies, reads back and overwrites only its own 16-byte units
+    static constexpr int RAW_OFF = SC_OFF + (WB == 4 ? STAGES * SC_STAGE_BYTES : 0);
+    static constexpr int BAR_OFF = RAW_OFF + (WQ ? MP * CHUNK * 2 : 0);
     static constexpr int SMEM = BAR_OFF + 2 * STAGES * 8 + 16 + 1024;  // + barriers, abort flag, last flag, alignment slack
 };
 
@@ -245,11 +259,14 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
     constexpr bool W8 = WB == 8, W4 = WB == 4, WQ = WB != 16;
     constexpr int MP = L::MP, XROW = L::XROW, STAGES = L::STAGES;
     constexpr int KE = STAGE_K_BYTES * 8 / WB;        // K elements per stage: 64 / 128 / 256
+    constexpr int CHUNK_K = L::CHUNK;
     constexpr int STAGES_PER_CHUNK = CHUNK_K / KE;
     constexpr int MMA_PER_LOAD = 32 / WB;             // MMAs (16 K each) fed by one 16-byte piece of two rows
 
     extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // aligned to 1024 bytes by pointer arithmetic on the __shared__ array itself: through an integer round trip the
+    // compiler loses the address space and every access below becomes a generic load / store (slower, 64-bit addresses)
+    unsigned char* smem = smem_raw + (((smem_u32(smem_raw) + 1023u) & ~1023u) - smem_u32(smem_raw));
     unsigned char* xbuf = smem + L::X_OFF;
     unsigned* smax = (unsigned*)(smem + L::AUX_OFF);
     int* sexp = (int*)(smem + L::AUX_OFF + MP * CWARPS * 4);
@@ -350,21 +367,57 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
         // new chunk brings a different one; the scale is undone after the last stage of a piece.
         int cur_e[NT][2];
 
-        // Stages CHUNK_K activation elements of all MP rows, starting at stage ks of a row: 128 sixteen-byte units per
-        // row, the 256 consumer threads take two rows per pass.  All loads of a thread are issued before the first is
-        // converted / stored.
-        constexpr int UNITS = CHUNK_K / 8;                    // 128
-        constexpr int ROWS_PER_PASS = CTHREADS / UNITS;       // 2
+        // Stages CHUNK_K activation elements of all MP rows, starting at stage ks of a row: UNITS sixteen-byte units per
+        // row, the 256 consumer threads take ROWS_PER_PASS rows per pass.  All loads of a thread are issued before the
+        // first is converted / stored.
+        constexpr int UNITS = CHUNK_K / 8;                    // 128 or 64
+        constexpr int ROWS_PER_PASS = CTHREADS / UNITS;       // 2 or 4
         constexpr int PASSES = MP / ROWS_PER_PASS;
+        constexpr int WPR = UNITS / 32;                       // consumer warps that share one activation row
         const int unit = ctid % UNITS, row0 = ctid / UNITS;
-        auto stage_x = [&](int ks, int ks_end) {
+        unsigned char* xraw = smem + L::RAW_OFF;
+        // Quantised weights: asks for the chunk that starts at stage ks (this thread's units of it) to be copied into the
+        // raw buffer.  Called for the first chunk of a piece right before it is staged, and for every later chunk right
+        // after the previous one has been staged, so that the copy runs under a whole chunk of multiplications: the
+        // global-memory latency of the activations (about a microsecond while the weight stream saturates the memory
+        // system) otherwise stops all eight warps at every chunk boundary.
+        auto prefetch_x = [&](int ks, int ks_end) {
+            if constexpr (WQ) {
+                if (x_fast) {
+                    const int k = ks * KE + unit * 8;
+                    if (k < ks_end * KE && k < p.K) {
+#pragma unroll
+                        for (int i = 0; i < PASSES; i++) {
+                            const int row = row0 + i * ROWS_PER_PASS;
+                            if (row < p.M)
+                                cp_async16(smem_u32(xraw + (row * UNITS + unit) * 16), p.X + (long long)row * p.ldx + (long long)k * 2);
+                        }
+                    }
+                    asm volatile("cp.async.commit_group;" ::: "memory");
+                }
+            }
+        };
+        auto stage_x = [&](int ks, int ks_end, bool more) {
             const int k = ks * KE + unit * 8;
             const bool need = k < ks_end * KE;
-            consumer_sync();  // everyone is done with the previous chunk
+            const bool raw = WQ && x_fast;
+            // bf16 weights store right after the loads: everyone must be done with the previous chunk first.  The raw path
+            // stores only after the barrier that follows the maximum search, which no warp reaches before it has finished
+            // the previous chunk.
+            if (!raw) consumer_sync();
             if (threadIdx.x == 0 && ks * KE < CHUNK_K) TRACE_STAMP(6);   // staging of a first chunk begins
             uint4 v[PASSES];
+            if (raw) {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
 #pragma unroll
-            for (int i = 0; i < PASSES; i++) v[i] = need ? load_x_unit(row0 + i * ROWS_PER_PASS, k) : make_uint4(0, 0, 0, 0);
+                for (int i = 0; i < PASSES; i++) {
+                    const int row = row0 + i * ROWS_PER_PASS;
+                    v[i] = (need && row < p.M && k < p.K) ? *(const uint4*)(xraw + (row * UNITS + unit) * 16) : make_uint4(0, 0, 0, 0);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < PASSES; i++) v[i] = need ? load_x_unit(row0 + i * ROWS_PER_PASS, k) : make_uint4(0, 0, 0, 0);
+            }
             if constexpr (WQ) {
 #pragma unroll
                 for (int i = 0; i < PASSES; i++) {
@@ -373,19 +426,21 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
 #pragma unroll
                     for (int q = 0; q < 4; q++) m = max(m, max(w4[q] & 0x7fffu, (w4[q] >> 16) & 0x7fffu));
                     m = __reduce_max_sync(0xffffffffu, m);
-                    if (lane == 0) smax[(row0 + i * ROWS_PER_PASS) * CWARPS + warp] = m;   // 4 of the 8 slots per row
+                    if (lane == 0) smax[(row0 + i * ROWS_PER_PASS) * CWARPS + warp] = m;   // WPR of the 8 slots per row
                 }
                 consumer_sync();
+                // the raw values are in registers: the same units may now receive the next chunk
+                if (more) prefetch_x(ks + STAGES_PER_CHUNK, ks_end);
             }
 #pragma unroll
             for (int i = 0; i < PASSES; i++) {
                 const int row = row0 + i * ROWS_PER_PASS;
                 uint4 o4 = v[i];
                 if constexpr (WQ) {
-                    // the four warps that hold this row: warps 4 * row0 .. 4 * row0 + 3
+                    // the warps that hold this row: warps WPR * row0 .. WPR * row0 + WPR - 1
                     unsigned m = 0;
 #pragma unroll
-                    for (int q = 0; q < 4; q++) m = max(m, smax[row * CWARPS + row0 * 4 + q]);
+                    for (int q = 0; q < WPR; q++) m = max(m, smax[row * CWARPS + row0 * WPR + q]);
                     int field = (int)(m >> 7);          // biased exponent of the largest magnitude (bf16 layout)
                     field = field < 1 ? 1 : field;
                     int e = field - 127 - 13;
@@ -473,7 +528,10 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
             }
             for (int ks = ks0; ks < ks1; ks++) {
                 const int it_in_chunk = (ks - ks0) % STAGES_PER_CHUNK;
-                if (it_in_chunk == 0) stage_x(ks, ks1);
+                if (it_in_chunk == 0) {
+                    if (ks == ks0) prefetch_x(ks, ks1);                       // nothing was in flight for a piece's first chunk
+                    stage_x(ks, ks1, ks + STAGES_PER_CHUNK < ks1);
+                }
                 if (ks == ks0 && ctid < ROWS_PER_CTA) {
                     // (the first barrier of stage_x has been passed: nobody still reads the previous piece's vectors)
                     s_ep[ctid] = ep_deq; s_ep[ROWS_PER_CTA + ctid] = ep_bias; s_ep[2 * ROWS_PER_CTA + ctid] = ep_q;
