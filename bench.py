@@ -627,7 +627,8 @@ def decode_legs(torch, mlp, x, w, peaks):
 
 def other_configs(torch, capi, dev, peaks, only=None):
     """Single bf16 Linear (M=256, +bias, fp32 out), int8-weight decode GEMV (K=4096, N in {4096, 11008}, M in
-    {1, 4, 16}), int8 GEMM 2048x4096x4096 with quantised post-ops.  Each case rotates over enough independently packed
+    {1, 4, 16}), the same for 4-bit group-quantised weights, decode attention over a bf16 key/value cache, int8 GEMM
+    2048x4096x4096 with quantised post-ops.  Each case rotates over enough independently packed
     weight sets to exceed L2 several times and is timed as one CUDA graph (kernels of a few microseconds).
     `only` (--case): run just the case of that name, with plain launches (no graph) — the form a profiler is pointed at."""
     out = {}
@@ -738,6 +739,24 @@ def other_configs(torch, capi, dev, peaks, only=None):
             out["int4w_gemv_M%d_%dx%d" % (M, K, N)] = {"us": t * 1e6, "gbs": nbytes / t / 1e9,
                                                        "hbm_frac": nbytes / t / 1e9 / peaks["hbm_gbs"], "weight_sets": nset}
         del ws
+    # decode attention over a bf16 key/value cache (one query token per sequence): bytes = K and V once + q + out
+    for (B, Hq, Hkv, N, D) in ((16, 32, 32, 2048, 128), (16, 64, 8, 4096, 128), (1, 32, 32, 4096, 128)):
+        key = "decode_attention_B%d_H%d_Hkv%d_N%d_D%d" % (B, Hq, Hkv, N, D)
+        if not want(key):
+            continue
+        kv_bytes = 2 * B * Hkv * N * D * 2
+        nset = max(2, int(600e6 / kv_bytes) + 1) if only is None else 2
+        caches = [(torch.randn((B, Hkv, N, D), generator=g, device=dev).to(torch.bfloat16),
+                   torch.randn((B, Hkv, N, D), generator=g, device=dev).to(torch.bfloat16)) for _ in range(nset)]
+        q = torch.randn((B, Hq, D), generator=g, device=dev).to(torch.bfloat16)
+        o = torch.empty((B, Hq, D), dtype=torch.bfloat16, device=dev)
+        descs = [capi.Attention(B, Hq, Hkv, N, D, q.data_ptr(), Hq * D * 2, D * 2, kc.data_ptr(), vc.data_ptr(),
+                                Hkv * N * D * 2, N * D * 2, D * 2, o.data_ptr(), Hq * D * 2, D * 2, capi.BF16, None,
+                                float(D) ** -0.5) for kc, vc in caches]
+        t = timed_graph(lambda s: [capi.decode_attention(dsc, stream=s) for dsc in descs], nset)
+        nbytes = kv_bytes + 2 * B * Hq * D * 2
+        out[key] = {"us": t * 1e6, "gbs": nbytes / t / 1e9, "hbm_frac": nbytes / t / 1e9 / peaks["hbm_gbs"], "caches": nset}
+        del caches, descs
     # config 4: int8 x int8 GEMM with quantised post-ops
     M, K, N = 2048, 4096, 4096
     if only is not None and not only.startswith("int8_gemm_2048x4096x4096_"):

@@ -106,20 +106,6 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) decode_attention_kernel(const 
     n_end = n_end > len ? len : n_end;
     const int nblocks = n_end > n_begin ? (n_end - n_begin + BLK - 1) / BLK : 0;
 
-    // ---- Q fragments: rows = the G query heads of this kv head (padded to 16 with zeros) ----
-    unsigned qa[KSTEPS][4];
-    {
-        const unsigned char* qb = p.q + (long long)b * p.q_bs + (long long)(hkv * G) * p.q_hs;
-#pragma unroll
-        for (int ks = 0; ks < KSTEPS; ks++) {
-            const int d0 = ks * 16 + 2 * t;
-            qa[ks][0] = g < G ? *(const unsigned*)(qb + (long long)g * p.q_hs + d0 * 2) : 0u;
-            qa[ks][1] = g + 8 < G ? *(const unsigned*)(qb + (long long)(g + 8) * p.q_hs + d0 * 2) : 0u;
-            qa[ks][2] = g < G ? *(const unsigned*)(qb + (long long)g * p.q_hs + (d0 + 8) * 2) : 0u;
-            qa[ks][3] = g + 8 < G ? *(const unsigned*)(qb + (long long)(g + 8) * p.q_hs + (d0 + 8) * 2) : 0u;
-        }
-    }
-
     const unsigned char* kbase = p.k + (long long)b * p.kv_bs + (long long)hkv * p.kv_hs;
     const unsigned char* vbase = p.v + (long long)b * p.kv_bs + (long long)hkv * p.kv_hs;
     unsigned char* ring = smem + warp * SM::WARP_BYTES;
@@ -152,6 +138,22 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) decode_attention_kernel(const 
     const int my_blocks = nblocks > warp ? (nblocks - warp + ATT_WARPS - 1) / ATT_WARPS : 0;
 #pragma unroll
     for (int j = 0; j < ATT_STAGES - 1; j++) issue(j);
+
+    // (the first blocks of K and V are on their way: the latency of the query loads hides under theirs)
+    // ---- Q fragments: rows = the G query heads of this kv head (padded to 16 with zeros) ----
+    unsigned qa[KSTEPS][4];
+    {
+        const unsigned char* qb = p.q + (long long)b * p.q_bs + (long long)(hkv * G) * p.q_hs;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ks++) {
+            const int d0 = ks * 16 + 2 * t;
+            qa[ks][0] = g < G ? *(const unsigned*)(qb + (long long)g * p.q_hs + d0 * 2) : 0u;
+            qa[ks][1] = g + 8 < G ? *(const unsigned*)(qb + (long long)(g + 8) * p.q_hs + d0 * 2) : 0u;
+            qa[ks][2] = g < G ? *(const unsigned*)(qb + (long long)g * p.q_hs + (d0 + 8) * 2) : 0u;
+            qa[ks][3] = g + 8 < G ? *(const unsigned*)(qb + (long long)(g + 8) * p.q_hs + (d0 + 8) * 2) : 0u;
+        }
+    }
+
 
     for (int j = 0; j < my_blocks; j++) {
         issue(j + ATT_STAGES - 1);
@@ -360,15 +362,17 @@ int launch_decode_attention(const b200fc_attention_t& a, cudaStream_t s) {
     p.seq_lens = a.seq_lens;
     p.H = a.H; p.Hkv = a.Hkv; p.G = a.H / a.Hkv; p.N = a.N;
     p.scale_log2e = a.scale * 1.4426950408889634f;
-    // splits: fill two CTAs per SM, at least one 16-token block per warp and split
+    // splits: as many as still give ONE round of two CTAs per SM (measured: a ragged second round costs more than a
+    // partly filled first one; 96 KB in flight per CTA saturate HBM from ~130 CTAs on), at least two 16-token blocks per
+    // warp and split
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     static int force_splits = -1;
     if (force_splits < 0) { const char* e = getenv("B200FC_ATTN_SPLITS"); force_splits = e ? atoi(e) : 0; }
     const long long pairs = (long long)a.B * a.Hkv;
-    int splits = (int)((2LL * sms + pairs - 1) / pairs);
-    const int max_by_len = (a.N + BLK * ATT_WARPS - 1) / (BLK * ATT_WARPS);
+    int splits = (int)(2LL * sms / pairs);
+    const int max_by_len = (a.N + 2 * BLK * ATT_WARPS - 1) / (2 * BLK * ATT_WARPS);
     if (splits > max_by_len) splits = max_by_len;
     if (force_splits > 0) splits = force_splits;
     if (splits > MAX_SPLITS) splits = MAX_SPLITS;
