@@ -96,7 +96,8 @@ int* kernel_status_word();  // device int, 0 = OK; kernels store a non-zero code
 int check_kernel_status(cudaStream_t s);  // synchronises and reads it
 // growing device scratch owned by (device, stream, slot): work on one stream is ordered, so kernels launched on it
 // may share it; slot 0 = re-strided activations, slot 1 = split-K partial tiles of the GEMM, 3 = widened weight
-// rows, 4 = normalised activations of the MLP block, 5 = sub-states of the decode attention
+// rows, 4 = normalised activations of the MLP block, 5 = sub-states of the decode attention, 6 = pre-converted activations
+// of the decode kernel
 int get_stream_scratch(size_t bytes, cudaStream_t s, int slot, void** out);
 // the decode kernel's scratch for stream s (gemv_scratch_bytes(), counters zero); never re-allocated once handed out
 int get_gemv_scratch(cudaStream_t s, void** out);

@@ -69,6 +69,9 @@ struct Params {
                           // shared memory instead of the global scratch
     int pf_cap;           // stages beyond the ring that the producer prefetches into L2 when the CTA starts
     const float* scales;  // 4-bit weights: [row block][stage][2][128] group scales, row block 0 = packed rows [0, 128)
+    const unsigned char* ximg;   // quantised weights, optional: the activations already converted by xstage_kernel, one
+                                 // image of the shared-memory chunk buffer per CHUNK of K ([chunk][MP][XROW], the row's
+                                 // exponent in the first word of its pad); null = the consumers convert them themselves
 #ifdef B200FC_TRACE
     unsigned long long* trace;   // [launch % 64][gridDim.x <= 320][8] globaltimer stamps (timeline studies only)
     int trace_launch;
@@ -225,7 +228,8 @@ template <int WB, int NT> struct Layout {
     // quantised weights: the next chunk's activations as they lie in global memory (bf16), fetched with cp.async while
     // the current chunk is multiplied; every thread copies, reads back and overwrites only its own 16-byte units
     static constexpr int RAW_OFF = SC_OFF + (WB == 4 ? STAGES * SC_STAGE_BYTES : 0);
-    static constexpr int BAR_OFF = RAW_OFF + (WQ ? MP * CHUNK * 2 : 0);
+    // (with pre-converted activations the same region is the second chunk buffer, filled while the first is in use)
+    static constexpr int BAR_OFF = RAW_OFF + (WQ ? MP * XROW : 0);
     static constexpr int SMEM = BAR_OFF + 2 * STAGES * 8 + 16 + 1024;  // + barriers, abort flag, last flag, alignment slack
 };
 
@@ -268,6 +272,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
     // compiler loses the address space and every access below becomes a generic load / store (slower, 64-bit addresses)
     unsigned char* smem = smem_raw + (((smem_u32(smem_raw) + 1023u) & ~1023u) - smem_u32(smem_raw));
     unsigned char* xbuf = smem + L::X_OFF;
+    unsigned char* xcur = xbuf;   // chunk buffer the MMAs read: xbuf, or with pre-converted activations xbuf / the raw region in turn
     unsigned* smax = (unsigned*)(smem + L::AUX_OFF);
     int* sexp = (int*)(smem + L::AUX_OFF + MP * CWARPS * 4);
     const unsigned bar_full = smem_u32(smem + L::BAR_OFF);
@@ -484,6 +489,50 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
             }
         };
 
+        // Pre-converted activations (p.ximg): the chunk images lie ready in global memory (L2), chunk c covering stages
+        // [c * STAGES_PER_CHUNK, +STAGES_PER_CHUNK) of every row whatever piece reads them.  A chunk boundary is then one
+        // wait for the copy issued a chunk earlier and ONE barrier; nothing is converted here.
+        const bool img = WQ && p.ximg != nullptr;
+        int xb = 0;
+        constexpr int IMG_BYTES = MP * XROW;
+        auto copy_img = [&](int c, int buf) {
+            const unsigned char* src = p.ximg + (size_t)c * IMG_BYTES;
+            const unsigned dst = smem_u32(buf ? xraw : xbuf);
+            for (int u = ctid; u < IMG_BYTES / 16; u += CTHREADS) cp_async16(dst + u * 16, src + u * 16);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        auto stage_img = [&](int ks, int ks0, int ks_end, bool first_piece) {
+            if constexpr (WQ) {
+                const int c = ks / STAGES_PER_CHUNK;
+                if (ks == ks0) {
+                    // a piece's first chunk: nothing is in flight.  The previous piece's partial tile lies over xbuf and
+                    // may still be read by a slower warp.
+                    if (!first_piece) consumer_sync();
+                    copy_img(c, xb);
+                }
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                consumer_sync();   // every thread's part of the image is there; every warp has left the previous chunk
+                if ((c + 1) * STAGES_PER_CHUNK < ks_end) copy_img(c + 1, xb ^ 1);
+                xcur = xb ? xraw : xbuf;
+                xb ^= 1;
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const int e0 = *(const int*)(xcur + (nt * 8 + 2 * t) * XROW + CHUNK_K * 2);
+                    const int e1 = *(const int*)(xcur + (nt * 8 + 2 * t + 1) * XROW + CHUNK_K * 2);
+                    if (cur_e[nt][0] != e0 || cur_e[nt][1] != e1) {
+#pragma unroll
+                        for (int rb = 0; rb < RB; rb++) {
+                            acc[0][rb][nt][0] = scalbnf(acc[0][rb][nt][0], cur_e[nt][0] - e0);
+                            acc[0][rb][nt][2] = scalbnf(acc[0][rb][nt][2], cur_e[nt][0] - e0);
+                            acc[0][rb][nt][1] = scalbnf(acc[0][rb][nt][1], cur_e[nt][1] - e1);
+                            acc[0][rb][nt][3] = scalbnf(acc[0][rb][nt][3], cur_e[nt][1] - e1);
+                        }
+                        cur_e[nt][0] = e0; cur_e[nt][1] = e1;
+                    }
+                }
+            }
+        };
+
         int stage = 0;
         unsigned phase = 0;
         // byte offsets of this thread's 16-byte pieces inside a stage: rows (rb, h) -> warp*32 + rb*16 + h*8 + g,
@@ -527,10 +576,14 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
                 }
             }
             for (int ks = ks0; ks < ks1; ks++) {
-                const int it_in_chunk = (ks - ks0) % STAGES_PER_CHUNK;
-                if (it_in_chunk == 0) {
-                    if (ks == ks0) prefetch_x(ks, ks1);                       // nothing was in flight for a piece's first chunk
-                    stage_x(ks, ks1, ks + STAGES_PER_CHUNK < ks1);
+                const int it_in_chunk = img ? ks % STAGES_PER_CHUNK : (ks - ks0) % STAGES_PER_CHUNK;
+                if (it_in_chunk == 0 || ks == ks0) {
+                    if (img) {
+                        stage_img(ks, ks0, ks1, first_piece);
+                    } else {
+                        if (ks == ks0) prefetch_x(ks, ks1);                   // nothing was in flight for a piece's first chunk
+                        stage_x(ks, ks1, ks + STAGES_PER_CHUNK < ks1);
+                    }
                 }
                 if (ks == ks0 && ctid < ROWS_PER_CTA) {
                     // (the first barrier of stage_x has been passed: nobody still reads the previous piece's vectors)
@@ -558,7 +611,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
                     unsigned xb[NT][16];
 #pragma unroll
                     for (int nt = 0; nt < NT; nt++) {
-                        const unsigned char* xs = xbuf + (nt * 8 + g) * XROW + xoff;
+                        const unsigned char* xs = xcur + (nt * 8 + g) * XROW + xoff;
 #pragma unroll
                         for (int i = 0; i < 4; i++) {
                             const uint4 a = *(const uint4*)(xs + i * 128);
@@ -602,7 +655,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
                 unsigned xb[NT][W8 ? 8 : 4];
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
-                    const unsigned char* xs = xbuf + (nt * 8 + g) * XROW + xoff;
+                    const unsigned char* xs = xcur + (nt * 8 + g) * XROW + xoff;
                     uint4 a = *(const uint4*)xs;
                     xb[nt][0] = a.x; xb[nt][1] = a.y; xb[nt][2] = a.z; xb[nt][3] = a.w;
                     if constexpr (W8) {
@@ -804,6 +857,80 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
     if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, 3);
 }
 
+
+// Converts the activations of a call with quantised weights ONCE: block c writes the image of chunk c as the decode
+// kernel's chunk buffer wants it — per row CHUNK fp16 values, scaled by the power of two that puts the row's largest
+// magnitude within the chunk at 2^13 (exact: fp16 keeps the 8-bit significand of bf16), in the slot order of the
+// variant's fragment loads, followed by a 64-byte pad whose first word is the exponent.  Rows >= M are zeros.  Used for
+// large matrices, where every CTA walks several chunks and would otherwise convert them itself behind two CTA-wide
+// barriers per chunk; the images (M_pad x K x 2 bytes) stay in L2.
+template <int WB, int NT>
+__global__ void __launch_bounds__(CTHREADS) xstage_kernel(const unsigned char* __restrict__ X, long long ldx, int M, int K,
+                                                          unsigned char* __restrict__ img) {
+    using L = Layout<WB, NT>;
+    constexpr int MP = L::MP, XROW = L::XROW, CHUNK_K = L::CHUNK;
+    constexpr int UNITS = CHUNK_K / 8, ROWS_PER_PASS = CTHREADS / UNITS, PASSES = MP / ROWS_PER_PASS, WPR = UNITS / 32;
+    __shared__ unsigned smax[MP * CWARPS];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int ctid = threadIdx.x, warp = ctid >> 5, lane = ctid & 31;
+    const int unit = ctid % UNITS, row0 = ctid / UNITS;
+    const int k = blockIdx.x * CHUNK_K + unit * 8;
+    const bool x_vec = (((uintptr_t)X & 15) == 0) && ((ldx & 15) == 0);
+    uint4 v[PASSES];
+#pragma unroll
+    for (int i = 0; i < PASSES; i++) {
+        const int row = row0 + i * ROWS_PER_PASS;
+        v[i] = make_uint4(0, 0, 0, 0);
+        if (row < M && k < K) {
+            const unsigned char* src = X + (long long)row * ldx + (long long)k * 2;
+            if (x_vec && k + 8 <= K) {
+                v[i] = *(const uint4*)src;
+            } else {
+                unsigned short e[8];
+#pragma unroll
+                for (int q = 0; q < 8; q++) e[q] = (k + q < K) ? ((const unsigned short*)src)[q] : (unsigned short)0;
+                v[i] = make_uint4(e[0] | ((unsigned)e[1] << 16), e[2] | ((unsigned)e[3] << 16), e[4] | ((unsigned)e[5] << 16),
+                                  e[6] | ((unsigned)e[7] << 16));
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < PASSES; i++) {
+        const unsigned w4[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+        unsigned m = 0;
+#pragma unroll
+        for (int q = 0; q < 4; q++) m = max(m, max(w4[q] & 0x7fffu, (w4[q] >> 16) & 0x7fffu));
+        m = __reduce_max_sync(0xffffffffu, m);
+        if (lane == 0) smax[(row0 + i * ROWS_PER_PASS) * CWARPS + warp] = m;
+    }
+    __syncthreads();
+    unsigned char* out = img + (size_t)blockIdx.x * (MP * XROW);
+#pragma unroll
+    for (int i = 0; i < PASSES; i++) {
+        const int row = row0 + i * ROWS_PER_PASS;
+        unsigned m = 0;
+#pragma unroll
+        for (int q = 0; q < WPR; q++) m = max(m, smax[row * CWARPS + row0 * WPR + q]);
+        int field = (int)(m >> 7);
+        field = field < 1 ? 1 : field;
+        int e = field - 127 - 13;
+        e = e < -126 ? -126 : e;
+        const float sc = __int_as_float((127 - e) << 23);
+        const unsigned w4[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+        unsigned o[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            __half2 h = __floats2half2_rn(__uint_as_float(w4[q] << 16) * sc, __uint_as_float(w4[q] & 0xffff0000u) * sc);
+            o[q] = *(unsigned*)&h;
+        }
+        const int slot = WB == 8 ? ((unit & ~15) | ((unit & 3) << 2) | ((unit >> 2) & 3))
+                                 : ((unit & ~31) | ((unit & 3) << 3) | ((unit >> 2) & 7));
+        *(uint4*)(out + row * XROW + slot * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+        if (unit < 4) *(uint4*)(out + row * XROW + CHUNK_K * 2 + unit * 16) = make_uint4(unit == 0 ? (unsigned)e : 0u, 0u, 0u, 0u);
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -828,8 +955,8 @@ int device_sms() {
 }
 
 template <int WB, int NT>
-int launch_variant(const CUtensorMap& map, const Params& p, int grid, cudaStream_t s) {
-    const int cluster = p.cluster ? p.S : 1;
+int launch_variant(const CUtensorMap& map, const Params& p_in, int grid, cudaStream_t s) {
+    const int cluster = p_in.cluster ? p_in.S : 1;
     using L = Layout<WB, NT>;
     static_assert(L::MP * L::XROW >= 2 * ROWS_PER_CTA * L::MP * 4, "partial tiles must fit the activation buffer");
     static std::atomic<unsigned long long> attr_devices{0};
@@ -840,14 +967,38 @@ int launch_variant(const CUtensorMap& map, const Params& p, int grid, cudaStream
         });
         if (arc) return arc;
     }
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    Params p = p_in;
+    p.ximg = nullptr;
+    if constexpr (WB != 16) {
+        // Pre-converted activations pay from about two chunks per CTA on (they add a small launch to the chain).
+        static int force_img = -1;
+        if (force_img < 0) { const char* e = getenv("B200FC_GEMV_XIMG"); force_img = e ? (atoi(e) ? 1 : 0) : 2; }
+        constexpr int SPC = L::CHUNK / (STAGE_K_BYTES * 8 / WB);
+        const bool use_img = force_img == 2 ? (p.total / grid >= 2 * SPC) : force_img == 1;
+        if (use_img) {
+            const int n_chunks = (p.spr + SPC - 1) / SPC;
+            void* img = nullptr;
+            int rc = get_stream_scratch((size_t)n_chunks * L::MP * L::XROW, s, 6, &img);
+            if (rc) return rc;
+            cudaLaunchConfig_t c0 = {};
+            c0.gridDim = dim3(n_chunks, 1, 1);
+            c0.blockDim = dim3(CTHREADS, 1, 1);
+            c0.stream = s;
+            c0.attrs = attr;
+            c0.numAttrs = 1;
+            B200FC_CUDA(cudaLaunchKernelEx(&c0, xstage_kernel<WB, NT>, p.X, p.ldx, p.M, p.K, (unsigned char*)img));
+            count_launch();
+            p.ximg = (const unsigned char*)img;
+        }
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);
     cfg.blockDim = dim3(THREADS, 1, 1);
     cfg.dynamicSmemBytes = L::SMEM;
     cfg.stream = s;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
     attr[1].id = cudaLaunchAttributeClusterDimension;
     attr[1].val.clusterDim.x = cluster;
     attr[1].val.clusterDim.y = 1;
