@@ -210,6 +210,15 @@ __device__ __forceinline__ unsigned nib_hi_to_f16x2(unsigned w) {
     return *(unsigned*)&r;
 }
 
+// acc * 2^d for |d| <= 252 as two multiplications by exact powers of two (scalbnf costs ~20 instructions per value and
+// the accumulators change their scale at most chunk boundaries)
+__device__ __forceinline__ void pow2_factors(int d, float& f1, float& f2) {
+    d = d < -252 ? -252 : (d > 252 ? 252 : d);
+    const int h = d / 2;
+    f1 = __int_as_float((127 + h) << 23);
+    f2 = __int_as_float((127 + d - h) << 23);
+}
+
 template <int WB, int NT> struct Layout {
     static constexpr bool WQ = WB != 16;   // quantised weights: activations are staged as fp16
     static constexpr int STAGES = (NT == 1 && !WQ) ? 5 : 4;
@@ -474,14 +483,17 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
                 for (int nt = 0; nt < NT; nt++) {
                     const int e0 = sexp[nt * 8 + 2 * t], e1 = sexp[nt * 8 + 2 * t + 1];
                     if (cur_e[nt][0] != e0 || cur_e[nt][1] != e1) {
+                        float a1, a2, b1, b2;
+                        pow2_factors(cur_e[nt][0] - e0, a1, a2);
+                        pow2_factors(cur_e[nt][1] - e1, b1, b2);
 #pragma unroll
                         for (int as = 0; as < AS; as++)
 #pragma unroll
                             for (int rb = 0; rb < RB; rb++) {
-                                acc[as][rb][nt][0] = scalbnf(acc[as][rb][nt][0], cur_e[nt][0] - e0);
-                                acc[as][rb][nt][2] = scalbnf(acc[as][rb][nt][2], cur_e[nt][0] - e0);
-                                acc[as][rb][nt][1] = scalbnf(acc[as][rb][nt][1], cur_e[nt][1] - e1);
-                                acc[as][rb][nt][3] = scalbnf(acc[as][rb][nt][3], cur_e[nt][1] - e1);
+                                acc[as][rb][nt][0] = acc[as][rb][nt][0] * a1 * a2;
+                                acc[as][rb][nt][2] = acc[as][rb][nt][2] * a1 * a2;
+                                acc[as][rb][nt][1] = acc[as][rb][nt][1] * b1 * b2;
+                                acc[as][rb][nt][3] = acc[as][rb][nt][3] * b1 * b2;
                             }
                         cur_e[nt][0] = e0; cur_e[nt][1] = e1;
                     }
@@ -520,12 +532,15 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
                     const int e0 = *(const int*)(xcur + (nt * 8 + 2 * t) * XROW + CHUNK_K * 2);
                     const int e1 = *(const int*)(xcur + (nt * 8 + 2 * t + 1) * XROW + CHUNK_K * 2);
                     if (cur_e[nt][0] != e0 || cur_e[nt][1] != e1) {
+                        float a1, a2, b1, b2;
+                        pow2_factors(cur_e[nt][0] - e0, a1, a2);
+                        pow2_factors(cur_e[nt][1] - e1, b1, b2);
 #pragma unroll
                         for (int rb = 0; rb < RB; rb++) {
-                            acc[0][rb][nt][0] = scalbnf(acc[0][rb][nt][0], cur_e[nt][0] - e0);
-                            acc[0][rb][nt][2] = scalbnf(acc[0][rb][nt][2], cur_e[nt][0] - e0);
-                            acc[0][rb][nt][1] = scalbnf(acc[0][rb][nt][1], cur_e[nt][1] - e1);
-                            acc[0][rb][nt][3] = scalbnf(acc[0][rb][nt][3], cur_e[nt][1] - e1);
+                            acc[0][rb][nt][0] = acc[0][rb][nt][0] * a1 * a2;
+                            acc[0][rb][nt][2] = acc[0][rb][nt][2] * a1 * a2;
+                            acc[0][rb][nt][1] = acc[0][rb][nt][1] * b1 * b2;
+                            acc[0][rb][nt][3] = acc[0][rb][nt][3] * b1 * b2;
                         }
                         cur_e[nt][0] = e0; cur_e[nt][1] = e1;
                     }
