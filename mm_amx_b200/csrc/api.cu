@@ -335,7 +335,29 @@ static int mlp_down_device(Mlp& m, int M, void* out, int out_dtype, int64_t ldo,
     return rc;
 }
 
+// Decode-shaped batches: both projections in one launch when the shape and the device allow it.  B200FC_ERR_UNSUPPORTED
+// (no message) = not this time; the caller launches the two projections one after the other.
+int mlp_decode_fused_device(const Mlp& m, const void* x, int64_t ldx, int M, void* act, void* out, int out_dtype,
+                            int64_t ldo, cudaStream_t s, void* gemv_scratch, const void* residual, int64_t ld_res) {
+    if (M < 1 || M > 16 || (out_dtype != B200FC_BF16 && out_dtype != B200FC_F32)) return B200FC_ERR_UNSUPPORTED;
+    if (ldx < (int64_t)m.K * 2) { set_error("mlp: ldx smaller than a row"); return B200FC_ERR_INVALID; }
+    Epilogue ep = {};
+    ep.steps = 0; ep.out_dtype = out_dtype; ep.C = out; ep.ldc = ldo;
+    ep.deq_scale = 1.0f; ep.q_scale = 1.0f;
+    ep.residual = residual; ep.ld_res = ld_res;
+    return launch_mlp_decode_fused(m.gate_up, m.down, x, ldx, M, m.K, m.Ns, act, ep, s, gemv_scratch);
+}
+
 static int mlp_run_device(Mlp& m, const void* x, int64_t ldx, int M, void* out, int out_dtype, int64_t ldo, cudaStream_t s) {
+    if (M >= 1 && M <= 16) {
+        int rc = grow(&m.act, &m.act_bytes, (size_t)M * m.Ns * 2, s);
+        if (rc) return rc;
+        rc = mlp_decode_fused_device(m, x, ldx, M, m.act, out, out_dtype, ldo, s, nullptr, nullptr, 0);
+        if (rc != B200FC_ERR_UNSUPPORTED) {
+            if (!rc) m.act_rows = M;
+            return rc;
+        }
+    }
     int rc = mlp_gate_up_device(m, x, ldx, M, s);
     if (rc) return rc;
     return mlp_down_device(m, M, out, out_dtype, ldo, s);
@@ -876,6 +898,15 @@ int b200fc_mlp_run_block(b200fc_mlp_t* h, const void* x, int64_t ldx, int M, flo
     const int64_t ldn = (int64_t)m.K * 2;
     int rc = get_stream_scratch((size_t)M * ldn, s, 4, &xn);
     if (!rc) rc = launch_rmsnorm(x, ldx, M, m.K, norm_weight, eps, xn, ldn, s);
+    if (!rc && M <= 16) {
+        rc = grow(&m.act, &m.act_bytes, (size_t)M * m.Ns * 2, s);
+        if (!rc) rc = mlp_decode_fused_device(m, xn, ldn, M, m.act, out, B200FC_BF16, ldo, s, nullptr, add_residual ? x : nullptr, ldx);
+        if (rc != B200FC_ERR_UNSUPPORTED) {
+            if (!rc) m.act_rows = M;
+            return rc;
+        }
+        rc = B200FC_OK;
+    }
     if (!rc) rc = mlp_gate_up_device(m, xn, ldn, M, s);
     if (rc) return rc;
     b200fc_epilogue_t e2 = {};

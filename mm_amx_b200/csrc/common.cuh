@@ -110,6 +110,10 @@ unsigned long long wait_limit_ns();
         if (e__ != cudaSuccess) return ::b200fc::cuda_fail(e__, #call);     \
     } while (0)
 
+// api.cu: gate/up + down of a decode-shaped MLP (1 <= M <= 16) in one launch; B200FC_ERR_UNSUPPORTED without a message =
+// not possible here, launch the two projections separately
+int mlp_decode_fused_device(const Mlp& m, const void* x, int64_t ldx, int M, void* act, void* out, int out_dtype,
+                            int64_t ldo, cudaStream_t s, void* gemv_scratch, const void* residual, int64_t ld_res);
 // api.cu: validated dispatch of one Matmul call on device pointers (w_mut is unused and kept for call-site symmetry)
 // gemv_scratch: counters + partial-sum slots for the decode kernel (gemv_scratch_bytes(), counters zero), or null to
 // use the stream's own
@@ -144,6 +148,10 @@ constexpr int kGemvMaxCtas = 320;
 size_t gemv_scratch_bytes();
 int launch_gemv_tma(const Weight& w, const void* A, int M, int K, int64_t lda, int n0, int n1, const Epilogue& ep,
                     cudaStream_t s, void* scratch);
+// gemv_tma.cu: gate/up + down of a decode-shaped MLP (bf16 weights, M <= 16) in one launch; B200FC_ERR_UNSUPPORTED
+// without a message = not possible for this shape / device, launch the two matrices one after the other
+int launch_mlp_decode_fused(const Weight& gate_up, const Weight& down, const void* x, int64_t ldx, int M, int K, int ns,
+                            void* act, const Epilogue& ep_down, cudaStream_t s, void* scratch);
 // gemm_tc.cu: tcgen05 GEMM, bf16 x bf16 -> fp32 or 8-bit x 8-bit -> int32
 int launch_gemm_tc(const void* W_data, int w_dtype, int W_K_pad, int W_N_pad, const void* A, int dtypeA, int M, int K,
                    int64_t lda, int n0, int n1, const Epilogue& ep, cudaStream_t s);

@@ -266,8 +266,13 @@ __device__ __forceinline__ float postop_staged(float v, int row, int steps, cons
     return v;
 }
 
-template <int WB, int NT>
-__global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
+// The kernel body.  NJ = 1: one matrix.  NJ = 2: two dependent matrices in ONE launch (the decode-shaped MLP: gate/up with
+// the SiLU*up store, then the down projection over the activation the first job wrote): the producer goes straight on
+// into the second matrix, so its first ring of stages arrives while the consumers finish the first job and wait at a
+// grid-wide barrier (every CTA must have stored its part of the activation before anyone multiplies by it).
+template <int WB, int NT, int NJ>
+__device__ __forceinline__ void decode_body(const CUtensorMap* map0, const CUtensorMap* map1, const Params* p0, const Params* p1) {
+    const Params& p = *p0;            // job 0; the role loops below shadow it with the job they work on
     using L = Layout<WB, NT>;
     constexpr bool W8 = WB == 8, W4 = WB == 4, WQ = WB != 16;
     constexpr int MP = L::MP, XROW = L::XROW, STAGES = L::STAGES;
@@ -292,12 +297,12 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int G = (int)gridDim.x, cta = (int)blockIdx.x;
-    const long long it_begin = piece_begin(p, G, cta), it_end = piece_begin(p, G, cta + 1);
     const unsigned long long limit = p.wait_limit_ns;
 
     if (threadIdx.x == 0) {
         TRACE_STAMP(0);   // CTA started
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(map0) : "memory");
+        if (NJ > 1) asm volatile("prefetch.tensormap [%0];" ::"l"(map1) : "memory");
         for (int i = 0; i < STAGES; i++) {
             mbar_init(bar_full + 8 * i, 1);
             mbar_init(bar_empty + 8 * i, CWARPS);
@@ -314,6 +319,12 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
         if (lane == 0) {
             int stage = 0;
             unsigned phase = 0;
+            bool alive = true;
+#pragma unroll 1
+            for (int job = 0; job < NJ && alive; job++) {
+            const Params& p = job ? *p1 : *p0;
+            const CUtensorMap* map_w = job ? map1 : map0;
+            const long long it_begin = piece_begin(p, G, cta), it_end = piece_begin(p, G, cta + 1);
             int rb = (int)(it_begin / p.spr), ks = (int)(it_begin - (long long)rb * p.spr);
             for (long long it = it_begin; it < it_end; it++) {
                 if (it == it_begin + STAGES && p.pf_cap > 0) {
@@ -323,13 +334,13 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
                     long long pf_to = it + p.pf_cap < it_end ? it + p.pf_cap : it_end;
                     int pf_rb = rb, pf_ks = ks;
                     for (long long pf = it; pf < pf_to; pf++) {
-                        tma_prefetch_l2_2d(&map_w, pf_ks * STAGE_K_BYTES, p.n0 + pf_rb * ROWS_PER_CTA);
+                        tma_prefetch_l2_2d(map_w, pf_ks * STAGE_K_BYTES, p.n0 + pf_rb * ROWS_PER_CTA);
                         if (++pf_ks == p.spr) { pf_ks = 0; pf_rb++; }
                     }
                 }
-                if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, limit)) break;
+                if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, limit)) { alive = false; break; }
                 mbar_expect_tx(bar_full + 8 * stage, STAGE_BYTES + (W4 ? L::SC_STAGE_BYTES : 0));
-                tma_load_2d(smem_u32(smem + stage * STAGE_BYTES), &map_w, bar_full + 8 * stage, ks * STAGE_K_BYTES,
+                tma_load_2d(smem_u32(smem + stage * STAGE_BYTES), map_w, bar_full + 8 * stage, ks * STAGE_K_BYTES,
                             p.n0 + rb * ROWS_PER_CTA);
                 if constexpr (W4)
                     bulk_load_1d(smem_u32(smem + L::SC_OFF + stage * L::SC_STAGE_BYTES),
@@ -338,6 +349,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
                 if (++ks == p.spr) { ks = 0; rb++; }
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
+            }
         }
     } else {
         // ---------------- consumers ----------------
@@ -345,6 +357,14 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
         asm volatile("griddepcontrol.wait;" ::: "memory");
         if (threadIdx.x == 0) TRACE_STAMP(1);   // previous kernel complete
         const int ctid = threadIdx.x;                        // 0 .. 255
+        int stage = 0;
+        unsigned phase = 0;
+        bool ok = true;
+#pragma unroll 1
+        for (int job = 0; job < NJ; job++) {
+        const Params& p = job ? *p1 : *p0;
+        const long long it_begin = piece_begin(p, G, cta), it_end = piece_begin(p, G, cta + 1);
+        xcur = xbuf;
         const bool x_vec = (((uintptr_t)p.X & 15) == 0) && ((p.ldx & 15) == 0);
         const bool x_fast = x_vec && (p.K & 7) == 0;
         auto load_x_unit = [&](int row, int k) -> uint4 {
@@ -548,8 +568,6 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
             }
         };
 
-        int stage = 0;
-        unsigned phase = 0;
         // byte offsets of this thread's 16-byte pieces inside a stage: rows (rb, h) -> warp*32 + rb*16 + h*8 + g,
         // logical chunk 2t + j, physical chunk = logical ^ (row & 7) = logical ^ g
         const int rg = warp >> 1, kh = warp & 1;       // row group (32 rows) and K half (64 bytes) of this warp
@@ -559,7 +577,6 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
         const Epilogue& ep = p.ep;
         const bool silu = (ep.steps & B200FC_STEP_SILU_MUL) != 0;
         float* s_ep = (float*)(smem + L::EP_OFF);
-        bool ok = true;
 
         long long it = it_begin;
         while (it < it_end) {
@@ -829,10 +846,42 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
                 }
             }
         }
+        if constexpr (NJ > 1) {
+            // ---- between two jobs: every CTA's stores of the first job (the activation) must be visible before any CTA
+            // reads them.  Arrivals are counted on a word of the scratch; the wait is bounded like every other one. ----
+            unsigned* gbar = p.counters + (kGemvMaxCtas - 2);     // [0] arrivals, [1] CTAs that finished the launch
+            if (job + 1 < NJ) {
+                __threadfence();          // every writer fences its own stores (see the slot exchange above)
+                consumer_sync();
+                if (ctid == 0) {
+                    unsigned seen;
+                    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(seen) : "l"(gbar) : "memory");
+                    seen += 1;
+                    unsigned long long t0 = 0;
+                    while (seen < (unsigned)G && !*abort_flag) {
+                        __nanosleep(100);     // 296 pollers on one word would otherwise delay the arrivals themselves
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(gbar) : "memory");
+                        if (seen >= (unsigned)G) break;
+                        const unsigned long long now = globaltimer();
+                        if (t0 == 0) t0 = now;
+                        if (now - t0 > limit) *abort_flag = 1;
+                    }
+                }
+                consumer_sync();
+                __threadfence();          // every reader fences too
+                if (*abort_flag) ok = false;
+            } else if (ctid == 0) {
+                // the launch's last CTA to get here leaves both words zero for the next launch
+                unsigned done;
+                asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(done) : "l"(gbar + 1) : "memory");
+                if (done == (unsigned)(G - 1)) { gbar[0] = 0; gbar[1] = 0; }
+            }
+        }
+        }   // jobs
         if (ctid == 0) TRACE_STAMP(5);   // done
     }
 
-    if (p.cluster) {
+    if (NJ == 1 && p.cluster) {
         // ---- the S pieces of this row block meet: every CTA of the cluster finishes 1/S of the outputs, adding the
         // partial tiles of all S CTAs in rank order (deterministic) ----
         __syncwarp();
@@ -870,6 +919,19 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_const
         cluster_sync_all();  // nobody leaves while a peer may still read its partial tile
     }
     if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, 3);
+}
+
+template <int WB, int NT>
+__global__ void __launch_bounds__(THREADS, 2) gemv_tma_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
+    decode_body<WB, NT, 1>(&map_w, &map_w, &p, &p);
+}
+
+// gate/up (SiLU*up store into the activation) and down projection of a decode-shaped MLP in one launch (bf16 weights)
+template <int NT>
+__global__ void __launch_bounds__(THREADS, 2) mlp_decode_kernel(const __grid_constant__ CUtensorMap map_gate_up,
+                                                                const __grid_constant__ CUtensorMap map_down,
+                                                                const Params p_gate_up, const Params p_down) {
+    decode_body<16, NT, 2>(&map_gate_up, &map_down, &p_gate_up, &p_down);
 }
 
 
@@ -1034,16 +1096,15 @@ extern "C" void* b200fc_debug_trace_ptr(void) { return g_trace_ptr; }
 
 size_t gemv_scratch_bytes() { return (size_t)kGemvMaxCtas * (2 * SLOT_FLOATS * sizeof(float) + sizeof(unsigned)); }
 
-int launch_gemv_tma(const Weight& w, const void* A, int M, int K, int64_t lda, int n0, int n1, const Epilogue& ep,
-                    cudaStream_t s, void* scratch) {
+// validation, tensor map and the parameters that do not depend on how the work is cut
+static int prepare_job(const Weight& w, const void* A, int M, int K, int64_t lda, int n0, int n1, const Epilogue& ep,
+                       cudaStream_t s, void*& scratch, CUtensorMap& map, Params& p, int& row_blocks) {
     if (M < 1 || M > 16) { set_error("gemv: M must be in [1, 16]"); return B200FC_ERR_INVALID; }
     if (w.dtype == B200FC_U8) { set_error("gemv: unsigned 8-bit weights are not supported with bf16 activations"); return B200FC_ERR_UNSUPPORTED; }
-    if (n1 <= n0) return B200FC_OK;
     if ((ep.steps & B200FC_STEP_SILU_MUL) && (n0 % 32)) { set_error("gemv: SILU_MUL needs n0 %% 32 == 0"); return B200FC_ERR_INVALID; }
     EncodeTiledFn fn = encode_fn();
     if (!fn) { set_error("cuTensorMapEncodeTiled entry point not available"); return B200FC_ERR_CUDA; }
     // the packed weights as a byte matrix [N_pad, K_pad bytes]; box = 128 bytes of K x 128 rows, 128-byte swizzle
-    CUtensorMap map;
     cuuint64_t dims[2] = {(cuuint64_t)w.ld_bytes(), (cuuint64_t)w.N_pad};
     cuuint64_t strides[1] = {(cuuint64_t)w.ld_bytes()};
     cuuint32_t box[2] = {STAGE_K_BYTES, ROWS_PER_CTA};
@@ -1052,9 +1113,8 @@ int launch_gemv_tma(const Weight& w, const void* A, int M, int K, int64_t lda, i
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed (%d)", (int)r); return B200FC_ERR_CUDA; }
 
-    Params p;
     p.spr = (int)(w.ld_bytes() / STAGE_K_BYTES);
-    const int row_blocks = (n1 - n0 + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
+    row_blocks = (n1 - n0 + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
     p.total = (long long)row_blocks * p.spr;
     p.X = (const unsigned char*)A;
     p.ldx = lda;
@@ -1064,41 +1124,8 @@ int launch_gemv_tma(const Weight& w, const void* A, int M, int K, int64_t lda, i
     p.status = kernel_status_word();
     if (!p.status) { set_error("gemv: no kernel status word on this device"); return B200FC_ERR_CUDA; }
     p.wait_limit_ns = wait_limit_ns();
-    static int pf_cap = -1, per_sm = 0, force_stream = 0, force_aligned = 0;   // environment switches, for experiments
-    if (pf_cap < 0) {
-        const char* e = getenv("B200FC_GEMV_PREFETCH");      // stages prefetched into L2 at CTA start (0 = none)
-        pf_cap = e ? atoi(e) : 0;
-        if (pf_cap < 0) pf_cap = 0;
-        if (pf_cap > 64) pf_cap = 64;
-        e = getenv("B200FC_GEMV_CTAS_PER_SM");               // 1 leaves the second resident place to the next kernel
-        per_sm = (e && atoi(e) == 1) ? 1 : 2;
-        e = getenv("B200FC_GEMV_STREAMK");                   // 1: never align pieces with row blocks
-        force_stream = (e && atoi(e) == 1) ? 1 : 0;
-        force_aligned = (e && atoi(e) == 2) ? 1 : 0;         // 2: align whenever the row blocks fit the grid
-    }
-    p.pf_cap = pf_cap;
-    int sms = device_sms();
-    if (sm_limit() > 0 && sm_limit() < sms) sms = sm_limit();
-    long long gmax = (long long)sms * per_sm;
-    if (gmax > kGemvMaxCtas) gmax = kGemvMaxCtas;
-    // Three ways to cut the work; the cost model counts the stages of the longest CTA plus the time of the reduction
-    // that follows, in units of one stage's streaming time.
-    //   stream-K: equal pieces whatever the shape; a CTA may hold the end of one row block and the start of the next,
-    //             partial sums meet through the global scratch (several round trips to L2, twice for such a CTA);
-    //   aligned:  S pieces per row block, one per CTA.  S = 1 needs no reduction; 2 <= S <= 8 runs as clusters of S CTAs
-    //             whose partial sums meet in distributed shared memory (fast, so this wins for small matrices).
-    long long grid = gmax < p.total / 2 ? gmax : p.total / 2;
-    if (grid < 1) grid = 1;
-    long long best = (p.total + grid - 1) / grid + 6;
-    p.S = 0; p.cluster = 0;
-    if (!force_stream && row_blocks <= gmax) {
-        int S = (int)(gmax / row_blocks);
-        if (S > 8) S = 8;
-        if (S > p.spr / 2) S = p.spr / 2;
-        if (S < 1) S = 1;
-        const long long cost = (p.spr + S - 1) / S + (S > 1 ? 1 : 0);
-        if (cost <= best || force_aligned) { best = cost; p.S = S; p.cluster = S > 1 ? 1 : 0; grid = (long long)row_blocks * S; }
-    }
+    p.S = 0; p.cluster = 0; p.pf_cap = 0;
+    p.ximg = nullptr;
 #ifdef B200FC_TRACE
     {
         static unsigned long long* tr = nullptr;
@@ -1118,6 +1145,58 @@ int launch_gemv_tma(const Weight& w, const void* A, int M, int K, int64_t lda, i
     p.counters = (unsigned*)scratch;
     p.slots = (float*)((char*)scratch + (size_t)kGemvMaxCtas * sizeof(unsigned));
     p.scales = w.scale_grp;
+    return B200FC_OK;
+}
+
+// environment switches, for experiments
+static int g_pf_cap = -1, g_per_sm = 2, g_force_stream = 0, g_force_aligned = 0;
+static void read_switches() {
+    if (g_pf_cap >= 0) return;
+    const char* e = getenv("B200FC_GEMV_CTAS_PER_SM");   // 1 leaves the second resident place to the next kernel
+    g_per_sm = (e && atoi(e) == 1) ? 1 : 2;
+    e = getenv("B200FC_GEMV_STREAMK");                   // 1: never align pieces with row blocks
+    g_force_stream = (e && atoi(e) == 1) ? 1 : 0;
+    g_force_aligned = (e && atoi(e) == 2) ? 1 : 0;       // 2: align whenever the row blocks fit the grid
+    e = getenv("B200FC_GEMV_PREFETCH");                  // stages prefetched into L2 at CTA start (0 = none)
+    int v = e ? atoi(e) : 0;
+    g_pf_cap = v < 0 ? 0 : (v > 64 ? 64 : v);
+}
+
+static long long max_ctas() {
+    int sms = device_sms();
+    if (sm_limit() > 0 && sm_limit() < sms) sms = sm_limit();
+    long long gmax = (long long)sms * g_per_sm;
+    return gmax > kGemvMaxCtas - 2 ? kGemvMaxCtas - 2 : gmax;   // the last two counter words serve the two-job barrier
+}
+
+int launch_gemv_tma(const Weight& w, const void* A, int M, int K, int64_t lda, int n0, int n1, const Epilogue& ep,
+                    cudaStream_t s, void* scratch) {
+    if (n1 <= n0 && M >= 1 && M <= 16) return B200FC_OK;
+    CUtensorMap map;
+    Params p;
+    int row_blocks = 0;
+    int rc = prepare_job(w, A, M, K, lda, n0, n1, ep, s, scratch, map, p, row_blocks);
+    if (rc) return rc;
+    read_switches();
+    p.pf_cap = g_pf_cap;
+    const long long gmax = max_ctas();
+    // Three ways to cut the work; the cost model counts the stages of the longest CTA plus the time of the reduction
+    // that follows, in units of one stage's streaming time.
+    //   stream-K: equal pieces whatever the shape; a CTA may hold the end of one row block and the start of the next,
+    //             partial sums meet through the global scratch (several round trips to L2, twice for such a CTA);
+    //   aligned:  S pieces per row block, one per CTA.  S = 1 needs no reduction; 2 <= S <= 8 runs as clusters of S CTAs
+    //             whose partial sums meet in distributed shared memory (fast, so this wins for small matrices).
+    long long grid = gmax < p.total / 2 ? gmax : p.total / 2;
+    if (grid < 1) grid = 1;
+    long long best = (p.total + grid - 1) / grid + 6;
+    if (!g_force_stream && row_blocks <= gmax) {
+        int S = (int)(gmax / row_blocks);
+        if (S > 8) S = 8;
+        if (S > p.spr / 2) S = p.spr / 2;
+        if (S < 1) S = 1;
+        const long long cost = (p.spr + S - 1) / S + (S > 1 ? 1 : 0);
+        if (cost <= best || g_force_aligned) { best = cost; p.S = S; p.cluster = S > 1 ? 1 : 0; grid = (long long)row_blocks * S; }
+    }
     if (w.dtype == B200FC_S4) {
         if (!w.scale_grp || (n0 % ROWS_PER_CTA)) { set_error("gemv: 4-bit weights need group scales and n0 %% 128 == 0"); return B200FC_ERR_INVALID; }
         return M <= 8 ? launch_variant<4, 1>(map, p, (int)grid, s) : launch_variant<4, 2>(map, p, (int)grid, s);
@@ -1125,6 +1204,71 @@ int launch_gemv_tma(const Weight& w, const void* A, int M, int K, int64_t lda, i
     const bool w8 = w.dtype == B200FC_S8;
     if (M <= 8) return w8 ? launch_variant<8, 1>(map, p, (int)grid, s) : launch_variant<16, 1>(map, p, (int)grid, s);
     return w8 ? launch_variant<8, 2>(map, p, (int)grid, s) : launch_variant<16, 2>(map, p, (int)grid, s);
+}
+
+template <int NT>
+static int launch_mlp_variant(const CUtensorMap& m1, const CUtensorMap& m2, const Params& p1, const Params& p2, int grid,
+                              cudaStream_t s) {
+    using L = Layout<16, NT>;
+    static std::atomic<unsigned long long> attr_devices{0};
+    static std::atomic<int> resident{0};     // CTAs of this kernel an SM holds (all CTAs of the grid must be resident)
+    {
+        const int arc = once_per_device(attr_devices, [] {
+            B200FC_CUDA(cudaFuncSetAttribute(mlp_decode_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM));
+            int n = 0;
+            B200FC_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, mlp_decode_kernel<NT>, THREADS, L::SMEM));
+            resident.store(n);
+            return (int)B200FC_OK;
+        });
+        if (arc) return arc;
+    }
+    if ((long long)resident.load() * device_sms() < grid) return B200FC_ERR_UNSUPPORTED;   // caller falls back to two launches
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(THREADS, 1, 1);
+    cfg.dynamicSmemBytes = L::SMEM;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B200FC_CUDA(cudaLaunchKernelEx(&cfg, mlp_decode_kernel<NT>, m1, m2, p1, p2));
+    count_launch();
+    return B200FC_OK;
+}
+
+// Decode-shaped MLP (bf16 weights, M <= 16) as ONE launch: job 1 = gate/up with the SiLU*up store into `act`
+// ([M, ns] bf16), job 2 = down over `act`.  Both jobs are cut stream-K over the same grid (no clusters: the CTAs of a
+// job meet through the global scratch), and the CTAs wait for one another between the jobs, so the whole grid must be
+// resident: at most two CTAs per SM, and the SM limit of the GEMMs is not honoured.  Returns B200FC_ERR_UNSUPPORTED
+// (without an error message) when the shape or the device does not allow it; the caller then launches twice.
+int launch_mlp_decode_fused(const Weight& gate_up, const Weight& down, const void* x, int64_t ldx, int M, int K, int ns,
+                            void* act, const Epilogue& ep_down, cudaStream_t s, void* scratch) {
+    if (gate_up.dtype != B200FC_BF16 || down.dtype != B200FC_BF16 || M < 1 || M > 16) return B200FC_ERR_UNSUPPORTED;
+    if (sm_limit() > 0 && sm_limit() < device_sms()) return B200FC_ERR_UNSUPPORTED;
+    static int enabled = -1;
+    // Off unless B200FC_MLP_FUSED=1: measured slower than two launches (Llama-7B MLP, M = 1: 57.6 vs 51.5 us) — the second
+    // job cannot use the cluster reduction (a grid of clusters would not be resident as a whole), which alone costs 3.5 us,
+    // and the barrier between the jobs with its fences costs more than the programmatic launch edge it replaces.
+    if (enabled < 0) { const char* e = getenv("B200FC_MLP_FUSED"); enabled = (e && atoi(e)) ? 1 : 0; }
+    if (!enabled) return B200FC_ERR_UNSUPPORTED;
+    Epilogue ep1 = {};
+    ep1.steps = B200FC_STEP_SILU_MUL; ep1.out_dtype = B200FC_BF16; ep1.C = act; ep1.ldc = (long long)ns * 2;
+    ep1.deq_scale = 1.0f; ep1.q_scale = 1.0f;
+    CUtensorMap m1, m2;
+    Params p1, p2;
+    int rb1 = 0, rb2 = 0;
+    int rc = prepare_job(gate_up, x, M, K, ldx, 0, 2 * ns, ep1, s, scratch, m1, p1, rb1);
+    if (rc) return rc;
+    rc = prepare_job(down, act, M, ns, (int64_t)ns * 2, 0, K, ep_down, s, scratch, m2, p2, rb2);
+    if (rc) return rc;
+    read_switches();
+    long long grid = (long long)device_sms() * 2;
+    if (grid > kGemvMaxCtas - 2) grid = kGemvMaxCtas - 2;
+    // every CTA needs at least two stages of either job for the piece arithmetic (and the launch is pointless below that)
+    if (p1.total < 2 * grid || p2.total < 2 * grid) return B200FC_ERR_UNSUPPORTED;
+    return M <= 8 ? launch_mlp_variant<1>(m1, m2, p1, p2, (int)grid, s) : launch_mlp_variant<2>(m1, m2, p1, p2, (int)grid, s);
 }
 
 }  // namespace b200fc

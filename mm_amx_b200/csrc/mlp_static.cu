@@ -84,6 +84,8 @@ int b200fc_mlp_run_decode_static(b200fc_mlp_t* h, const void* x, int64_t ldx, in
     // gate/up projection + SiLU*up writes all M x Ns activation elements before the down projection reads them, and
     // the down projection reads nothing beyond them, so nothing in the activation array has to be cleared between
     // calls.  The decode kernel writes every partial-sum slot before it reads it and returns its counters to zero.
+    rc = mlp_decode_fused_device(m, x, ldx, M, act, out, out_dtype, ldo, s, addr.gemv, nullptr, 0);   // one launch if possible
+    if (rc != B200FC_ERR_UNSUPPORTED) return rc;
     b200fc_epilogue_t e1 = {};
     e1.steps = B200FC_STEP_SILU_MUL; e1.out_dtype = B200FC_BF16; e1.C = act; e1.ldc_bytes = (int64_t)m.Ns * 2;
     rc = matmul_device(m.gate_up, nullptr, x, B200FC_BF16, M, m.K, ldx, 0, 2 * m.Ns, &e1, s, addr.gemv);

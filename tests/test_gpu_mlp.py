@@ -192,3 +192,43 @@ def test_rmsnorm_and_mlp_block(M, with_weight, residual):
         mlp.run(dn.ptr, dn.ld, M, plain.ptr, plain.ld)
         capi.sync_check()
         assert np.array_equal(plain.numpy(), out.numpy())
+
+
+def test_decode_mlp_in_one_launch_subprocess():
+    """B200FC_MLP_FUSED=1 (read once per process, hence the child process): gate/up and down of a decode-shaped MLP run
+    as two jobs of ONE launch with a bounded grid-wide barrier between them.  Off by default (measured slower than two
+    launches); the path must still be right: against the CPU oracle at M = 1, 5, 16, with and without the residual block."""
+    import os, subprocess, sys, textwrap
+    code = textwrap.dedent("""
+        import numpy as np
+        import helpers as H
+        from mm_amx_b200 import capi
+        from oracle import port
+        from oracle._common import bf16_to_f32
+        rng = np.random.default_rng(77)
+        K, N = 2048, 5504
+        gate = H.normal_bf16(rng, (N, K), 0.02); up = H.normal_bf16(rng, (N, K), 0.02); down = H.normal_bf16(rng, (K, N), 0.02)
+        dg, du, dd = H.Dev(gate), H.Dev(up), H.Dev(down)
+        mlp = capi.Mlp(dg.ptr, du.ptr, dd.ptr, K, N)
+        before = capi.launch_count()
+        for M in (1, 5, 16):
+            x = H.normal_bf16(rng, (M, K))
+            dx = H.Dev(x); out = H.Dev(shape=(M, K), dtype=np.uint16, fill=0xCD)
+            n0 = capi.launch_count()
+            mlp.run(dx.ptr, K * 2, M, out.ptr, K * 2)
+            capi.sync_check()
+            assert capi.launch_count() - n0 == 1, "expected one launch"
+            ref = port.mlp(x, gate, up, down)
+            assert H.rel_to_max(bf16_to_f32(out.numpy()), bf16_to_f32(ref)) < 1e-2
+            out2 = H.Dev(shape=(M, K), dtype=np.uint16, fill=0xCD)
+            mlp.run_block(dx.ptr, K * 2, M, 1e-5, out2.ptr, K * 2)
+            capi.sync_check()
+            ref2 = port.mlp_block(x, gate, up, down, 1e-5)
+            assert H.rel_to_max(bf16_to_f32(out2.numpy()), bf16_to_f32(ref2)) < 1e-2
+        print("fused ok")
+    """)
+    env = dict(os.environ, B200FC_MLP_FUSED="1")
+    here = os.path.dirname(os.path.abspath(__file__))
+    env["PYTHONPATH"] = os.pathsep.join([here, os.path.dirname(here), env.get("PYTHONPATH", "")])
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "fused ok" in r.stdout, r.stdout + r.stderr
