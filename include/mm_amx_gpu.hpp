@@ -290,6 +290,26 @@ struct Matmul<ov::bfloat16, int8_t, float> : detail::MatmulImpl<ov::bfloat16, ov
     }
 };
 
+// bf16 activations, bf16 weights stored as 4-bit values with one absmax scale per output channel and 128 K
+// (B200FC_PACK_INT4_GROUP).  The reference reserves this precision in its dispatcher (Weight_INT4, main.cpp:36) without
+// implementing it; the tag type stands where int8_t stands in the specialisation above.  Steps must include DEQUANT.
+struct int4_t {};
+template <>
+struct Matmul<ov::bfloat16, int4_t, float> : detail::MatmulImpl<ov::bfloat16, ov::bfloat16, B200FC_PACK_INT4_GROUP> {
+    constexpr static int kStep = 32;
+    Matmul(bool constB = false, bool transposeB = false)
+        : detail::MatmulImpl<ov::bfloat16, ov::bfloat16, B200FC_PACK_INT4_GROUP>(constB, transposeB) {}
+    template <typename PPK>
+    void operator()(tensor2D<ov::bfloat16>& A, tensor2D<ov::bfloat16>& B, int n0, int n1, PPK pp) {
+        static_assert((PPK::kSteps & PP::DEQUANT) != 0, "compressed weights need a post-op with the DEQUANT step");
+        this->run(A, B, n0, n1, pp);
+    }
+    template <typename PPK>
+    void operator()(tensor2D<ov::bfloat16>& A, tensor2D<ov::bfloat16>& B, PPK pp) {
+        (*this)(A, B, 0, B.dims[this->transposeB ? 0 : 1], pp);
+    }
+};
+
 // c[M] = A[M, K] * b[K]
 template <typename TA, typename TB, typename TC = typename acc_type<TA>::type>
 struct MatmulVector {

@@ -153,6 +153,60 @@ static void mlp() {
     report("fused MLP (err/max <= 1e-2)", M, K, N, max_err <= 1e-2 * max_ref);
 }
 
+// The reference's dynamic precision dispatcher (struct Matmul, main.cpp:32-80) with the Weight_INT4 branch it reserves
+// (main.cpp:36) filled in: bf16 weights are compressed to 4-bit group-quantised form inside the object.
+struct DispatchMatmul {
+    enum WeightPrecision { Weight_BF16, Weight_INT8, Weight_INT4 };
+    amx_kernel::Matmul<bfloat16, bfloat16> mbf16bf16;
+    amx_kernel::Matmul<bfloat16, int8_t, float> mbf16s8;
+    amx_kernel::Matmul<bfloat16, amx_kernel::int4_t, float> mbf16s4;
+    WeightPrecision wei_prec;
+    bool transposeB;
+    DispatchMatmul(bool constB, bool transposeB, WeightPrecision prec)
+        : mbf16bf16(constB, transposeB), mbf16s8(constB, transposeB), mbf16s4(constB, transposeB), wei_prec(prec), transposeB(transposeB) {}
+    template <typename PPK>
+    void operator()(tensor2D<bfloat16>& A, tensor2D<bfloat16>& B, int n0, int n1, PPK pp) {
+        if (wei_prec == Weight_INT8) mbf16s8(A, B, n0, n1, pp);
+        if (wei_prec == Weight_INT4) mbf16s4(A, B, n0, n1, pp);
+    }
+};
+
+static void int4_dispatch() {
+    // expected: per output channel and group of 128 K, q = rne(w * (7 / absmax)), value = q * (absmax / 7), plain loops
+    const int K = 384, N = 200;
+    for (int M : {5, 40}) {
+        tensor2D<bfloat16> A(M, K), B(K, N);
+        for (int k = 0; k < K; k++) for (int n = 0; n < N; n++) B(k, n) = bfloat16(0.02f * (float)(((k * 131 + n * 71) % 97) - 48) / 48.0f);
+        for (int m = 0; m < M; m++) for (int k = 0; k < K; k++) A(m, k) = bfloat16((float)(((m * 37 + k * 11) % 61) - 30) / 30.0f);
+        std::vector<float> deq((size_t)K * N);
+        for (int n = 0; n < N; n++)
+            for (int g0 = 0; g0 < K; g0 += 128) {
+                float amax = 0;
+                for (int k = g0; k < g0 + 128 && k < K; k++) amax = std::fmax(amax, std::fabs((float)B(k, n)));
+                const float qs = amax > 0 ? 7.0f / amax : 0.0f, d = amax / 7.0f;
+                for (int k = g0; k < g0 + 128 && k < K; k++) {
+                    float q = std::nearbyint((float)B(k, n) * qs);
+                    q = q > 7 ? 7 : (q < -7 ? -7 : q);
+                    deq[(size_t)k * N + n] = q * d;
+                }
+            }
+        tensor2D<float> C(M, N);
+        C = 0.0f;
+        DispatchMatmul mm(true, false, DispatchMatmul::Weight_INT4);
+        PP::BiasGeluStore<float, PP::DEQUANT> pp(C);
+        mm(A, B, 0, N, pp);
+        double max_ref = 0, max_err = 0;
+        for (int m = 0; m < M; m++) for (int n = 0; n < N; n++) {
+            double s = 0;
+            for (int k = 0; k < K; k++) s += (double)(float)A(m, k) * (double)deq[(size_t)k * N + n];
+            max_ref = std::fmax(max_ref, std::fabs(s)); max_err = std::fmax(max_err, std::fabs(s - (double)C(m, n)));
+        }
+        // M <= 16: group sums are exact, one fp32 scale per group; M > 16: values rounded to bf16 before the GEMM
+        report(M <= 16 ? "Weight_INT4 decode (err/max<=1e-5)" : "Weight_INT4 prefill (err/max<=1e-2)", M, K, N,
+               max_err <= (M <= 16 ? 1e-5 : 1e-2) * max_ref);
+    }
+}
+
 static void errors() {
     tensor2D<bfloat16> A(4, 64), B(32, 64);   // K mismatch
     tensor2D<float> C(4, 64);
@@ -168,6 +222,7 @@ int main() {
     all_shapes<bfloat16, amx_kernel::Matmul<bfloat16, bfloat16>, PP::NONE>("bf16 NONE");
     all_shapes<bfloat16, amx_kernel::Matmul<bfloat16, int8_t, float>, PP::DEQUANT>("bf16 x int8-compressed DEQUANT");
     column_split();
+    int4_dispatch();
     bias_gelu();
     quant_out();
     matvec();
