@@ -660,6 +660,36 @@ def other_configs(torch, capi, dev, peaks, only=None):
             e1.record(); torch.cuda.synchronize()
         return e0.elapsed_time(e1) * 1e-3 / reps / n_launch
 
+    def timed_graph_independent(launch_one, n_launch, n_streams=4, reps=5):
+        """The same launches as INDEPENDENT layers, which is how the reference times its weight stream (L layers that
+        share no data: weight_compression/fc16m.cpp:687-734, main.cpp:811-846): round-robin over n_streams streams
+        forked from and joined to the capturing stream, so that one layer's ramp and tail overlap its neighbours'."""
+        streams = [torch.cuda.Stream() for _ in range(n_streams)]
+
+        def fan_out(cur):
+            ev0 = torch.cuda.Event(); ev0.record(cur)
+            for st in streams:
+                st.wait_event(ev0)
+            for i in range(n_launch):
+                st = streams[i % n_streams]
+                with torch.cuda.stream(st):
+                    launch_one(i, i % n_streams, st.cuda_stream)
+            for st in streams:
+                ev = torch.cuda.Event(); ev.record(st); cur.wait_event(ev)
+
+        with torch.cuda.stream(side):
+            fan_out(side); torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                fan_out(torch.cuda.current_stream())
+            graph.replay(); torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                graph.replay()
+            e1.record(); torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e-3 / reps / n_launch
+
     # config 1: A[256,4096] x B[4096,4096] + bias -> fp32
     M, K, N = 256, 4096, 4096
     if want("bf16_linear_256x4096x4096_bias_f32"):
@@ -697,7 +727,18 @@ def other_configs(torch, capi, dev, peaks, only=None):
             t = timed_graph(lambda s: [w.matmul(x.data_ptr(), capi.BF16, M, K, K * 2, ep, stream=s) for w in ws], nset)
             nbytes = K * N + N * 4 + M * (K + N) * 2
             out["int8w_gemv_M%d_4096x%d" % (M, N)] = {"us": t * 1e6, "gbs": nbytes / t / 1e9,
-                                                      "hbm_frac": nbytes / t / 1e9 / peaks["hbm_gbs"], "weight_sets": nset}
+                                                      "hbm_frac": nbytes / t / 1e9 / peaks["hbm_gbs"], "weight_sets": nset,
+                                                      "chain": "dependent: every launch waits for the one before it"}
+            if only is None:
+                Cs = [torch.empty((M, N), dtype=torch.bfloat16, device=dev) for _ in range(4)]
+                eps = [capi.make_epilogue(c.data_ptr(), N * 2, capi.BF16, capi.STEP_DEQUANT) for c in Cs]
+                capi.set_decode_ctas_per_sm(1)      # two kernels of different streams resident together
+                t = timed_graph_independent(
+                    lambda i, si, s: ws[i].matmul(x.data_ptr(), capi.BF16, M, K, K * 2, eps[si], stream=s), nset)
+                capi.set_decode_ctas_per_sm(0)
+                out["int8w_gemv_M%d_4096x%d_independent" % (M, N)] = {
+                    "us": t * 1e6, "gbs": nbytes / t / 1e9, "hbm_frac": nbytes / t / 1e9 / peaks["hbm_gbs"], "weight_sets": nset,
+                    "chain": "independent layers on 4 streams (one CTA per SM and kernel), as the reference times its weight stream"}
         del ws
     # one large int8-weight matrix (a tensor-parallel shard of the Llama-70B gate/up projection), where the kernel's
     # ramp no longer counts: the weight stream itself

@@ -75,6 +75,12 @@ int64_t b200fc_launch_count(void);
  * all-reduce with the GEMMs leaves the collective a few SMs this way; otherwise its CTAs queue behind the GEMM's. */
 int b200fc_set_sm_limit(int sms);
 
+/* CTAs per SM of the decode kernel (M <= 16): 2 (the default, 0 restores it) is fastest for a chain of dependent layers
+ * on one stream; 1 lets two decode kernels of DIFFERENT streams be resident together, so that independent layers
+ * overlap one another's ramp and tail (how the reference times its weight stream: L layers that share no data,
+ * weight_compression/fc16m.cpp:687-734, main.cpp:811-846). */
+int b200fc_set_decode_ctas_per_sm(int n);
+
 /* waits for `stream` and reports whether any kernel of this library gave up on a bounded wait since the last check
  * (B200FC_ERR_KERNEL); the _host entry points do this themselves */
 int b200fc_sync_check(void* stream);

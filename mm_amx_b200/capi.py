@@ -45,6 +45,7 @@ SIGNATURES = {
     "b200fc_sync_check": (c_int, [c_void_p]),
     "b200fc_set_wait_limit_ns": (c_int, [ctypes.c_uint64]),
     "b200fc_set_sm_limit": (c_int, [c_int]),
+    "b200fc_set_decode_ctas_per_sm": (c_int, [c_int]),
     "b200fc_weight_pack": (c_int, [c_void_p, c_int, c_int, c_int, c_i64, c_int, c_int, c_void_p,
                                    ctypes.POINTER(c_void_p), c_void_p]),
     "b200fc_weight_free": (c_int, [c_void_p]),
@@ -126,6 +127,11 @@ def launch_count():
 
 def set_sm_limit(sms):
     check(lib().b200fc_set_sm_limit(sms))
+
+
+def set_decode_ctas_per_sm(n):
+    """0 = default (2); 1 lets decode kernels of different streams overlap; see include/b200fc.h."""
+    check(lib().b200fc_set_decode_ctas_per_sm(n))
 
 
 def sync_check(stream=None):

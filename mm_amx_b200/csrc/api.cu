@@ -380,6 +380,12 @@ int b200fc_set_sm_limit(int sms) {
     return B200FC_OK;
 }
 
+int b200fc_set_decode_ctas_per_sm(int n) {
+    if (n < 0 || n > 2) { set_error("set_decode_ctas_per_sm: 0 (default), 1 or 2"); return B200FC_ERR_INVALID; }
+    set_decode_ctas_per_sm(n);
+    return B200FC_OK;
+}
+
 int b200fc_sync_check(void* stream) { return check_kernel_status((cudaStream_t)stream); }
 
 int b200fc_set_wait_limit_ns(uint64_t ns) {

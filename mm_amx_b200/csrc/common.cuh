@@ -146,6 +146,7 @@ int launch_rmsnorm(const void* x, int64_t ldx, int M, int K, const void* weight,
 // zero), shared by the launches of one stream; null = the stream's own (allocated on first use).
 constexpr int kGemvMaxCtas = 320;
 size_t gemv_scratch_bytes();
+void set_decode_ctas_per_sm(int n);
 int launch_gemv_tma(const Weight& w, const void* A, int M, int K, int64_t lda, int n0, int n1, const Epilogue& ep,
                     cudaStream_t s, void* scratch);
 // gemv_tma.cu: gate/up + down of a decode-shaped MLP (bf16 weights, M <= 16) in one launch; B200FC_ERR_UNSUPPORTED

@@ -1162,10 +1162,14 @@ static void read_switches() {
     g_pf_cap = v < 0 ? 0 : (v > 64 ? 64 : v);
 }
 
+static std::atomic<int> g_per_sm_api{0};      // b200fc_set_decode_ctas_per_sm: 0 = the default / the environment's choice
+void set_decode_ctas_per_sm(int n) { g_per_sm_api.store(n); }
+
 static long long max_ctas() {
     int sms = device_sms();
     if (sm_limit() > 0 && sm_limit() < sms) sms = sm_limit();
-    long long gmax = (long long)sms * g_per_sm;
+    const int api = g_per_sm_api.load();
+    long long gmax = (long long)sms * (api == 1 || api == 2 ? api : g_per_sm);
     return gmax > kGemvMaxCtas - 2 ? kGemvMaxCtas - 2 : gmax;   // the last two counter words serve the two-job barrier
 }
 

@@ -339,3 +339,23 @@ def test_argument_errors():
     ep2 = capi.make_epilogue(C.ptr, C.ld, capi.F32, capi.STEP_BIAS)  # bias missing
     with pytest.raises(capi.B200FCError):
         w.matmul(A.ptr, capi.BF16, 4, 64, 128, ep2)
+
+
+def test_decode_ctas_per_sm_setter():
+    """one CTA per SM (for independent layers on several streams) computes the same values as the default two"""
+    rng = np.random.default_rng(21)
+    M, K, N = 4, 4096, 1536
+    x = H.normal_bf16(rng, (M, K))
+    Wq = rng.integers(-127, 128, (K, N), dtype=np.int8)
+    scale = rng.uniform(0.001, 0.02, N).astype(np.float32)
+    w = H.pack(Wq, False, capi.PACK_INT8_CHANNEL, scales=scale)
+    ref = port.postops(port.gemm_bf16_w8(x, Wq), port.DEQUANT, port.F32, deq_scale=1.0, deq_scale_per_oc=scale)
+    try:
+        capi.set_decode_ctas_per_sm(1)
+        got1 = H.run_matmul(w, x, capi.F32, steps=capi.STEP_DEQUANT)
+    finally:
+        capi.set_decode_ctas_per_sm(0)
+    got2 = H.run_matmul(w, x, capi.F32, steps=capi.STEP_DEQUANT)
+    assert H.rel_to_max(got1, ref) < 1e-5 and H.rel_to_max(got2, ref) < 1e-5
+    with pytest.raises(capi.B200FCError):
+        capi.set_decode_ctas_per_sm(3)
