@@ -852,6 +852,38 @@ __global__ void splitk_reduce_kernel(const unsigned* __restrict__ ws, long long 
     const long long total = (long long)M * cols;
     // launched as a programmatic dependent of the GEMM: resident early, waits here for the slabs
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    // fp32 accumulators, four consecutive columns per thread: one 16-byte load per slab, all of them in flight together
+    // (the scalar loop below is bound by the latency of its dependent 4-byte loads)
+    if (!silu && !acc_is_int && !ep.residual && (cols & 3) == 0 && (pitch & 3) == 0 && splits <= 8 &&
+        (ep.out_dtype == B200FC_F32 || ep.out_dtype == B200FC_BF16) && ((uintptr_t)ep.C & 15) == 0 && (ep.ldc & 15) == 0 &&
+        (n0 & 3) == 0) {
+        const int c4 = cols >> 2;
+        const long long total4 = (long long)M * c4;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (long long)gridDim.x * blockDim.x) {
+            const int m = (int)(i / c4), c = (int)(i % c4) * 4;
+            const float4* src = (const float4*)(ws + (long long)m * pitch + c);
+            float4 v[8];
+#pragma unroll
+            for (int q = 0; q < 8; q++)
+                if (q < splits) v[q] = src[(long long)q * (slab_elems >> 2)];
+            float4 sum = v[0];
+#pragma unroll
+            for (int q = 1; q < 8; q++)
+                if (q < splits) { sum.x += v[q].x; sum.y += v[q].y; sum.z += v[q].z; sum.w += v[q].w; }
+            const int n = n0 + c;
+            const float o0 = postop_scalar(sum.x, n, ep), o1 = postop_scalar(sum.y, n + 1, ep);
+            const float o2 = postop_scalar(sum.z, n + 2, ep), o3 = postop_scalar(sum.w, n + 3, ep);
+            char* crow = (char*)ep.C + (long long)m * ep.ldc;
+            if (ep.out_dtype == B200FC_F32) {
+                *(float4*)(crow + (long long)n * 4) = make_float4(o0, o1, o2, o3);
+            } else {
+                const unsigned lo = (unsigned)f32_to_bf16_bits(o0) | ((unsigned)f32_to_bf16_bits(o1) << 16);
+                const unsigned hi = (unsigned)f32_to_bf16_bits(o2) | ((unsigned)f32_to_bf16_bits(o3) << 16);
+                *(uint2*)(crow + (long long)n * 2) = make_uint2(lo, hi);
+            }
+        }
+        return;
+    }
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int m = (int)(i / cols), c = (int)(i % cols);
         const unsigned* row = ws + (long long)m * pitch;
