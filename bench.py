@@ -638,6 +638,17 @@ def other_configs(torch, capi, dev, peaks, only=None):
     def want(key):
         return only is None or key == only
 
+    def warm_replays(graph, ms=20.0):
+        """replays until about `ms` of GPU time have passed: rows of a few microseconds must not depend on what ran (or
+        did not run) before them — the first replays after an idle stretch see ramping clocks"""
+        w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0.record()
+        for _ in range(1000):
+            graph.replay()
+            w1.record(); w1.synchronize()
+            if w0.elapsed_time(w1) >= ms:
+                break
+
     def timed_graph(launch_all, n_launch, reps=5):
         with torch.cuda.stream(side):
             s = side.cuda_stream
@@ -652,7 +663,7 @@ def other_configs(torch, capi, dev, peaks, only=None):
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=side):
                 launch_all(torch.cuda.current_stream().cuda_stream)
-            graph.replay(); torch.cuda.synchronize()
+            warm_replays(graph)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             for _ in range(reps):
@@ -682,7 +693,7 @@ def other_configs(torch, capi, dev, peaks, only=None):
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=side):
                 fan_out(torch.cuda.current_stream())
-            graph.replay(); torch.cuda.synchronize()
+            warm_replays(graph)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             for _ in range(reps):

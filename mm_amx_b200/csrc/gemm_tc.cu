@@ -181,22 +181,40 @@ struct EpiArgs {       // what the epilogue of one 32-column chunk needs to know
 };
 // 32 rows x 32 four-byte values, one row per lane in registers -> global memory with full-line stores: the tile goes
 // through shared memory and comes back with eight lanes per row (16 bytes each), so that one store instruction writes
-// four whole 128-byte row segments instead of 32 scattered 16-byte pieces.  Called by all lanes of the warp.
+// four whole 128-byte row segments instead of 32 scattered 16-byte pieces.  Both passes use 16-byte accesses: row r
+// keeps its 16-byte piece j at position j ^ (r & 7), which makes the eight lanes of every shared-memory wavefront hit
+// eight different bank groups on the way in (lanes = rows) and on the way out (lanes = pieces of one row).
+// Called by all lanes of the warp; `tile` is 16-byte aligned.
 __device__ __forceinline__ void store_tile_4b(const unsigned (&val)[32], unsigned* tile, char* C, long long ldc, int m, int n,
                                               int M) {
     const int lane = threadIdx.x & 31, m0 = m - lane;
+    uint4* t4 = (uint4*)tile;
 #pragma unroll
-    for (int j = 0; j < 32; j++) tile[lane * 33 + j] = val[j];
+    for (int j = 0; j < 8; j++)
+        t4[lane * 8 + (j ^ (lane & 7))] = make_uint4(val[4 * j], val[4 * j + 1], val[4 * j + 2], val[4 * j + 3]);
     __syncwarp();
-    const int c = (lane & 7) * 4;
+    const int piece = lane & 7;
 #pragma unroll
     for (int it = 0; it < 8; it++) {
         const int rr = it * 4 + (lane >> 3);
-        const unsigned* t = tile + rr * 33 + c;
-        const uint4 q = make_uint4(t[0], t[1], t[2], t[3]);
-        if (m0 + rr < M) *(uint4*)(C + (long long)(m0 + rr) * ldc + (long long)(n + c) * 4) = q;
+        const uint4 q = t4[rr * 8 + (piece ^ (rr & 7))];
+        if (m0 + rr < M) *(uint4*)(C + (long long)(m0 + rr) * ldc + (long long)(n + piece * 4) * 4) = q;
     }
     __syncwarp();
+}
+// the 32 per-column values vec[n .. n + 32) of a chunk (every lane needs all of them): eight 16-byte loads when the
+// chunk is whole and the vector 16-byte aligned, else 32 scalar loads clamped to the last valid column
+__device__ __forceinline__ void load_col_vec(const float* __restrict__ vec, int n, int n1, float (&out)[32]) {
+    if (n + 32 <= n1 && (((uintptr_t)(vec + n)) & 15) == 0) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float4 t = __ldg((const float4*)(vec + n) + j);
+            out[4 * j] = t.x; out[4 * j + 1] = t.y; out[4 * j + 2] = t.z; out[4 * j + 3] = t.w;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; j++) out[j] = __ldg(vec + min(n + j, n1 - 1));
+    }
 }
 __device__ __forceinline__ void epilogue_chunk(const unsigned (&r)[32], int m, int n, const EpiArgs p, bool row_ok,
                                                long long c_offset = 0) {
@@ -285,16 +303,20 @@ __device__ __forceinline__ void epilogue_chunk(const unsigned (&r)[32], int m, i
 
     if (ep.steps & B200FC_STEP_DEQUANT) {
         if (ep.deq_per_oc) {
+            float sc[32];
+            load_col_vec(ep.deq_per_oc, n, p.n1, sc);
 #pragma unroll
-            for (int j = 0; j < 32; j++) v[j] *= ep.deq_scale * __ldg(ep.deq_per_oc + min(n + j, p.n1 - 1));
+            for (int j = 0; j < 32; j++) v[j] *= ep.deq_scale * sc[j];
         } else {
 #pragma unroll
             for (int j = 0; j < 32; j++) v[j] *= ep.deq_scale;
         }
     }
     if (ep.steps & B200FC_STEP_BIAS) {
+        float bs[32];
+        load_col_vec(ep.bias, n, p.n1, bs);
 #pragma unroll
-        for (int j = 0; j < 32; j++) v[j] += __ldg(ep.bias + min(n + j, p.n1 - 1));
+        for (int j = 0; j < 32; j++) v[j] += bs[j];
     }
     if (ep.steps & B200FC_STEP_GELU) {
 #pragma unroll
@@ -302,8 +324,10 @@ __device__ __forceinline__ void epilogue_chunk(const unsigned (&r)[32], int m, i
     }
     if (ep.steps & B200FC_STEP_QUANT) {
         if (ep.q_per_oc) {
+            float qs[32];
+            load_col_vec(ep.q_per_oc, n, p.n1, qs);
 #pragma unroll
-            for (int j = 0; j < 32; j++) v[j] *= __ldg(ep.q_per_oc + min(n + j, p.n1 - 1));
+            for (int j = 0; j < 32; j++) v[j] *= qs[j];
         } else {
 #pragma unroll
             for (int j = 0; j < 32; j++) v[j] *= ep.q_scale;
