@@ -87,3 +87,21 @@ def test_decode_attention_argument_errors():
     q = H.normal_bf16(rng, (1, 4, 96)); k = H.normal_bf16(rng, (1, 4, 32, 96))
     with pytest.raises(capi.B200FCError):       # head size 96
         run(q, k, k, 1.0)
+
+
+def test_decode_attention_strided_cache_and_padded_heads():
+    """a cache with room for more tokens than are used (token and head strides larger than the data), q and out as
+    slices of wider buffers: every stride of the descriptor is honoured"""
+    rng = np.random.default_rng(13)
+    B, Hq, Hkv, N, D, Ncap, Dpad = 2, 8, 4, 130, 128, 256, 160
+    q_full = H.normal_bf16(rng, (B, Hq, Dpad)); kc = H.normal_bf16(rng, (B, Hkv, Ncap, Dpad)); vc = H.normal_bf16(rng, (B, Hkv, Ncap, Dpad))
+    dq, dk, dv = H.Dev(q_full), H.Dev(kc), H.Dev(vc)
+    out = H.Dev(shape=(B, Hq, Dpad), dtype=np.float32, fill=0xCD)
+    a = capi.Attention(B, Hq, Hkv, N, D, dq.ptr, Hq * Dpad * 2, Dpad * 2, dk.ptr, dv.ptr, Hkv * Ncap * Dpad * 2, Ncap * Dpad * 2,
+                       Dpad * 2, out.ptr, Hq * Dpad * 4, Dpad * 4, capi.F32, None, 0.09)
+    capi.decode_attention(a)
+    capi.sync_check()
+    got = out.numpy()
+    ref = port.decode_attention(q_full[:, :, :D], kc[:, :, :N, :D], vc[:, :, :N, :D], 0.09)
+    assert H.rel_to_max(got[:, :, :D], ref) < 5e-3
+    assert (got[:, :, D:].view(np.uint32) == 0xCDCDCDCD).all()      # nothing written past the head size

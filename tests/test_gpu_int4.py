@@ -133,3 +133,41 @@ def test_int4_export_import_round_trip(tmp_path):
     assert w2.export() == blob
     with pytest.raises(capi.B200FCError):
         capi.Weight.from_blob(blob[: len(blob) - 16])
+
+
+def test_int4_host_buffers_and_k_major_source():
+    """b200fc_matmul_host with 4-bit weights packed from a [K, N] host matrix whose K is no multiple of the group size;
+    bias and GeLU behind the dequantisation, bf16 out"""
+    rng = np.random.default_rng(8)
+    M, K, N = 7, 1000, 384
+    x = H.normal_bf16(rng, (M, K)); W = H.normal_bf16(rng, (K, N), 0.05)
+    q, d = port.quantize_weight_int4(np.ascontiguousarray(W.T))
+    bias = rng.standard_normal(N).astype(np.float32)
+    w = H.pack(W, False, capi.PACK_INT4_GROUP, from_host=True)
+    out = np.full((M, N), 0xCDCD, np.uint16)
+    ep = capi.make_epilogue(out.ctypes.data, N * 2, capi.BF16, capi.STEP_DEQUANT | capi.STEP_BIAS | capi.STEP_GELU, bias.ctypes.data)
+    w.matmul_host(x.ctypes.data, capi.BF16, M, K, K * 2, ep)
+    ref = port.postops(port.gemm_bf16_w4(x, q, d), port.DEQUANT | port.BIAS | port.GELU, port.BF16, bias=bias)
+    assert H.rel_to_max(bf16_to_f32(out), bf16_to_f32(ref)) < 1e-2
+
+
+def test_int4_outliers_and_tiny_groups():
+    """a group dominated by one outlier quantises the rest to zero; a group of tiny values keeps its resolution through
+    its own scale — the per-group scheme's reason to exist.  Stored integers and scales still equal the oracle's."""
+    rng = np.random.default_rng(4)
+    N, K = 256, 512
+    Wf = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    Wf[:, 5] = 3.0                       # outlier in group 0 of every row
+    Wf[:, 128:256] *= 1e-4               # a tiny group
+    W = H.bf16_bits(Wf)
+    q, d = port.quantize_weight_int4(W)
+    w = H.pack(W, True, capi.PACK_INT4_GROUP)
+    unp = H.Dev(shape=(N, K), dtype=np.int8)
+    w.unpack(unp.ptr, K)
+    sc = np.zeros((N, 4), np.float32)
+    w.group_scales(sc.ctypes.data, sc.strides[0])
+    assert np.array_equal(unp.numpy(), q) and np.array_equal(sc, d)
+    assert np.abs(q[:, 128:256]).max() == 7 and d[:, 1].max() < 1e-4
+    x = H.normal_bf16(rng, (3, K))
+    got = H.run_matmul(w, x, capi.F32, steps=capi.STEP_DEQUANT)
+    assert H.rel_to_max(got, port.gemm_bf16_w4(x, q, d)) < 1e-5
