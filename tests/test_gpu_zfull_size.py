@@ -226,3 +226,45 @@ def test_reference_builders_on_cpu():
     r = int8_weight_reference(x, wq, scale)
     assert r.shape == (3, 32) and r.dtype == torch.bfloat16
     assert rel_to_max(r, r) == 0.0
+
+
+@pytest.mark.parametrize("mode", ["int8", "int4"])
+def test_quantised_decode_large_matrix_is_deterministic_and_right(mode):
+    """8192 x 28672 with quantised weights at M = 16: every CTA walks several activation chunks (pre-converted images
+    copied asynchronously into alternating buffers) and most row blocks are summed across CTAs through the scratch.
+    Twenty launches must give identical bits (a race in the ring or in the chunk buffers shows as a flicker), and rows
+    checked against a float64 product of the dequantised weights."""
+    import torch
+    torch.manual_seed(5)
+    M, K, N = 16, 8192, 28672
+    x = torch.randn((M, K), device="cuda").to(torch.bfloat16)
+    if mode == "int8":
+        Wq = torch.randint(-127, 128, (N, K), dtype=torch.int8, device="cuda")
+        sc = torch.rand(N, device="cuda") * 0.019 + 0.001
+        w = capi.Weight(Wq.data_ptr(), capi.S8, K, N, K, True, capi.PACK_INT8_CHANNEL, sc.data_ptr())
+        deq_rows = lambda rows: Wq[rows].double() * sc[rows].double()[:, None]
+    else:
+        W = (torch.randn((N, K), device="cuda") * 0.02).to(torch.bfloat16)
+        w = capi.Weight(W.data_ptr(), capi.BF16, K, N, K * 2, True, capi.PACK_INT4_GROUP)
+        q = torch.empty((N, K), dtype=torch.int8, device="cuda")
+        w.unpack(q.data_ptr(), K)
+        gs = np.zeros((N, K // 128), np.float32)
+        w.group_scales(gs.ctypes.data, gs.strides[0])
+        gs_t = torch.from_numpy(gs).cuda()
+        deq_rows = lambda rows: q[rows].double() * gs_t[rows].double().repeat_interleave(128, dim=1)
+    out = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    ep = capi.make_epilogue(out.data_ptr(), N * 4, capi.F32, capi.STEP_DEQUANT)
+    first = None
+    for it in range(20):
+        out.fill_(float("nan"))
+        w.matmul(x.data_ptr(), capi.BF16, M, K, K * 2, ep)
+        capi.sync_check()
+        cur = out.clone()
+        if first is None:
+            first = cur
+        else:
+            assert torch.equal(first.view(torch.int32), cur.view(torch.int32)), "launch %d differs from the first" % it
+    rows = torch.arange(0, N, 97, device="cuda")
+    ref = x.double() @ deq_rows(rows).T
+    err = (first[:, rows].double() - ref).abs().max() / ref.abs().max()
+    assert err.item() < 1e-5
