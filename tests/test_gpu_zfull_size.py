@@ -228,6 +228,7 @@ def test_reference_builders_on_cpu():
     assert rel_to_max(r, r) == 0.0
 
 
+@pytest.mark.gpu
 @pytest.mark.parametrize("mode", ["int8", "int4"])
 def test_quantised_decode_large_matrix_is_deterministic_and_right(mode):
     """8192 x 28672 with quantised weights at M = 16: every CTA walks several activation chunks (pre-converted images
