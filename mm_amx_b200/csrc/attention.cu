@@ -342,6 +342,7 @@ int launch_decode_attention(const b200fc_attention_t& a, cudaStream_t s) {
         set_error("decode_attention: need H %% Hkv == 0 and at most 16 query heads per kv head");
         return B200FC_ERR_INVALID;
     }
+    if (a.B > 65535 || a.Hkv > 65535) { set_error("decode_attention: at most 65535 sequences and kv heads per call"); return B200FC_ERR_INVALID; }
     if (a.D != 64 && a.D != 128) { set_error("decode_attention: head size must be 64 or 128"); return B200FC_ERR_UNSUPPORTED; }
     if (a.out_dtype != B200FC_BF16 && a.out_dtype != B200FC_F32) { set_error("decode_attention: out_dtype must be bf16 or f32"); return B200FC_ERR_INVALID; }
     if (((uintptr_t)a.k & 15) || ((uintptr_t)a.v & 15) || (a.kv_batch_stride & 15) || (a.kv_head_stride & 15) || (a.kv_token_stride & 15) ||
