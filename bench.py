@@ -701,7 +701,7 @@ def other_configs(torch, capi, dev, peaks, only=None):
             e1.record(); torch.cuda.synchronize()
         return e0.elapsed_time(e1) * 1e-3 / reps / n_launch
 
-    # config 1: A[256,4096] x B[4096,4096] + bias -> fp32
+    # single bf16 Linear: A[256,4096] x B[4096,4096] + bias -> fp32
     M, K, N = 256, 4096, 4096
     if want("bf16_linear_256x4096x4096_bias_f32"):
         A = (torch.rand((M, K), generator=g, device=dev) * 2 - 1).to(torch.bfloat16)
@@ -718,7 +718,7 @@ def other_configs(torch, capi, dev, peaks, only=None):
                                                        "gbs": nbytes / t / 1e9, "hbm_frac": nbytes / t / 1e9 / peaks["hbm_gbs"],
                                                        "weight_sets": len(ws)}
         del ws
-    # config 3: int8-weight decode GEMV
+    # int8-weight decode GEMV (fc16m-style)
     K = 4096
     for N in (4096, 11008):
         if not any(want("int8w_gemv_M%d_4096x%d" % (M, N)) for M in (1, 4, 16)):
@@ -809,7 +809,7 @@ def other_configs(torch, capi, dev, peaks, only=None):
         nbytes = kv_bytes + 2 * B * Hq * D * 2
         out[key] = {"us": t * 1e6, "gbs": nbytes / t / 1e9, "hbm_frac": nbytes / t / 1e9 / peaks["hbm_gbs"], "caches": nset}
         del caches, descs
-    # config 4: int8 x int8 GEMM with quantised post-ops
+    # int8 x int8 GEMM with quantised post-ops
     M, K, N = 2048, 4096, 4096
     if only is not None and not only.startswith("int8_gemm_2048x4096x4096_"):
         return out

@@ -1,4 +1,4 @@
-"""GPU: the BASELINE configurations at their FULL sizes, where the CPU oracle would take minutes.
+"""GPU: the benchmark configurations at their FULL sizes, where the CPU oracle would take minutes.
 
 The small-shape tests pin the kernels against the oracle bit for bit; here the same entry points run the shapes the
 benchmark is quoted on and are checked against an independent full-size computation on the same GPU (torch fp32 /
@@ -31,7 +31,7 @@ def mlp_reference(x, gate, up, down):
 
 
 def int8_weight_reference(x, wq, scale):
-    """bf16 activations x int8 weights, per-output-channel fp32 scale, bf16 output (BASELINE config 3)."""
+    """bf16 activations x int8 weights, per-output-channel fp32 scale, bf16 output (the fc16m-style decode configuration of the benchmark list)."""
     return ((x.float() @ wq.float().T) * scale[None, :]).to(torch.bfloat16)
 
 
