@@ -359,3 +359,36 @@ def test_decode_ctas_per_sm_setter():
     assert H.rel_to_max(got1, ref) < 1e-5 and H.rel_to_max(got2, ref) < 1e-5
     with pytest.raises(capi.B200FCError):
         capi.set_decode_ctas_per_sm(3)
+
+
+def test_tensor_memory_decode_kernel_all_row_counts_subprocess():
+    """The decode kernel on the tcgen05 tensor cores takes calls with more than 8 rows by default; B200FC_GEMV_TC=2 (read
+    once per process, hence the child) routes every decode-shaped bf16 call through it: M = 1..16, K and N tails, a column
+    range, bias + GeLU, exact on two-valued data."""
+    import os, subprocess, sys, textwrap
+    code = textwrap.dedent("""
+        import numpy as np
+        import helpers as H
+        from mm_amx_b200 import capi
+        from oracle import port
+        rng = np.random.default_rng(3)
+        for (M, K, N) in [(1, 4096, 4096), (3, 1000, 777), (8, 2560, 10752), (11, 320, 257), (16, 8192, 1536)]:
+            A = H.two_valued_bf16(rng, (M, K)); B = H.two_valued_bf16(rng, (K, N))
+            w = H.pack(B)
+            got = H.run_matmul(w, A, capi.F32)
+            assert np.array_equal(got, port.gemm_bf16(A, B)), (M, K, N)
+        M, K, N = 5, 1536, 1000
+        A = H.normal_bf16(rng, (M, K)); B = H.normal_bf16(rng, (N, K), 0.02)
+        bias = rng.standard_normal(N).astype(np.float32)
+        w = H.pack(B, True)
+        got = H.run_matmul(w, A, capi.F32, steps=capi.STEP_BIAS | capi.STEP_GELU, bias=bias, n0=128, n1=900)
+        ref = port.postops(port.gemm_bf16(A, B, transposeB=True), port.BIAS | port.GELU, port.F32, bias=bias)
+        assert H.rel_to_max(got[:, 128:900], ref[:, 128:900]) < 1e-5
+        assert (np.delete(got, np.s_[128:900], axis=1).view(np.uint32) == 0xCDCDCDCD).all()
+        print("tc ok")
+    """)
+    env = dict(os.environ, B200FC_GEMV_TC="2")
+    here = os.path.dirname(os.path.abspath(__file__))
+    env["PYTHONPATH"] = os.pathsep.join([here, os.path.dirname(here), env.get("PYTHONPATH", "")])
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "tc ok" in r.stdout, r.stdout + r.stderr
