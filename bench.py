@@ -770,6 +770,23 @@ def other_configs(torch, capi, dev, peaks, only=None):
         out["int8w_gemv_M%d_8192x28672" % M] = {"us": t * 1e6, "gbs": nbytes / t / 1e9,
                                                 "hbm_frac": nbytes / t / 1e9 / peaks["hbm_gbs"], "weight_sets": len(ws)}
     del ws
+    # the same large matrix with bf16 weights (470 MB): M = 1 runs the mma.sync decode kernel, M = 16 the tcgen05 one
+    K, N = 8192, 28672
+    ws = []
+    for _ in range(3 if any(want("bf16w_gemv_M%d_8192x28672" % M) for M in (1, 16)) else 0):
+        B = (torch.randn((N, K), generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        ws.append(capi.Weight(B.data_ptr(), capi.BF16, K, N, K * 2, True)); del B
+    for M in (1, 16):
+        if not want("bf16w_gemv_M%d_8192x28672" % M):
+            continue
+        x = torch.randn((M, K), generator=g, device=dev).to(torch.bfloat16)
+        C = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        ep = capi.make_epilogue(C.data_ptr(), N * 2, capi.BF16, 0)
+        t = timed_graph(lambda s: [w.matmul(x.data_ptr(), capi.BF16, M, K, K * 2, ep, stream=s) for w in ws], len(ws))
+        nbytes = K * N * 2 + M * (K + N) * 2
+        out["bf16w_gemv_M%d_8192x28672" % M] = {"us": t * 1e6, "gbs": nbytes / t / 1e9,
+                                                "hbm_frac": nbytes / t / 1e9 / peaks["hbm_gbs"], "weight_sets": len(ws)}
+    del ws
     # 4-bit group-quantised weights (bf16 matrix quantised by the library: one fp32 scale per 128 K and output channel),
     # same kernel family; bytes = the stored nibbles + the group scales + activations in and out
     for K, N in ((4096, 11008), (8192, 28672)):
