@@ -1,5 +1,6 @@
 // C ABI of the b200fc library (declared in include/b200fc.h): argument checking, packed-weight and MLP objects,
 // dispatch between the decode (gemv.cu) and prefill (gemm_tc.cu) kernels, host-buffer convenience entry points.
+#include <algorithm>
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
@@ -819,6 +820,156 @@ int b200fc_mlp_down_allreduce(b200fc_mlp_t* h, int M, const b200fc_allreduce_t* 
                                     (cudaStream_t)stream);
 }
 
+// Row chunks of the host-buffer pipeline of b200fc_mlp_run_host: gu = rows per gate/up launch (each preceded by the
+// host-to-device copy of its rows), dn = rows per down launch (each followed by the device-to-host copy of its rows);
+// both lists sum to M.  The two lists are chosen independently: a handful of growing sequences (short chunks first,
+// so that little of the first copy is exposed) for gate/up, the same sequences reversed and a halving sequence for
+// down (short chunks last), each pair rated by a small model of the three engines — the copy engines at PCIe speed and
+// the GEMMs as whole waves of 256 x 256 tiles over the CTA pairs, which is what makes a chunk of 7 x 256 rows of the
+// Llama-70B down projection (224 tiles on 74 pairs) cost four waves instead of three.  The model only has to rank
+// plans; measured on Llama-70B at M = 4096 its first choices are the measured first choices.
+// B200FC_HOST_PLAN="a,b,c;d,e,f" (chunks in tiles of 256 rows; the last entry of each list takes what is left)
+// replaces the choice, for experiments.
+namespace {
+constexpr int kPlanTile = 256;
+
+struct PlanModel {
+    double t_gu_wave, t_dn_wave;  // seconds per wave of tiles
+    double h2d_tile, d2h_tile;    // seconds per 256 rows
+    int cols_gu, cols_dn, pairs;
+    int slabs_gu, slabs_dn;       // K of the two GEMMs in 64-element slabs
+    // rounds of tiles a launch of `rows` row tiles x `cols` column tiles takes; a short ragged last round of a long-K
+    // GEMM is split along K by the launcher (launch_gemm_tc) and costs well under a round
+    double waves(int rows, int cols, int k_slabs) const {
+        const long long tiles = (long long)rows * cols;
+        const long long full = tiles / pairs, rem = tiles % pairs;
+        if (rem == 0) return (double)full;
+        if (full == 0 && tiles * 2 <= pairs && k_slabs >= 16) {  // few tiles: the launcher splits K over the idle pairs
+            long long sp = std::min<long long>(std::min<long long>(8, pairs / tiles), k_slabs / 8);
+            return 1.0 / (double)std::max<long long>(1, sp) + 0.35;  // (+ the slab round trip and the reduction kernel)
+        }
+        const bool split = full > 0 && rem * 4 <= pairs && k_slabs >= 96 && (rem / rows == 0 || rem % rows == 0);
+        return (double)full + (split ? 0.45 : 1.0);
+    }
+    double run(const std::vector<int>& gu, const std::vector<int>& dn) const {
+        const double copy_lat = 8e-6, launch_lat = 3e-6;
+        double t_in = 0, t_cmp = 0, t_out = 0;
+        size_t gi = 0;
+        int done = 0, d0 = 0;
+        for (size_t j = 0; j < dn.size(); j++) {
+            const int d1 = d0 + dn[j];
+            while (done < d1 && gi < gu.size()) {
+                t_in += gu[gi] * h2d_tile + copy_lat;
+                t_cmp = std::max(t_cmp, t_in) + waves(gu[gi], cols_gu, slabs_gu) * t_gu_wave + launch_lat;
+                done += gu[gi++];
+            }
+            t_cmp += waves(dn[j], cols_dn, slabs_dn) * t_dn_wave + launch_lat;
+            t_out = std::max(t_out, t_cmp) + dn[j] * d2h_tile + copy_lat;
+            d0 = d1;
+        }
+        return t_out;
+    }
+};
+
+// growing sequence: first, then each chunk `ratio` times the one before, at most `cap`, until `tiles` are covered
+std::vector<int> growing(int tiles, int first, double ratio, int cap) {
+    std::vector<int> v;
+    int left = tiles;
+    double cur = first;
+    while (left > 0) {
+        int c = std::min(left, std::min(cap, (int)(cur + 0.5)));
+        if (c < 1) c = 1;
+        v.push_back(c);
+        left -= c;
+        cur = std::min((double)cap, std::max(cur * ratio, cur));
+    }
+    if (v.size() > 1 && v.back() * 2 < v[v.size() - 2]) {  // a crumb at the end joins its neighbour
+        v[v.size() - 2] += v.back();
+        v.pop_back();
+    }
+    return v;
+}
+}  // namespace
+
+static void host_plan(Mlp& m, int M, std::vector<int>* gu, std::vector<int>* dn) {
+    const int tile = kPlanTile;
+    const int tiles = (M + tile - 1) / tile;
+    auto finish = [&](std::vector<int>& v) {  // tiles -> rows, clipped to M
+        int left = M;
+        std::vector<int> r;
+        for (size_t i = 0; i < v.size() && left > 0; i++) {
+            int rows = (i + 1 == v.size()) ? left : (int)std::min<long long>(left, (long long)v[i] * tile);
+            if (rows > 0) r.push_back(rows);
+            left -= rows;
+        }
+        if (left > 0) r.push_back(left);
+        v.swap(r);
+    };
+    std::vector<int> g, d;
+    const char* env = getenv("B200FC_HOST_PLAN");
+    if (env && *env) {
+        std::vector<int>* cur = &g;
+        int val = 0; bool have = false;
+        for (const char* c = env;; c++) {
+            if (*c >= '0' && *c <= '9') { val = val * 10 + (*c - '0'); have = true; continue; }
+            if (have && val > 0) cur->push_back(val);
+            val = 0; have = false;
+            if (*c == ';') cur = &d;
+            if (!*c) break;
+        }
+        if (!g.empty() && !d.empty()) {
+            finish(g); finish(d);
+            gu->swap(g); dn->swap(d);
+            return;
+        }
+    }
+    if (m.plan_M == M && !m.plan_gu.empty()) { *gu = m.plan_gu; *dn = m.plan_dn; return; }
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    PlanModel pm;
+    pm.pairs = std::max(1, sms / 2);
+    const double pair_rate = 1.35e15 / 74.0;  // flop/s of one CTA pair in a long launch
+    pm.cols_gu = (2 * m.Ns + 255) / 256;
+    pm.cols_dn = (m.K + 255) / 256;
+    pm.slabs_gu = (m.K + 63) / 64;
+    pm.slabs_dn = (m.Ns + 63) / 64;
+    pm.t_gu_wave = 2.0 * 256 * 256 * m.K / pair_rate;
+    pm.t_dn_wave = 2.0 * 256 * 256 * m.Ns / pair_rate;
+    pm.h2d_tile = (double)tile * m.K * 2 / 50e9;
+    pm.d2h_tile = (double)tile * m.K * 2 / 45e9;
+    std::vector<std::vector<int>> fam_g, fam_d;
+    const int firsts[] = {1, 2, 3, 4};
+    const double ratios[] = {1.0, 1.5, 2.0};
+    const int caps[] = {4, 6, 8, 12, 16};
+    for (int f : firsts) for (double q : ratios) for (int c : caps) {
+        if (tiles > 256 && c < 8) continue;  // very large batches: keep the lists short
+        std::vector<int> v = growing(tiles, f, q, c);
+        fam_g.push_back(v);
+        std::reverse(v.begin(), v.end());
+        fam_d.push_back(v);
+    }
+    for (double frac : {0.5, 0.55, 0.6}) {  // halving sequence: most rows first, the rest in ever shorter chunks
+        std::vector<int> v;
+        int left = tiles;
+        while (left > 0) {
+            int c = std::max(1, std::min(left, (int)(left * frac + 0.999)));
+            if (tiles > 256 && left * 2 < tiles && c < 8) c = std::min(left, 8);
+            v.push_back(c);
+            left -= c;
+        }
+        fam_d.push_back(v);
+    }
+    double best = 1e30;
+    for (const auto& a : fam_g) for (const auto& b : fam_d) {
+        const double t = pm.run(a, b);
+        if (t < best) { best = t; g = a; d = b; }
+    }
+    finish(g); finish(d);
+    m.plan_M = M; m.plan_gu = g; m.plan_dn = d;
+    gu->swap(g); dn->swap(d);
+}
+
 int b200fc_mlp_run_host(b200fc_mlp_t* h, const void* x, int64_t ldx, int M, void* out, int64_t ldo, void* stream) {
     cudaStream_t s = (cudaStream_t)stream;
     if (!h || !x || !out || M <= 0) { set_error("mlp_run_host: null pointer or M <= 0"); return B200FC_ERR_INVALID; }
@@ -835,17 +986,19 @@ int b200fc_mlp_run_host(b200fc_mlp_t* h, const void* x, int64_t ldx, int M, void
         B200FC_CUDA(cudaMemcpy2DAsync(out, (size_t)ldo, m.stage_o, row, row, (size_t)M, cudaMemcpyDeviceToHost, s));
         return check_kernel_status(s);
     }
-    // Large batches: rows are independent, so the batch is cut into chunks of 1024 rows that flow through three
-    // streams — host-to-device copy, compute, device-to-host copy — and the PCIe transfers of neighbouring chunks
-    // overlap the tensor-core work (the copy engines are full duplex).
-    const int chunk = 1024;  // 4 x 256-row tiles per column block: keeps the GEMM waves full
-    const int n_chunks = (M + chunk - 1) / chunk;
+    // Large batches: rows are independent, so the batch flows through three streams — host-to-device copy,
+    // compute, device-to-host copy — and the PCIe transfers overlap the tensor-core work (the copy engines are full
+    // duplex).  The gate/up projection and the down projection are cut into row chunks independently of one
+    // another (host_plan): short chunks at the head of the first and at the tail of the second keep the exposed
+    // copies small, long chunks in between keep the GEMM waves full.
+    std::vector<int> gu_rows, dn_rows;
+    host_plan(m, M, &gu_rows, &dn_rows);
     if (!m.pipe_streams[0]) {
         for (int i = 0; i < 3; i++) B200FC_CUDA(cudaStreamCreateWithFlags(&m.pipe_streams[i], cudaStreamNonBlocking));
         B200FC_CUDA(cudaEventCreateWithFlags(&m.ev_fork, cudaEventDisableTiming));
         B200FC_CUDA(cudaEventCreateWithFlags(&m.ev_join, cudaEventDisableTiming));
     }
-    while ((int)m.ev_in.size() < n_chunks) {
+    while (m.ev_in.size() < gu_rows.size() || m.ev_out.size() < dn_rows.size()) {
         cudaEvent_t a, b;
         B200FC_CUDA(cudaEventCreateWithFlags(&a, cudaEventDisableTiming));
         B200FC_CUDA(cudaEventCreateWithFlags(&b, cudaEventDisableTiming));
@@ -857,27 +1010,35 @@ int b200fc_mlp_run_host(b200fc_mlp_t* h, const void* x, int64_t ldx, int M, void
     cudaStream_t s_in = m.pipe_streams[0], s_cmp = m.pipe_streams[1], s_out = m.pipe_streams[2];
     B200FC_CUDA(cudaEventRecord(m.ev_fork, s));
     for (int i = 0; i < 3; i++) B200FC_CUDA(cudaStreamWaitEvent(m.pipe_streams[i], m.ev_fork, 0));
-    for (int c = 0; c < n_chunks; c++) {
-        const int r0 = c * chunk, rows = (M - r0 < chunk) ? (M - r0) : chunk;
-        char* xs = (char*)m.stage_x + (size_t)r0 * row;
-        char* os = (char*)m.stage_o + (size_t)r0 * row;
-        char* as = (char*)m.act + (size_t)r0 * m.Ns * 2;
-        B200FC_CUDA(cudaMemcpy2DAsync(xs, row, (const char*)x + (size_t)r0 * ldx, (size_t)ldx, row, (size_t)rows,
-                                      cudaMemcpyHostToDevice, s_in));
-        B200FC_CUDA(cudaEventRecord(m.ev_in[c], s_in));
-        B200FC_CUDA(cudaStreamWaitEvent(s_cmp, m.ev_in[c], 0));
-        b200fc_epilogue_t e1 = {};
-        e1.steps = B200FC_STEP_SILU_MUL; e1.out_dtype = B200FC_BF16; e1.C = as; e1.ldc_bytes = (int64_t)m.Ns * 2;
-        rc = matmul_device(m.gate_up, nullptr, xs, B200FC_BF16, rows, m.K, (int64_t)row, 0, 2 * m.Ns, &e1, s_cmp);
-        if (rc) return rc;
+    size_t gi = 0;
+    int gu_done = 0, d0 = 0;  // rows whose gate/up launch has been issued; first row of the next down chunk
+    for (size_t j = 0; j < dn_rows.size(); j++) {
+        const int d1 = d0 + dn_rows[j];
+        while (gu_done < d1) {  // the activation rows this down chunk reads
+            const int rows = gu_rows[gi];
+            char* xs = (char*)m.stage_x + (size_t)gu_done * row;
+            B200FC_CUDA(cudaMemcpy2DAsync(xs, row, (const char*)x + (size_t)gu_done * ldx, (size_t)ldx, row,
+                                          (size_t)rows, cudaMemcpyHostToDevice, s_in));
+            B200FC_CUDA(cudaEventRecord(m.ev_in[gi], s_in));
+            B200FC_CUDA(cudaStreamWaitEvent(s_cmp, m.ev_in[gi], 0));
+            b200fc_epilogue_t e1 = {};
+            e1.steps = B200FC_STEP_SILU_MUL; e1.out_dtype = B200FC_BF16;
+            e1.C = (char*)m.act + (size_t)gu_done * m.Ns * 2; e1.ldc_bytes = (int64_t)m.Ns * 2;
+            rc = matmul_device(m.gate_up, nullptr, xs, B200FC_BF16, rows, m.K, (int64_t)row, 0, 2 * m.Ns, &e1, s_cmp);
+            if (rc) return rc;
+            gu_done += rows; gi++;
+        }
+        char* os = (char*)m.stage_o + (size_t)d0 * row;
         b200fc_epilogue_t e2 = {};
         e2.steps = 0; e2.out_dtype = B200FC_BF16; e2.C = os; e2.ldc_bytes = (int64_t)row;
-        rc = matmul_device(m.down, nullptr, as, B200FC_BF16, rows, m.Ns, (int64_t)m.Ns * 2, 0, m.K, &e2, s_cmp);
+        rc = matmul_device(m.down, nullptr, (char*)m.act + (size_t)d0 * m.Ns * 2, B200FC_BF16, d1 - d0, m.Ns,
+                           (int64_t)m.Ns * 2, 0, m.K, &e2, s_cmp);
         if (rc) return rc;
-        B200FC_CUDA(cudaEventRecord(m.ev_out[c], s_cmp));
-        B200FC_CUDA(cudaStreamWaitEvent(s_out, m.ev_out[c], 0));
-        B200FC_CUDA(cudaMemcpy2DAsync((char*)out + (size_t)r0 * ldo, (size_t)ldo, os, row, row, (size_t)rows,
+        B200FC_CUDA(cudaEventRecord(m.ev_out[j], s_cmp));
+        B200FC_CUDA(cudaStreamWaitEvent(s_out, m.ev_out[j], 0));
+        B200FC_CUDA(cudaMemcpy2DAsync((char*)out + (size_t)d0 * ldo, (size_t)ldo, os, row, row, (size_t)(d1 - d0),
                                       cudaMemcpyDeviceToHost, s_out));
+        d0 = d1;
     }
     B200FC_CUDA(cudaEventRecord(m.ev_join, s_out));
     B200FC_CUDA(cudaStreamWaitEvent(s, m.ev_join, 0));

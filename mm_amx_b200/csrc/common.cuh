@@ -69,6 +69,8 @@ struct Mlp {
     cudaStream_t pipe_streams[3] = {nullptr, nullptr, nullptr};
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     std::vector<cudaEvent_t> ev_in, ev_out;
+    int plan_M = 0;                                 // row chunks of that pipeline, as planned for plan_M rows
+    std::vector<int> plan_gu, plan_dn;
 };
 
 // cudaFuncSetAttribute applies to the current device only.  Runs `set_attr` (returns a status code) the first time

@@ -60,6 +60,9 @@ struct GemmParams {
     // slab `split` of a workspace ([splits][M][row pitch]) and a second kernel reduces and runs the post-ops
     int splits;
     long long split_stride;  // bytes between workspace slabs
+    // 2-CTA kernel, splits == 1: > 0 = only the first item_limit tiles (in tile order) are computed by this launch; the
+    // launcher hands the few tiles of a ragged last round to a second, K-split launch instead (launch_gemm_tc)
+    int item_limit = 0;
     // Fused tensor-parallel all-reduce (2-CTA kernel, ar_world > 0).  The epilogue stores this rank's bf16 tile into
     // its replica of a symmetric "partial" buffer (ep.C) and bumps the tile's arrival counter on the tile's owner
     // rank; the last CTA pairs of the grid do not multiply but reduce the tiles this rank owns.
@@ -713,7 +716,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int num_pairs = p.ar_world ? p.ar_gemm_pairs : grid_pairs;  // pairs that take part in the multiplication
     const bool comm_role = p.ar_world && pair >= num_pairs;
     const int num_tiles = p.tiles_m * p.tiles_n;  // tiles of 256 x BN
-    const int num_items = num_tiles * p.splits;   // (tile, K split) work items
+    const int num_items = p.item_limit > 0 ? p.item_limit : num_tiles * p.splits;   // (tile, K split) work items
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < C::STAGES; i++) {
@@ -1062,7 +1065,8 @@ int launch_cfg2(const CUtensorMap& ma, const CUtensorMap& mw, GemmParams p, cuda
         p.ep.ldc = (long long)pitch * 4;
         p.vec_ok = (p.n0 % 4) == 0 ? 1 : 0;
     }
-    int items = tiles * splits;
+    if (splits > 1) p.item_limit = 0;
+    int items = p.item_limit > 0 ? p.item_limit : tiles * splits;
     int pairs = items < max_pairs ? items : max_pairs;
     gemm_tc2_kernel<BN, I8><<<2 * pairs, NUM_THREADS, C::SMEM_BYTES, s>>>(ma, mw, p);
     count_launch();
@@ -1088,6 +1092,16 @@ int launch_cfg2(const CUtensorMap& ma, const CUtensorMap& mw, GemmParams p, cuda
     }
     (void)final_vec;
     return B200FC_OK;
+}
+
+// B200FC_GEMM_TAIL=0 keeps the tiles of a ragged last round in the main launch (for measurements)
+bool tail_split_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("B200FC_GEMM_TAIL");
+        v = e ? atoi(e) : 1;
+    }
+    return v != 0;
 }
 
 // 0 = choose by shape, 1 = force the 1-CTA kernel, 2 = force the 2-CTA kernel (B200FC_GEMM_CTAS, for experiments)
@@ -1223,6 +1237,29 @@ int launch_gemm_tc(const void* W_data, int w_dtype, int W_K_pad, int W_N_pad, co
         rc = make_map(&mw, W_data, i8, (uint64_t)W_K_pad, (uint64_t)W_N_pad, (uint64_t)W_K_pad * (i8 ? 1 : 2),
                       (uint32_t)(bn2 / 2));
         if (rc) return rc;
+        // Ragged last round: tiles % pairs tiles would occupy a few CTA pairs for a whole tile time while the others
+        // idle (Llama-70B gate/up at M = 1024: 896 tiles on 74 pairs, 8 left over).  When the tile time is long (K >=
+        // 6144) and the left-over tiles (the last ones in tile order) form one rectangle — whole column blocks, or the
+        // bottom of the last one — the main launch stops before them and they go through this function again as a
+        // GEMM of their own, which takes the K-split route (a few tiles, every pair busy for a fraction of a tile
+        // time, then the reduction kernel with the same post-ops).
+        const int tiles = p.tiles_m * p.tiles_n, pairs = num_sms() / 2;
+        const int rem = tiles % pairs;
+        const int last_cols = nspan - (p.tiles_n - 1) * bn2;
+        const int whole = rem / p.tiles_m, part = rem % p.tiles_m;   // whole column blocks / tiles of a partial one
+        if (tail_split_enabled() && tiles > pairs && rem > 0 && (whole == 0 || part == 0) && rem * 4 <= pairs &&
+            p.k_slabs >= 96 && last_cols > 128 && !ep.mc_reduce) {
+            p.item_limit = tiles - rem;
+            rc = i8 ? launch_cfg2<256, true>(ma, mw, p, s) : launch_cfg2<256, false>(ma, mw, p, s);
+            if (rc) return rc;
+            const long long row0 = whole ? 0 : (long long)(p.tiles_m - part) * 2 * BM;
+            const int col0 = n0 + (p.tiles_n - (whole ? whole : 1)) * bn2;
+            Epilogue e2 = ep;
+            e2.C = (char*)ep.C + row0 * ep.ldc;
+            if (ep.residual) e2.residual = (const char*)ep.residual + row0 * ep.ld_res;
+            return launch_gemm_tc(W_data, w_dtype, W_K_pad, W_N_pad, (const char*)A + row0 * lda, dtypeA, (int)(M - row0), K, lda,
+                                  col0, n1, e2, s);
+        }
         return i8 ? launch_cfg2<256, true>(ma, mw, p, s) : launch_cfg2<256, false>(ma, mw, p, s);
     }
     rc = make_map(&mw, W_data, i8, (uint64_t)W_K_pad, (uint64_t)W_N_pad, (uint64_t)W_K_pad * (i8 ? 1 : 2), (uint32_t)bn);

@@ -67,6 +67,19 @@ def test_decode_attention_sequence_lengths_and_splits(monkeypatch):
     assert H.rel_to_max(got, ref) < 5e-3
 
 
+def test_decode_attention_repeated_calls_of_mixed_shapes():
+    """calls of different shapes follow one another on a stream and share the workspace of the sub-states (it grows and
+    is reused); every call must see only its own sub-states"""
+    rng = np.random.default_rng(21)
+    shapes = [(2, 8, 8, 3000, 128), (2, 8, 8, 3000, 128), (1, 16, 1, 4096, 128), (3, 16, 4, 1111, 64), (2, 8, 8, 3000, 128)]
+    for B, Hq, Hkv, N, D in shapes:
+        q = H.normal_bf16(rng, (B, Hq, D)); k = H.normal_bf16(rng, (B, Hkv, N, D)); v = H.normal_bf16(rng, (B, Hkv, N, D))
+        scale = 1.0 / np.sqrt(D)
+        ref = port.decode_attention(q, k, v, scale)
+        for _ in range(2):
+            assert H.rel_to_max(run(q, k, v, scale), ref) < 5e-3
+
+
 def test_decode_attention_uniform_probabilities_exact():
     """q = 0 makes every probability 1/n: the output is the mean of v; with +-0.5 values and n a power of two all sums
     are exact, so fp32 output equals the oracle bit for bit"""

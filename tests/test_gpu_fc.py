@@ -230,6 +230,31 @@ def test_split_k_shapes_exact(M, K, N):
     assert np.abs(got8.astype(np.int32) - ref8.astype(np.int32)).max() <= 1
 
 
+def test_ragged_last_round_goes_through_a_k_split_launch():
+    """76 tiles of 256 x 256 on 74 CTA pairs with a long K: the main launch stops after 74 tiles and the two left-over
+    tiles (bottom rows of the last column block; the last row tile and the last column block are partial) run as a
+    K-split GEMM of their own.  Exact arithmetic (two-valued data), so every element must match however K was cut."""
+    rng = np.random.default_rng(76)
+    M, K, N = 1000, 6144, 5056
+    A = H.two_valued_bf16(rng, (M, K)); B = H.two_valued_bf16(rng, (K, N))
+    bias = (rng.integers(-8, 9, N) * 0.25).astype(np.float32)
+    w = H.pack(B)
+    ref = port.gemm_bf16(A, B)
+    got = H.run_matmul(w, A, capi.F32, steps=capi.STEP_BIAS, bias=bias, n0=256)       # 19 column blocks, the last 192 wide
+    assert np.array_equal(got[:, 256:], port.postops(ref, port.BIAS, port.F32, bias=bias)[:, 256:])
+    assert (got[:, :256].view(np.uint32) == 0xCDCDCDCD).all()
+    got = H.run_matmul(w, A[:512], capi.BF16, n0=0, n1=4864)                          # 2 x 19 tiles = 38: one round, no split
+    assert np.array_equal(got[:, :4864], port.postops(ref[:512], 0, port.BF16)[:, :4864])
+    got = H.run_matmul(w, A, capi.BF16, n0=192)                                       # 4 x 19 tiles again, bf16 output
+    assert np.array_equal(got[:, 192:], port.postops(ref, 0, port.BF16)[:, 192:])
+    # 2 x 38 tiles: the left-over is the whole last column block (all rows of it)
+    M, N = 300, 9728
+    A = H.two_valued_bf16(rng, (M, K)); B = H.two_valued_bf16(rng, (K, N))
+    bias = (rng.integers(-8, 9, N) * 0.25).astype(np.float32)
+    got = H.run_matmul(H.pack(B), A, capi.F32, steps=capi.STEP_BIAS, bias=bias)
+    assert np.array_equal(got, port.postops(port.gemm_bf16(A, B), port.BIAS, port.F32, bias=bias))
+
+
 @pytest.mark.parametrize("M,K,N", [(512, 192, 10280), (300, 128, 20000), (1024, 64, 5000), (700, 96, 7177)])
 def test_many_tiles_exact(M, K, N):
     """more 256 x 256 tiles than CTA pairs: every pair walks several tiles, both accumulator buffers get reused"""
