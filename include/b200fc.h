@@ -209,7 +209,10 @@ typedef struct {
     int comm_sms;            /* SMs that reduce instead of multiplying from the start (even; 8 measured best at 8 GPUs) */
 } b200fc_allreduce_t;
 int b200fc_mlp_down_allreduce(b200fc_mlp_t* mlp, int M, const b200fc_allreduce_t* ar, void* stream);
-/* x and out in HOST memory; copies, runs, copies back, synchronises. */
+/* x and out in HOST memory; copies, runs, copies back, synchronises.  From M = 2048 on the rows flow through a
+ * copy-in / compute / copy-out pipeline over three internal streams (short row chunks first and last, so that little of
+ * the PCIe time is exposed), which needs pinned host buffers to overlap; results per row are those of b200fc_mlp_run up
+ * to the last bit of a bf16 (a short chunk may take the K-split route of the GEMM, which adds in another order). */
 int b200fc_mlp_run_host(b200fc_mlp_t* mlp, const void* x, int64_t ldx_bytes, int M, void* out, int64_t ldo_bytes,
                         void* stream);
 /* The same forward for decode-shaped batches (1 <= M <= 16) WITHOUT any allocation — no counterpart in the
