@@ -181,6 +181,11 @@ struct EpiArgs {       // what the epilogue of one 32-column chunk needs to know
     int vec_ok, acc_is_int, n1;
     int M;             // rows of the output
     unsigned* tile;    // this warp's staging tile in shared memory (EPI_TILE_WORDS words)
+    // the chunk's 32 per-column values, staged in shared memory ahead of the tile (16-byte aligned), or null: read
+    // them from global memory
+    const float* cv_deq = nullptr;
+    const float* cv_bias = nullptr;
+    const float* cv_q = nullptr;
 };
 // 32 rows x 32 four-byte values, one row per lane in registers -> global memory with full-line stores: the tile goes
 // through shared memory and comes back with eight lanes per row (16 bytes each), so that one store instruction writes
@@ -217,6 +222,18 @@ __device__ __forceinline__ void load_col_vec(const float* __restrict__ vec, int 
     } else {
 #pragma unroll
         for (int j = 0; j < 32; j++) out[j] = __ldg(vec + min(n + j, n1 - 1));
+    }
+}
+// the same 32 values from the warp's staged copy (every lane reads the same addresses: broadcasts)
+__device__ __forceinline__ void load_col_vec(const float* staged, const float* __restrict__ vec, int n, int n1, float (&out)[32]) {
+    if (staged) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float4 t = ((const float4*)staged)[j];
+            out[4 * j] = t.x; out[4 * j + 1] = t.y; out[4 * j + 2] = t.z; out[4 * j + 3] = t.w;
+        }
+    } else {
+        load_col_vec(vec, n, n1, out);
     }
 }
 __device__ __forceinline__ void epilogue_chunk(const unsigned (&r)[32], int m, int n, const EpiArgs p, bool row_ok,
@@ -307,7 +324,7 @@ __device__ __forceinline__ void epilogue_chunk(const unsigned (&r)[32], int m, i
     if (ep.steps & B200FC_STEP_DEQUANT) {
         if (ep.deq_per_oc) {
             float sc[32];
-            load_col_vec(ep.deq_per_oc, n, p.n1, sc);
+            load_col_vec(p.cv_deq, ep.deq_per_oc, n, p.n1, sc);
 #pragma unroll
             for (int j = 0; j < 32; j++) v[j] *= ep.deq_scale * sc[j];
         } else {
@@ -317,7 +334,7 @@ __device__ __forceinline__ void epilogue_chunk(const unsigned (&r)[32], int m, i
     }
     if (ep.steps & B200FC_STEP_BIAS) {
         float bs[32];
-        load_col_vec(ep.bias, n, p.n1, bs);
+        load_col_vec(p.cv_bias, ep.bias, n, p.n1, bs);
 #pragma unroll
         for (int j = 0; j < 32; j++) v[j] += bs[j];
     }
@@ -328,7 +345,7 @@ __device__ __forceinline__ void epilogue_chunk(const unsigned (&r)[32], int m, i
     if (ep.steps & B200FC_STEP_QUANT) {
         if (ep.q_per_oc) {
             float qs[32];
-            load_col_vec(ep.q_per_oc, n, p.n1, qs);
+            load_col_vec(p.cv_q, ep.q_per_oc, n, p.n1, qs);
 #pragma unroll
             for (int j = 0; j < 32; j++) v[j] *= qs[j];
         } else {
@@ -572,7 +589,9 @@ template <int BN> struct Cfg2 {
     static constexpr int B_BYTES = (BN / 2) * SLAB_BYTES;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + EPI_TILE_BYTES;
+    // per epilogue warp: the tile's per-column vectors (dequantisation scales, bias, quantisation scales)
+    static constexpr int COLVEC_BYTES = 4 * 3 * BN * 4;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + EPI_TILE_BYTES + COLVEC_BYTES;
 };
 
 __device__ __forceinline__ unsigned cluster_ctarank() {
@@ -809,6 +828,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // ---------------- epilogue warps (both CTAs, own 128 rows) ----------------
         const int quarter = warp & 3;
         unsigned* epi_tile = (unsigned*)(smem + C::STAGES * C::STAGE_BYTES + 256) + quarter * EPI_TILE_WORDS;
+        float* colvec = (float*)(smem + C::STAGES * C::STAGE_BYTES + 256 + EPI_TILE_BYTES) + quarter * 3 * BN;
+        const bool plain_ep = !(p.ep.steps & B200FC_STEP_SILU_MUL) && !p.ep.mc_reduce && p.ep.out_dtype != B200FC_S32;
+        const bool use_deq = plain_ep && (p.ep.steps & B200FC_STEP_DEQUANT) && p.ep.deq_per_oc;
+        const bool use_bias = plain_ep && (p.ep.steps & B200FC_STEP_BIAS) && p.ep.bias;
+        const bool use_q = plain_ep && (p.ep.steps & B200FC_STEP_QUANT) && p.ep.q_per_oc;
+        const bool any_vec = use_deq || use_bias || use_q;
         int it = 0;
         bool ok = true;
         const unsigned leader_acc_empty = mapa_rank(bar_acc_empty, 0);
@@ -818,6 +843,19 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int ab = it & 1;
             const unsigned acc_phase = (unsigned)(it >> 1) & 1;
             const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+            // while the tile's MMAs run: this warp's copy of the per-column vectors of the tile's BN columns (clamped
+            // to the last valid column), so that no chunk waits for global memory
+            if (any_vec) {
+                const int nb = p.n0 + tn * BN;
+#pragma unroll
+                for (int j = 0; j < BN / 32; j++) {
+                    const int col = min(nb + j * 32 + lane, p.n1 - 1);
+                    if (use_deq) colvec[j * 32 + lane] = __ldg(p.ep.deq_per_oc + col);
+                    if (use_bias) colvec[BN + j * 32 + lane] = __ldg(p.ep.bias + col);
+                    if (use_q) colvec[2 * BN + j * 32 + lane] = __ldg(p.ep.q_per_oc + col);
+                }
+                __syncwarp();
+            }
             if (!mbar_wait<EPI_SLEEP_NS>(bar_acc_full + 8 * ab, acc_phase, abort_flag, p.wait_limit_ns)) { ok = false; break; }
             tc_fence_after();
             const int m = tm * (2 * BM) + (int)rank * BM + quarter * 32 + lane;
@@ -830,7 +868,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 unsigned r[32];
                 tc_ld32(taddr + (unsigned)(c * 32), r);
                 tc_wait_ld();
-                epilogue_chunk(r, m, n, EpiArgs{&p.ep, p.vec_ok, p.acc_is_int, p.n1, p.M, epi_tile}, row_ok, c_offset);
+                EpiArgs ea{&p.ep, p.vec_ok, p.acc_is_int, p.n1, p.M, epi_tile};
+                if (use_deq) ea.cv_deq = colvec + c * 32;
+                if (use_bias) ea.cv_bias = colvec + BN + c * 32;
+                if (use_q) ea.cv_q = colvec + 2 * BN + c * 32;
+                epilogue_chunk(r, m, n, ea, row_ok, c_offset);
             }
             tc_fence_before();
             if (p.ar_world) __threadfence_system();  // this warp's part of the tile is visible to every GPU ...
