@@ -209,7 +209,7 @@ typedef struct {
     int comm_sms;            /* SMs that reduce instead of multiplying from the start (even; 8 measured best at 8 GPUs) */
 } b200fc_allreduce_t;
 int b200fc_mlp_down_allreduce(b200fc_mlp_t* mlp, int M, const b200fc_allreduce_t* ar, void* stream);
-/* x and out in HOST memory; copies, runs, copies back, synchronises.  From M = 2048 on the rows flow through a
+/* x and out in HOST memory; copies, runs, copies back, synchronises.  From M = 512 on the rows flow through a
  * copy-in / compute / copy-out pipeline over three internal streams (short row chunks first and last, so that little of
  * the PCIe time is exposed), which needs pinned host buffers to overlap; results per row are those of b200fc_mlp_run up
  * to the last bit of a bf16 (a short chunk may take the K-split route of the GEMM, which adds in another order). */

@@ -979,7 +979,9 @@ int b200fc_mlp_run_host(b200fc_mlp_t* h, const void* x, int64_t ldx, int M, void
     int rc = grow(&m.stage_x, &m.stage_x_bytes, row * M, s);
     if (!rc) rc = grow(&m.stage_o, &m.stage_o_bytes, row * M, s);
     if (rc) return rc;
-    if (M < 2048) {
+    static int pipe_min = -1;
+    if (pipe_min < 0) { const char* e = getenv("B200FC_HOST_PIPE_MIN"); pipe_min = e ? atoi(e) : 512; }
+    if (M < pipe_min) {
         B200FC_CUDA(cudaMemcpy2DAsync(m.stage_x, row, x, (size_t)ldx, row, (size_t)M, cudaMemcpyHostToDevice, s));
         rc = mlp_run_device(m, m.stage_x, (int64_t)row, M, m.stage_o, B200FC_BF16, (int64_t)row, s);
         if (rc) return rc;

@@ -139,9 +139,22 @@ def test_mlp_ragged_last_round():
     assert np.abs(bf16_to_f32(act[rows]) - bf16_to_f32(ref_act)).max() < 0.02 * np.abs(bf16_to_f32(ref_act)).max()
 
 
+@pytest.mark.parametrize("M", [512, 700, 1100])
+def test_mlp_host_entry_point_mid_size_batches(M):
+    """from M = 512 on the host-buffer call is pipelined with the library's own choice of row chunks"""
+    rng = np.random.default_rng(M)
+    K, N = 256, 512
+    x, gate, up, down = make_mlp_inputs(rng, M, K, N)
+    mlp = capi.Mlp(gate.ctypes.data, up.ctypes.data, down.ctypes.data, K, N)
+    out = np.zeros((M, K), np.uint16)
+    mlp.run_host(x.ctypes.data, x.strides[0], M, out.ctypes.data, out.strides[0])
+    capi.sync_check()
+    assert H.rel_to_max(bf16_to_f32(out), bf16_to_f32(port.mlp(x, gate, up, down))) < 1e-2
+
+
 @pytest.mark.parametrize("plan", [None, "1,3,5;4,1,1,3", "2;9", "9;1,1"])
 def test_mlp_host_entry_point_large_batch_is_pipelined(plan, monkeypatch):
-    """M >= 2048 goes through the copy / compute / copy pipeline, gate/up and down cut into row chunks independently
+    """large batches go through the copy / compute / copy pipeline, gate/up and down cut into row chunks independently
     (the library's own choice, and forced uneven ones); rows must land where they belong."""
     if plan is None:
         monkeypatch.delenv("B200FC_HOST_PLAN", raising=False)
