@@ -63,6 +63,10 @@ struct GemmParams {
     // 2-CTA kernel, splits == 1: > 0 = only the first item_limit tiles (in tile order) are computed by this launch; the
     // launcher hands the few tiles of a ragged last round to a second, K-split launch instead (launch_gemm_tc)
     int item_limit = 0;
+    // 2-CTA kernel: > 0 = tiles are ordered in panels of this many row tiles (all column blocks of panel 0, then panel
+    // 1, ...) and the activation loads carry an L2 evict-last hint, so that a panel of activations (panel_rows x 256 rows
+    // x K) stays in L2 while the weights stream past it; 0 = one panel (row tile fastest over the whole M)
+    int panel_rows = 0;
     // Fused tensor-parallel all-reduce (2-CTA kernel, ar_world > 0).  The epilogue stores this rank's bf16 tile into
     // its replica of a symmetric "partial" buffer (ep.C) and bumps the tile's arrival counter on the tile's owner
     // rank; the last CTA pairs of the grid do not multiply but reduce the tiles this rank owns.
@@ -618,6 +622,25 @@ __device__ __forceinline__ void tma_load_2d_pair(unsigned dst, const CUtensorMap
         ::"r"(dst), "l"(map), "r"(leader_bar), "r"(x), "r"(y)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_2d_pair_keep(unsigned dst, const CUtensorMap* map, unsigned leader_bar, int x, int y,
+                                                      unsigned long long policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(dst), "l"(map), "r"(leader_bar), "r"(x), "r"(y), "l"(policy)
+        : "memory");
+}
+// tile index (the order in which the CTA pairs take tiles) -> row tile tm and column tile tn
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
+    if (p.panel_rows <= 0 || p.panel_rows >= p.tiles_m) {
+        tm = tile % p.tiles_m; tn = tile / p.tiles_m;
+    } else {
+        const int per_panel = p.panel_rows * p.tiles_n;
+        const int pi = tile / per_panel, r = tile - pi * per_panel;
+        const int ph = min(p.panel_rows, p.tiles_m - pi * p.panel_rows);   // the last panel may be shorter
+        tm = pi * p.panel_rows + r % ph; tn = r / ph;
+    }
+}
 __device__ __forceinline__ void tc_commit_pair(unsigned bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
                  ::"r"(bar), "h"((unsigned short)3)
@@ -663,7 +686,8 @@ __device__ void allreduce_units(const GemmParams& p, int num_tiles, volatile int
         const int u = *unit_slot;
         if (u >= n_units) break;
         const int tile = p.ar_rank + (u >> 1) * p.ar_world, half = u & 1;
-        const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+        int tm, tn;
+        tile_coords(p, tile, tm, tn);
         const int r0 = tm * (2 * BM) + half * BM, c0 = p.n0 + tn * BN;
         const int rows = min(BM, p.M - r0), cols = min(BN, p.n1 - c0);
         if (threadIdx.x == 0 && rows > 0) {
@@ -774,10 +798,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             unsigned phase = 0;
             bool ok = true;
             const unsigned leader_full = mapa_rank(bar_full, 0);
+            unsigned long long keep_policy = 0;
+            if (p.panel_rows > 0) asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(keep_policy));
             for (int item = pair; item < num_items && ok; item += num_pairs) {
                 const int tile = item % num_tiles, split = item / num_tiles;
                 const int ks0 = p.k_slabs * split / p.splits, ks1 = p.k_slabs * (split + 1) / p.splits;
-                const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+                int tm, tn;
+                tile_coords(p, tile, tm, tn);
                 const int row_a = tm * (2 * BM) + (int)rank * BM;
                 const int row_w = p.n0 + tn * BN + (int)rank * (BN / 2);
                 for (int ks = ks0; ks < ks1; ks++) {
@@ -785,7 +812,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     if (leader) mbar_expect_tx(bar_full + 8 * stage, 2 * C::STAGE_BYTES);
                     const unsigned sa = smem_u32(smem + stage * C::STAGE_BYTES);
                     const int kx = ks * (I8 ? SLAB_BYTES : SLAB_BYTES / 2);
-                    tma_load_2d_pair(sa, &map_a, leader_full + 8 * stage, kx, row_a);
+                    if (p.panel_rows > 0) tma_load_2d_pair_keep(sa, &map_a, leader_full + 8 * stage, kx, row_a, keep_policy);
+                    else tma_load_2d_pair(sa, &map_a, leader_full + 8 * stage, kx, row_a);
                     tma_load_2d_pair(sa + C::A_BYTES, &map_w, leader_full + 8 * stage, kx, row_w);
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -842,7 +870,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const long long c_offset = (long long)split * p.split_stride;
             const int ab = it & 1;
             const unsigned acc_phase = (unsigned)(it >> 1) & 1;
-            const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+            int tm, tn;
+            tile_coords(p, tile, tm, tn);
             // while the tile's MMAs run: this warp's copy of the per-column vectors of the tile's BN columns (clamped
             // to the last valid column), so that no chunk waits for global memory
             if (any_vec) {
@@ -1136,6 +1165,16 @@ int launch_cfg2(const CUtensorMap& ma, const CUtensorMap& mw, GemmParams p, cuda
     return B200FC_OK;
 }
 
+// B200FC_GEMM_PANEL=n: row tiles per panel of the 2-CTA GEMM's tile order (0 = no panels); unset = by shape
+int panel_rows_setting() {
+    static int v = -2;
+    if (v == -2) {
+        const char* e = getenv("B200FC_GEMM_PANEL");
+        v = e ? atoi(e) : -1;
+    }
+    return v;
+}
+
 // B200FC_GEMM_TAIL=0 keeps the tiles of a ragged last round in the main launch (for measurements)
 bool tail_split_enabled() {
     static int v = -1;
@@ -1286,15 +1325,27 @@ int launch_gemm_tc(const void* W_data, int w_dtype, int W_K_pad, int W_N_pad, co
         // GEMM of their own, which takes the K-split route (a few tiles, every pair busy for a fraction of a tile
         // time, then the reduction kernel with the same post-ops).
         const int tiles = p.tiles_m * p.tiles_n, pairs = num_sms() / 2;
+        // Activations larger than what stays in L2 beside the streaming weights (the whole of them is touched by every
+        // round of tiles): take the tiles panel by panel so that only panel_rows x 256 rows are live at a time, and keep
+        // those in L2 (evict-last hint on their loads).  Weights are then read once per panel.
+        {
+            const int want = panel_rows_setting();
+            const size_t a_bytes = (size_t)M * (size_t)K * (i8 ? 1 : 2);
+            if (want > 0) p.panel_rows = want;
+            else if (want < 0 && a_bytes > ((size_t)48 << 20) && p.tiles_m >= 12 && p.tiles_n >= 2 * pairs / 8) p.panel_rows = 8;
+            if (p.panel_rows >= p.tiles_m) p.panel_rows = 0;
+        }
         const int rem = tiles % pairs;
         const int last_cols = nspan - (p.tiles_n - 1) * bn2;
-        const int whole = rem / p.tiles_m, part = rem % p.tiles_m;   // whole column blocks / tiles of a partial one
+        // (the last tiles in tile order lie in the last panel, ph row tiles high)
+        const int ph = p.panel_rows > 0 ? p.tiles_m - (p.tiles_m - 1) / p.panel_rows * p.panel_rows : p.tiles_m;
+        const int whole = rem / ph, part = rem % ph;   // whole column blocks of that panel / tiles of a partial one
         if (tail_split_enabled() && tiles > pairs && rem > 0 && (whole == 0 || part == 0) && rem * 4 <= pairs &&
             p.k_slabs >= 96 && last_cols > 128 && !ep.mc_reduce) {
             p.item_limit = tiles - rem;
             rc = i8 ? launch_cfg2<256, true>(ma, mw, p, s) : launch_cfg2<256, false>(ma, mw, p, s);
             if (rc) return rc;
-            const long long row0 = whole ? 0 : (long long)(p.tiles_m - part) * 2 * BM;
+            const long long row0 = (long long)(p.tiles_m - (whole ? ph : part)) * 2 * BM;
             const int col0 = n0 + (p.tiles_n - (whole ? whole : 1)) * bn2;
             Epilogue e2 = ep;
             e2.C = (char*)ep.C + row0 * ep.ldc;
