@@ -66,8 +66,12 @@ def test_config1_bf16_linear_256x4096x4096_bias():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("M,K,N", [(2048, 4096, 22016), (2048, 11008, 4096), (4096, 8192, 7168)])
+@pytest.mark.parametrize("M,K,N", [(2048, 4096, 22016), (2048, 11008, 4096), (4096, 8192, 7168), (4096, 8192, 14336),
+                                   (3300, 8192, 5888)])
 def test_llama_shaped_gemms_against_fp32(M, K, N):
+    """the last three are taken in panels of 8 row tiles (x over 48 MB) and leave a ragged last round that a K-split
+    launch takes over: the bottom four tiles of the last column block, the last column block of the last panel, and a
+    short last panel (13 row tiles: 8 + 5)"""
     dev = torch.device("cuda")
     g = torch.Generator(device=dev); g.manual_seed(M + N)
     A = randn_bf16((M, K), 1.0, g, dev)
