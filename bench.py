@@ -444,12 +444,32 @@ def run_ours(args, w, M, name):
         k_ms = time_steps(torch, gate_up_only, args.steps)
         k_flops = 4.0 * M * H * Is
         achieved = k_flops / (k_ms * 1e-3) / 1e12
+        # The loop above is the kernel's average launch over args.steps back-to-back launches.  When that loop is long
+        # (the 70B launch is 3 ms: 200 of them are 0.6 s, on a GPU still warm from the timed steps) it runs under the
+        # power cap, and the matching denominator is the sustained cuBLAS figure; a short loop is compared with the
+        # burst figure.  Both fractions are printed whichever is chosen, and `burst` times single launches the way the
+        # burst peak was taken: after an idle pause, best of five.
+        loop_s = k_ms * 1e-3 * args.steps
+        long_loop = loop_s >= 0.25
+        k_peak = peaks["bf16_sustained"] if long_loop else peaks["bf16_burst"]
+        best = None
+        for _ in range(5):
+            time.sleep(0.3)
+            b_ms = time_steps(torch, gate_up_only, 1)
+            best = b_ms if best is None else min(best, b_ms)
+        b_ms = max_over_ranks(best)
         roofline = {"kernel": "gemm_tc2_kernel (gate/up projection + SiLU*up epilogue)", "bound": "tensor",
-                    "achieved": achieved, "peak": peaks["bf16_burst"], "unit": "TFLOP/s",
-                    "frac": achieved / peaks["bf16_burst"],
-                    "peak_source": peaks["source"] + " (cuBLAS bf16 burst figure: the kernel is timed alone, in a loop "
-                                                     "far shorter than the power-cap time constant)",
+                    "achieved": achieved, "peak": k_peak, "unit": "TFLOP/s", "frac": achieved / k_peak,
+                    "peak_source": peaks["source"] + (
+                        " (cuBLAS bf16 SUSTAINED figure: %d launches back to back are %.2f s, the power-capped regime)"
+                        % (args.steps, loop_s) if long_loop else
+                        " (cuBLAS bf16 burst figure: %d launches back to back are %.3f s, shorter than the power cap's "
+                        "reaction)" % (args.steps, loop_s)),
+                    "frac_of_burst_peak": achieved / peaks["bf16_burst"],
                     "frac_of_sustained_peak": achieved / peaks["bf16_sustained"], "us_per_launch": k_ms * 1e3,
+                    "burst": {"achieved": k_flops / (b_ms * 1e-3) / 1e12, "peak": peaks["bf16_burst"],
+                              "frac": k_flops / (b_ms * 1e-3) / 1e12 / peaks["bf16_burst"], "us_per_launch": b_ms * 1e3,
+                              "how": "single launches, each after 0.3 s of idle, best of 5"},
                     "flops_per_launch": k_flops, "traffic": ncu_traffic_bytes(name, world)}
 
     sustained = None
