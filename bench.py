@@ -15,7 +15,9 @@ so every step streams them from HBM again.
 
 The line also carries: parity (the timed path's output against an fp32 sum of the per-rank contributions over NCCL
 and, for the first rows, against the CPU oracle; a failure exits non-zero), e2e (the same step fed from pinned host
-memory with the result copied back), roofline of the dominant kernel (gate/up GEMM, timed live with CUDA events), a
+memory with the result copied back), roofline of the dominant kernel (gate/up GEMM, timed live with CUDA events: the
+average of --steps launches against the sustained library figure when that loop is long, else the burst one, and single
+launches after an idle pause against the burst figure), a
 sustained leg (the same step repeated for over a second), decode-shaped legs (M = 1 and 16, weight stream GB/s), the
 other single-GPU configurations, the CPU baseline (the reference's own AMX kernels on the host cores when the CPU has
 AMX, else the plain C++ oracle port), clocks sampled during the timed region, and the number of kernels this library
