@@ -215,6 +215,11 @@ int b200fc_mlp_down_allreduce(b200fc_mlp_t* mlp, int M, const b200fc_allreduce_t
  * to the last bit of a bf16 (a short chunk may take the K-split route of the GEMM, which adds in another order). */
 int b200fc_mlp_run_host(b200fc_mlp_t* mlp, const void* x, int64_t ldx_bytes, int M, void* out, int64_t ldo_bytes,
                         void* stream);
+/* How b200fc_mlp_run_host cuts a batch of M rows of an MLP with hidden size K and intermediate size N: rows per
+ * gate/up launch (each preceded by the copy-in of its rows) and rows per down launch (each followed by the copy-out of
+ * its rows); both lists sum to M.  A pure host function (no reference counterpart: AMX_MLP::MLP::run works in place in
+ * host memory, tests/amx-mlp.cpp:778-783); `capacity` = entries each array can take. */
+int b200fc_mlp_host_plan(int M, int K, int N, int* gate_up_rows, int* down_rows, int capacity, int* n_gate_up, int* n_down);
 /* The same forward for decode-shaped batches (1 <= M <= 16) WITHOUT any allocation — no counterpart in the
  * reference.  For callers that may not enter the CUDA allocator while they run (a serving loop with a frozen memory
  * plan, code that must not trigger the device synchronisation cudaMalloc / cudaFree imply).  The gate/up activation

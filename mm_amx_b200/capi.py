@@ -42,6 +42,9 @@ SIGNATURES = {
     "b200fc_last_error": (ctypes.c_char_p, []),
     "b200fc_version": (ctypes.c_char_p, []),
     "b200fc_launch_count": (c_i64, []),
+    "b200fc_mlp_host_plan": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int),
+                                            ctypes.POINTER(ctypes.c_int), ctypes.c_int, ctypes.POINTER(ctypes.c_int),
+                                            ctypes.POINTER(ctypes.c_int)]),
     "b200fc_sync_check": (c_int, [c_void_p]),
     "b200fc_set_wait_limit_ns": (c_int, [ctypes.c_uint64]),
     "b200fc_set_sm_limit": (c_int, [c_int]),
@@ -301,3 +304,11 @@ def add_round_bf16(a_ptr, b_ptr, out_ptr, n, stream=None):
 
 def flush_l2(stream=None):
     check(lib().b200fc_flush_l2(stream))
+
+
+def mlp_host_plan(M, K, N, capacity=4096):
+    """row chunks of the host-buffer MLP call: (rows per gate/up launch, rows per down launch)"""
+    g = (ctypes.c_int * capacity)(); d = (ctypes.c_int * capacity)()
+    ng, nd = ctypes.c_int(), ctypes.c_int()
+    check(lib().b200fc_mlp_host_plan(M, K, N, g, d, capacity, ctypes.byref(ng), ctypes.byref(nd)))
+    return list(g[:ng.value]), list(d[:nd.value])

@@ -891,7 +891,7 @@ std::vector<int> growing(int tiles, int first, double ratio, int cap) {
 }
 }  // namespace
 
-static void host_plan(Mlp& m, int M, std::vector<int>* gu, std::vector<int>* dn) {
+static void host_plan(Mlp* cache, int K_, int Ns_, int M, std::vector<int>* gu, std::vector<int>* dn) {
     const int tile = kPlanTile;
     const int tiles = (M + tile - 1) / tile;
     auto finish = [&](std::vector<int>& v) {  // tiles -> rows, clipped to M
@@ -923,21 +923,23 @@ static void host_plan(Mlp& m, int M, std::vector<int>* gu, std::vector<int>* dn)
             return;
         }
     }
-    if (m.plan_M == M && !m.plan_gu.empty()) { *gu = m.plan_gu; *dn = m.plan_dn; return; }
+    if (cache && cache->plan_M == M && !cache->plan_gu.empty()) { *gu = cache->plan_gu; *dn = cache->plan_dn; return; }
     int dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+        cudaGetLastError();   // no device (a host-only process asking for the plan): a B200's 148 SMs
+        sms = 148;
+    }
     PlanModel pm;
     pm.pairs = std::max(1, sms / 2);
     const double pair_rate = 1.35e15 / 74.0;  // flop/s of one CTA pair in a long launch
-    pm.cols_gu = (2 * m.Ns + 255) / 256;
-    pm.cols_dn = (m.K + 255) / 256;
-    pm.slabs_gu = (m.K + 63) / 64;
-    pm.slabs_dn = (m.Ns + 63) / 64;
-    pm.t_gu_wave = 2.0 * 256 * 256 * m.K / pair_rate;
-    pm.t_dn_wave = 2.0 * 256 * 256 * m.Ns / pair_rate;
-    pm.h2d_tile = (double)tile * m.K * 2 / 50e9;
-    pm.d2h_tile = (double)tile * m.K * 2 / 45e9;
+    pm.cols_gu = (2 * Ns_ + 255) / 256;
+    pm.cols_dn = (K_ + 255) / 256;
+    pm.slabs_gu = (K_ + 63) / 64;
+    pm.slabs_dn = (Ns_ + 63) / 64;
+    pm.t_gu_wave = 2.0 * 256 * 256 * K_ / pair_rate;
+    pm.t_dn_wave = 2.0 * 256 * 256 * Ns_ / pair_rate;
+    pm.h2d_tile = (double)tile * K_ * 2 / 50e9;
+    pm.d2h_tile = (double)tile * K_ * 2 / 45e9;
     std::vector<std::vector<int>> fam_g, fam_d;
     const int firsts[] = {1, 2, 3, 4};
     const double ratios[] = {1.0, 1.5, 2.0};
@@ -966,8 +968,22 @@ static void host_plan(Mlp& m, int M, std::vector<int>* gu, std::vector<int>* dn)
         if (t < best) { best = t; g = a; d = b; }
     }
     finish(g); finish(d);
-    m.plan_M = M; m.plan_gu = g; m.plan_dn = d;
+    if (cache) { cache->plan_M = M; cache->plan_gu = g; cache->plan_dn = d; }
     gu->swap(g); dn->swap(d);
+}
+
+int b200fc_mlp_host_plan(int M, int K, int N, int* gate_up_rows, int* down_rows, int capacity, int* n_gate_up, int* n_down) {
+    if (M <= 0 || K <= 0 || N <= 0 || !gate_up_rows || !down_rows || !n_gate_up || !n_down || capacity <= 0) {
+        set_error("mlp_host_plan: bad argument");
+        return B200FC_ERR_INVALID;
+    }
+    std::vector<int> g, d;
+    host_plan(nullptr, K, N, M, &g, &d);
+    *n_gate_up = (int)g.size(); *n_down = (int)d.size();
+    if ((int)g.size() > capacity || (int)d.size() > capacity) { set_error("mlp_host_plan: capacity too small"); return B200FC_ERR_INVALID; }
+    for (size_t i = 0; i < g.size(); i++) gate_up_rows[i] = g[i];
+    for (size_t i = 0; i < d.size(); i++) down_rows[i] = d[i];
+    return B200FC_OK;
 }
 
 int b200fc_mlp_run_host(b200fc_mlp_t* h, const void* x, int64_t ldx, int M, void* out, int64_t ldo, void* stream) {
@@ -994,7 +1010,7 @@ int b200fc_mlp_run_host(b200fc_mlp_t* h, const void* x, int64_t ldx, int M, void
     // another (host_plan): short chunks at the head of the first and at the tail of the second keep the exposed
     // copies small, long chunks in between keep the GEMM waves full.
     std::vector<int> gu_rows, dn_rows;
-    host_plan(m, M, &gu_rows, &dn_rows);
+    host_plan(&m, m.K, m.Ns, M, &gu_rows, &dn_rows);
     if (!m.pipe_streams[0]) {
         for (int i = 0; i < 3; i++) B200FC_CUDA(cudaStreamCreateWithFlags(&m.pipe_streams[i], cudaStreamNonBlocking));
         B200FC_CUDA(cudaEventCreateWithFlags(&m.ev_fork, cudaEventDisableTiming));
