@@ -213,8 +213,11 @@ def decode_attention(q, k, v, scale=1.0, seq_lens=None):
     """One query token per sequence: q [B, H, D], k and v [B, Hkv, N, D] (bf16 bits) -> fp32 [B, H, D].
     Restates one_head_attention of the reference (include/kernels_mha.hpp:325-355: scores = q k^T, softmax over the
     keys, weighted sum of the values; the reference applies no scale, i.e. scale = 1) in float64, with query head h
-    reading kv head h // (H // Hkv) and an optional per-sequence length.  PARITY UNPINNED: the reference's kernel is
-    fp32 AVX2 code outside the compiled oracle; this is the textbook definition it implements."""
+    reading kv head h // (H // Hkv) and an optional per-sequence length.  Pinned: tests/golden/golden_mha_v1.npz holds
+    outputs of the reference's own kernel (MHA2Kernels through oracle/ref_mha_harness.cpp) and this function agrees with
+    them to 1e-6 of max |ref| (scale = 1, one kv head per query head, N a multiple of 8 — for other N the reference's
+    AVX2 code itself leaves this definition); the scale, grouped heads and sequence lengths are this library's
+    extensions of it."""
     qf = bf16_to_f32(np.ascontiguousarray(q, np.uint16)).astype(np.float64)
     kf = bf16_to_f32(np.ascontiguousarray(k, np.uint16)).astype(np.float64)
     vf = bf16_to_f32(np.ascontiguousarray(v, np.uint16)).astype(np.float64)

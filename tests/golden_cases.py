@@ -128,3 +128,23 @@ def activation_points():
     x = x.astype(np.float32)
     pad = (-x.size) % 16
     return np.concatenate([x, np.zeros(pad, np.float32)])
+
+
+def mha_cases():
+    """one-token attention of the reference (MHA2Kernels, include/kernels_mha.hpp:89-318): B sequences, H heads (the
+    reference has no grouped heads), N cached tokens, head size K, sub-states of bn tokens.  N is a multiple of 8 in
+    every case: for other N the reference's own AVX2 kernels leave the textbook result (checked at N = 17, 255, 300,
+    700: up to a quarter of max |result|), so those lengths are covered against the float64 restatement only."""
+    shapes = [(1, 2, 16, 64, 256), (2, 4, 304, 128, 256), (1, 3, 1000, 128, 256), (2, 2, 704, 64, 128),
+              (1, 1, 248, 128, 256), (3, 5, 2048, 128, 256), (1, 2, 520, 32, 64), (2, 8, 8, 128, 256),
+              (1, 4, 4096, 64, 512)]
+    return {"mha/B%d_H%d_N%d_K%d_bn%d" % s: dict(B=s[0], H=s[1], N=s[2], K=s[3], bn=s[4]) for s in shapes}
+
+
+def mha_inputs(case):
+    """bf16 bit patterns: q [B, H, K], k and v [B, H, N, K] (the reference computes in fp32 on the widened values)"""
+    rng = np.random.default_rng(_seed("mha %(B)d %(H)d %(N)d %(K)d" % case))
+    B, H, N, K = case["B"], case["H"], case["N"], case["K"]
+    return dict(q=bf16_bits((rng.standard_normal((B, H, K)) * 0.5).astype(np.float32)),
+                k=bf16_bits((rng.standard_normal((B, H, N, K)) * 0.5).astype(np.float32)),
+                v=bf16_bits(rng.standard_normal((B, H, N, K)).astype(np.float32)))

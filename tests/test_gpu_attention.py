@@ -1,9 +1,12 @@
 """GPU: decode attention (b200fc_decode_attention) against oracle.port.decode_attention (float64 restatement of
 include/kernels_mha.hpp:325-355).  Bars: fp32 output within 5e-3 of max |ref| (the probabilities pass through bf16 on
 their way into the tensor-core product, 2^-9 relative each), bf16 output within 1e-2."""
+import os
+
 import numpy as np
 import pytest
 
+import golden_cases as gc
 import helpers as H
 from mm_amx_b200 import capi
 from oracle import port
@@ -118,3 +121,22 @@ def test_decode_attention_strided_cache_and_padded_heads():
     ref = port.decode_attention(q_full[:, :, :D], kc[:, :, :N, :D], vc[:, :, :N, :D], 0.09)
     assert H.rel_to_max(got[:, :, :D], ref) < 5e-3
     assert (got[:, :, D:].view(np.uint32) == 0xCDCDCDCD).all()      # nothing written past the head size
+
+
+GOLD_MHA = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "golden_mha_v1.npz"))
+
+
+@pytest.mark.parametrize("name", sorted(gc.mha_cases()))
+def test_decode_attention_matches_the_reference(name):
+    """the CUDA kernel against outputs recorded from the reference's own one-token attention (MHA2Kernels,
+    include/kernels_mha.hpp:89-318; no scale factor, one kv head per query head): fp32 output within 5e-3 of max |ref|
+    (the probabilities pass through bf16 on their way into the tensor-core product)"""
+    case = gc.mha_cases()[name]
+    inp = gc.mha_inputs(case)
+    ref = GOLD_MHA[name]
+    if case["K"] not in (64, 128):
+        with pytest.raises(capi.B200FCError):
+            run(inp["q"], inp["k"], inp["v"], 1.0)
+        return
+    got = run(inp["q"], inp["k"], inp["v"], 1.0)
+    assert H.rel_to_max(got, ref) < 5e-3

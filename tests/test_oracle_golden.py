@@ -151,3 +151,19 @@ def test_int4_group_quantiser_properties():
     ref = bf16_to_f32(x).astype(np.float64) @ port.dequant_int4(q, d).astype(np.float64).T
     got = port.gemm_bf16_w4(x, q, d)
     assert np.allclose(got, ref, rtol=1e-5, atol=1e-6)
+
+
+GOLD_MHA = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "golden_mha_v1.npz"))
+
+
+@pytest.mark.parametrize("name", sorted(gc.mha_cases()))
+def test_decode_attention_oracle_pinned_to_the_reference(name):
+    """oracle.port.decode_attention (float64, scale = 1 as in the reference) against outputs recorded from the
+    reference's own one-token attention, MHA2Kernels (include/kernels_mha.hpp:89-318; fp32 AVX2, exponentials by
+    polynomial, sub-states of bn tokens combined afterwards): measured <= 1e-6 of max |ref|, asserted at 1e-5."""
+    case = gc.mha_cases()[name]
+    inp = gc.mha_inputs(case)
+    ref = GOLD_MHA[name]
+    got = port.decode_attention(inp["q"], inp["k"], inp["v"], 1.0)
+    assert got.shape == ref.shape
+    assert np.abs(got - ref).max() <= 1e-5 * np.abs(ref).max()
